@@ -1,0 +1,62 @@
+// extern "C" surface of libpare_b200: argument checks and dispatch only.
+#include "common.cuh"
+
+namespace pare {
+size_t gemv_workspace_bytes(int M, int N, int K, int G);
+int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale,
+                 const float* zero, const void* meta_h2, const int32_t* col_perm, const float* input_scale,
+                 const void* bias, void* y, int64_t ldy, int M, int N, int K, int G, void* workspace,
+                 size_t workspace_bytes, cudaStream_t stream);
+void gemv_set_tuning(int rb, int splits, int pf);
+}  // namespace pare
+
+extern "C" {
+
+int pare_version(void) { return 100; }
+
+const char* pare_status_string(int status) {
+  switch (status) {
+    case PARE_OK: return "ok";
+    case PARE_ERR_SHAPE: return "invalid shape";
+    case PARE_ERR_DTYPE: return "unsupported dtype";
+    case PARE_ERR_ALIGN: return "pointer or leading dimension not 16-byte aligned";
+    case PARE_ERR_WORKSPACE: return "workspace missing or too small";
+    case PARE_ERR_UNSUPPORTED: return "unsupported configuration";
+    case PARE_ERR_CUDA: return "CUDA runtime error at launch";
+    case PARE_ERR_TIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+  }
+}
+
+size_t pare_w4a16_workspace_bytes(int M, int N, int K, int group_size) {
+  if (M <= 0 || N <= 0 || K <= 0 || group_size <= 0) return 0;
+  return pare::gemv_workspace_bytes(M, N, K, group_size);
+}
+
+int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale,
+                       const float* zero, const void* meta_h2, const int32_t* col_perm, const float* input_scale,
+                       const void* bias, void* y, int64_t ldy, int M, int N, int K, int group_size,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  PARE_REQUIRE(M > 0 && N > 0 && K > 0 && group_size > 0, PARE_ERR_SHAPE);
+  PARE_REQUIRE((K % 2) == 0 && (K % group_size) == 0, PARE_ERR_SHAPE);
+  PARE_REQUIRE(ldx >= K && ldy >= N, PARE_ERR_SHAPE);
+  PARE_REQUIRE(x_dtype == PARE_F16 || x_dtype == PARE_BF16, PARE_ERR_DTYPE);
+  PARE_REQUIRE(x && packed && y && (meta_h2 || (scale && zero)), PARE_ERR_SHAPE);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const size_t esz = 2;
+  for (int m0 = 0; m0 < M; m0 += 16) {
+    const int mc = (M - m0) < 16 ? (M - m0) : 16;
+    const int rc = pare::gemv_forward(reinterpret_cast<const unsigned char*>(x) + (size_t)m0 * ldx * esz, x_dtype, ldx,
+                                      packed, scale, zero, meta_h2, col_perm, input_scale, bias,
+                                      reinterpret_cast<unsigned char*>(y) + (size_t)m0 * ldy * esz, ldy, mc, N, K,
+                                      group_size, workspace, workspace_bytes, s);
+    if (rc != PARE_OK) return rc;
+  }
+  return PARE_OK;
+}
+
+void pare_w4a16_set_tuning(int row_blocks, int k_splits, int prefetch) {
+  pare::gemv_set_tuning(row_blocks, k_splits, prefetch);
+}
+
+}  // extern "C"

@@ -1,0 +1,149 @@
+// Shared device helpers for the sm_100a kernels of libpare_b200.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "pare_b200.h"
+
+namespace pare {
+
+// ---- status helpers (host) -------------------------------------------------
+#define PARE_REQUIRE(cond, code) \
+  do {                           \
+    if (!(cond)) return (code);  \
+  } while (0)
+
+inline int launch_status() { return cudaGetLastError() == cudaSuccess ? PARE_OK : PARE_ERR_CUDA; }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- programmatic dependent launch ------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start
+// while its predecessor still runs.  Everything that does not depend on the
+// predecessor's output (weight streaming) is issued before pdl_wait(); without the
+// attribute both instructions are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---- streaming 128-bit load: read-only path, no L1 allocation ---------------
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// (a & b) | c in one LOP3
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// ---- warp-level tensor-core step, fp32 accumulate ---------------------------
+// D[16x8] += A[16x16] * B[16x8]; used by the streaming kernels only to get exact
+// products with fp32 accumulation out of integer-valued 16-bit operands.
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1);
+
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                        uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---- 4-bit code -> 16-bit float without a conversion instruction ------------
+// OR-ing a code into the mantissa of a power of two gives an exact integer-valued
+// float.  A 32-bit word holds codes c0..c7 (c_i at bits 4i..4i+3); the four results
+// are the pairs (c0,c4) (c1,c5) (c2,c6) (c3,c7).
+//
+// fp16 (10 mantissa bits, magic 1024.0 = 0x6400): a code at bits 0..3 reads
+// 1024 + c, a code at bits 4..7 reads 1024 + 16c.  Pairs 0 and 2 are of the first
+// kind, pairs 1 and 3 of the second; the other operand of those products is stored
+// pre-divided by 16, so every product is (offset + value * c) with one shift per word.
+//
+// bf16 (7 mantissa bits, magic 128.0 = 0x4300): only bits 0..3 fit, so each pair
+// gets its own shift and reads 128 + c.
+template <typename T>
+struct Nibbles;
+
+template <>
+struct Nibbles<__half> {
+  static constexpr float kOffsetLo = 1024.f;   // pairs 0, 2
+  static constexpr float kOffsetHi = 1024.f;   // pairs 1, 3 (operand pre-divided by 16 -> 64 per unit)
+  static constexpr float kHiPrescale = 1.f / 16.f;
+  __device__ static __forceinline__ void unpack(uint32_t w, uint32_t (&p)[4]) {
+    const uint32_t t = w >> 8;
+    p[0] = and_or(w, 0x000f000fu, 0x64006400u);
+    p[1] = and_or(w, 0x00f000f0u, 0x64006400u);
+    p[2] = and_or(t, 0x000f000fu, 0x64006400u);
+    p[3] = and_or(t, 0x00f000f0u, 0x64006400u);
+  }
+};
+
+template <>
+struct Nibbles<__nv_bfloat16> {
+  static constexpr float kOffsetLo = 128.f;
+  static constexpr float kOffsetHi = 128.f;
+  static constexpr float kHiPrescale = 1.f;
+  __device__ static __forceinline__ void unpack(uint32_t w, uint32_t (&p)[4]) {
+    p[0] = and_or(w, 0x000f000fu, 0x43004300u);
+    p[1] = and_or(w >> 4, 0x000f000fu, 0x43004300u);
+    p[2] = and_or(w >> 8, 0x000f000fu, 0x43004300u);
+    p[3] = and_or(w >> 12, 0x000f000fu, 0x43004300u);
+  }
+};
+
+// ---- scalar conversions -----------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+}  // namespace pare

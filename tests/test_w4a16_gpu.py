@@ -1,0 +1,221 @@
+"""W4A16 CUDA kernels vs the CPU oracle and the committed reference outputs (GPU).
+
+Tolerances (stated once, used by every comparison here):
+  * fp16 activations / outputs: against the fp32 oracle, relative error
+    ``|y - ref| / max(|ref|, 1e-2 * max|ref|)`` has max <= 1e-2 and mean <= 1e-3;
+  * bf16 outputs carry 8 significant bits, so rounding alone costs up to 2^-8 = 3.9e-3:
+    max <= 1e-2 and mean <= 2.5e-3 against the fp32 oracle, and mean <= 1e-3 against the
+    oracle rounded to bf16 (the dtype the reference's eager path returns);
+  * the reference's own absolute gate (tests/test_triton_kernel.py:127-143): max abs err < 0.05.
+"""
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import w4a16 as ow
+from pare_b200.config import QuantConfig
+from pare_b200.core.pack import repack_int4_for_kernel
+from pare_b200.kernels import matmul_w4a16, w4a16_forward
+from pare_b200.kernels.matmul_int4 import pack_meta_h2
+from pare_b200.layers.linear import QuantizedLinear
+
+pytestmark = pytest.mark.gpu
+
+MAX_REL, MEAN_REL = 1e-2, 1e-3
+
+
+def make_ql(out=256, in_=256, seed=0, bias=False, granularity="per_group", group_size=128):
+    torch.manual_seed(seed)
+    lin = nn.Linear(in_, out, bias=bias)
+    cfg = QuantConfig(bits=4, scheme="rtn", granularity=granularity, group_size=group_size)
+    return QuantizedLinear.from_linear(lin, cfg)
+
+
+def oracle_y(ql, x, **kw):
+    n = ql.out_features
+    return ow.linear(
+        x.float().cpu().numpy(), ql.packed_weight.cpu().numpy(),
+        ql.scale.cpu().numpy().reshape(n, -1), ql.zero.cpu().numpy().reshape(n, -1),
+        bias=None if ql.bias is None else ql.bias.detach().float().cpu().numpy(), **kw)
+
+
+def check(y, ref, dtype):
+    y = y.float().cpu().numpy()
+    mx, mean = ow.rel_err(y, ref)
+    if dtype == torch.bfloat16:
+        assert mx <= MAX_REL and mean <= 2.5e-3, (mx, mean)
+        ref16 = torch.from_numpy(ref).to(torch.bfloat16).float().numpy()
+        assert ow.rel_err(y, ref16)[1] <= MEAN_REL
+    else:
+        assert mx <= MAX_REL and mean <= MEAN_REL, (mx, mean)
+
+
+def test_golden_reference_outputs(golden, cuda_lib):
+    """Kernel vs what the reference itself produced (fixture), M = 1..64."""
+    g = golden("w4a16_g128.npz")
+    packed = torch.from_numpy(g["packed"]).cuda()
+    scale = torch.from_numpy(g["scale"]).cuda().squeeze(-1).contiguous()
+    zero = torch.from_numpy(g["zero"]).cuda().squeeze(-1).contiguous()
+    for m in (1, 4, 16, 64):
+        x = torch.from_numpy(g["x"][:m]).cuda()
+        y = w4a16_forward(x, packed, scale, zero, 128)
+        assert y.dtype == torch.float16 and y.shape == (m, 256)
+        assert (y.float().cpu().numpy() - g["y"][:m]).__abs__().max() < 0.05
+        check(y, g["y"][:m], torch.float16)
+
+
+def test_golden_per_channel_bias(golden, cuda_lib):
+    g = golden("w4a16_channel.npz")
+    packed = torch.from_numpy(g["packed"]).cuda()
+    scale = torch.from_numpy(g["scale"]).cuda().reshape(128, 1).contiguous()
+    zero = torch.from_numpy(g["zero"]).cuda().reshape(128, 1).contiguous()
+    bias = torch.from_numpy(g["bias"]).cuda().half()
+    x = torch.from_numpy(g["x"]).cuda()
+    y = w4a16_forward(x, packed, scale, zero, 256, bias=bias)
+    ref = g["y"] - g["bias"] + bias.float().cpu().numpy()     # bias as the kernel sees it (fp16)
+    check(y, ref, torch.float16)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 7, 8, 9, 16, 17, 31, 33])
+def test_matches_oracle_small(m, dtype, cuda_lib):
+    ql = make_ql(256, 256, seed=0).cuda()
+    torch.manual_seed(1)
+    x = torch.randn(m, 256, device="cuda", dtype=dtype)
+    y = w4a16_forward(x, ql.packed_weight, ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous(), 128)
+    check(y, oracle_y(ql, x), dtype)
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336), (1000, 512), (48, 128)])
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_matches_oracle_layer_shapes(shape, m, cuda_lib):
+    """8B-shaped projections (out, in) plus ragged N; exercises split-K and the row-tile edge."""
+    n, k = shape
+    ql = make_ql(n, k, seed=n + k).cuda()
+    torch.manual_seed(m)
+    x = torch.randn(m, k, device="cuda", dtype=torch.float16)
+    s2, z2 = ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous()
+    y = w4a16_forward(x, ql.packed_weight, s2, z2, 128)
+    check(y, oracle_y(ql, x), torch.float16)
+    y2 = w4a16_forward(x, ql.packed_weight, s2, z2, 128)
+    assert torch.equal(y, y2)                                  # deterministic split-K reduction
+
+
+def test_fp16_metadata_option(cuda_lib):
+    ql = make_ql(1024, 1024, seed=5).cuda()
+    x = torch.randn(4, 1024, device="cuda", dtype=torch.float16)
+    s2, z2 = ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous()
+    y = w4a16_forward(x, ql.packed_weight, None, None, 128, meta_h2=pack_meta_h2(s2, z2))
+    check(y, oracle_y(ql, x), torch.float16)
+
+
+def test_generic_shapes_small_groups(cuda_lib):
+    """Group sizes / K that are not multiples of 128 take the any-shape kernel."""
+    for n, k, g in ((64, 128, 32), (40, 192, 64), (16, 64, 64)):
+        ql = make_ql(n, k, seed=k, group_size=g).cuda()
+        x = torch.randn(5, k, device="cuda", dtype=torch.float16)
+        y = w4a16_forward(x, ql.packed_weight, ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous(), g)
+        check(y, oracle_y(ql, x), torch.float16)
+
+
+def test_zero_input_gives_zero_output(cuda_lib):
+    ql = make_ql(128, 256).cuda()
+    x = torch.zeros(8, 256, device="cuda", dtype=torch.float16)
+    y = w4a16_forward(x, ql.packed_weight, ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous(), 128)
+    assert y.abs().max().item() == 0.0
+
+
+def test_strided_rows_and_out(cuda_lib):
+    ql = make_ql(512, 512, seed=9).cuda()
+    big = torch.randn(6, 1024, device="cuda", dtype=torch.float16)
+    x = big[:, :512]                                           # row stride 1024
+    y = w4a16_forward(x, ql.packed_weight, ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous(), 128)
+    check(y, oracle_y(ql, x), torch.float16)
+
+
+def test_act_order_g_idx(cuda_lib):
+    """Random column->group map (GPTQ act-order): kernel gathers x by the sorted-column permutation."""
+    torch.manual_seed(11)
+    n, k, g = 512, 1024, 128
+    w = torch.randn(n, k) * 0.02
+    perm = torch.randperm(k, generator=torch.Generator().manual_seed(3))
+    g_idx = torch.empty(k, dtype=torch.int32)
+    g_idx[perm] = (torch.arange(k) // g).to(torch.int32)
+    # scales per g_idx group: quantize the group-sorted matrix with RTN, then scatter codes back
+    order = torch.argsort(g_idx.long(), stable=True)
+    lin = nn.Linear(k, n, bias=False)
+    lin.weight.data = w[:, order]
+    qs = QuantizedLinear.from_linear(lin, QuantConfig(bits=4, scheme="rtn", group_size=g))
+    from pare_b200.core.pack import unpack_int4
+    codes = torch.empty(n, k, dtype=torch.int32)
+    codes[:, order] = unpack_int4(qs.packed_weight)
+    ql = QuantizedLinear(codes, qs.scale, qs.zero, qs.config, None, k, n, g_idx=g_idx).cuda()
+    ql.use_kernel = True
+    x = torch.randn(4, k, device="cuda", dtype=torch.float16)
+    y = ql(x)
+    ref = ow.linear(x.float().cpu().numpy(), ql.packed_weight.cpu().numpy(), ql.scale.cpu().numpy().reshape(n, -1),
+                    ql.zero.cpu().numpy().reshape(n, -1), g_idx=g_idx.numpy())
+    check(y, ref, torch.float16)
+    ql.use_kernel = False
+    check(ql(x), ref, torch.float16)                           # eager branch agrees too
+
+
+def test_runtime_input_scale(cuda_lib):
+    ql = make_ql(256, 512, seed=13)
+    s = torch.exp(torch.randn(512) * 0.3)
+    ql.input_scale = s
+    ql = ql.cuda()
+    ql.use_kernel = True
+    x = torch.randn(3, 512, device="cuda", dtype=torch.bfloat16)
+    y = ql(x)
+    ref = oracle_y(ql, x, input_scale=s.numpy(),
+                   round_input=lambda a: torch.from_numpy(a).to(torch.bfloat16).float().numpy())
+    check(y, ref, torch.bfloat16)
+
+
+# ---- the reference's own integration tests, run against this package -------------------
+
+def test_reference_signature_kernel_layout(cuda_lib):
+    """matmul_w4a16 accepts kernel-layout weights like the reference (tests/test_triton_kernel.py:127-143)."""
+    torch.manual_seed(1)
+    ql = make_ql(256, 256).cuda()
+    w_kernel = repack_int4_for_kernel(ql.packed_weight, 128)
+    for m in (1, 4, 16, 64):
+        x = torch.randn(m, 256, device="cuda", dtype=torch.float16)
+        with torch.no_grad():
+            y_ref = ql.forward(x).float()
+            y_k = matmul_w4a16(x, w_kernel, ql.scale, ql.zero, 128).float()
+        assert y_k.shape == (m, 256)
+        assert (y_ref - y_k).abs().max().item() < 0.05
+
+
+def test_use_kernel_dispatch_lazy_buffers_3d_and_cpu(cuda_lib):
+    ql = make_ql(128, 256)
+    ql.use_kernel = True
+    y_cpu = ql(torch.randn(4, 256))                            # CPU input takes the eager branch
+    assert y_cpu.shape == (4, 128)
+    ql = ql.cuda()
+    x = torch.randn(2, 64, 256, device="cuda", dtype=torch.float16)
+    assert not hasattr(ql, "_packed_weight_kernel")
+    with torch.no_grad():
+        y = ql(x)
+    assert y.shape == (2, 64, 128) and not y.isnan().any()
+    first = id(ql._packed_weight_kernel)
+    ql(x)
+    assert id(ql._packed_weight_kernel) == first
+    assert "_packed_weight_kernel" not in ql.state_dict()
+    ql.use_kernel = False
+    assert (ql(x).float() - y.float()).abs().max().item() < 0.05
+
+
+def test_error_conditions(cuda_lib):
+    ql = make_ql(128, 256).cuda()
+    w = repack_int4_for_kernel(ql.packed_weight, 128)
+    with pytest.raises(RuntimeError):
+        matmul_w4a16(torch.randn(2, 256, dtype=torch.float16), w, ql.scale, ql.zero, 128)      # CPU tensor
+    with pytest.raises(AssertionError):
+        matmul_w4a16(torch.randn(2, 256, device="cuda"), w, ql.scale, ql.zero, 128)            # fp32
+    with pytest.raises(AssertionError):
+        matmul_w4a16(torch.randn(2, 128, device="cuda", dtype=torch.float16), w, ql.scale, ql.zero, 128)
