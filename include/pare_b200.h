@@ -86,8 +86,81 @@ int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx,
                        void* stream);
 
 /* Tuning override for experiments (host state, process-wide, not thread-safe):
- * row blocks of 16 per warp, K splits, prefetch depth; 0 = choose automatically. */
-void pare_w4a16_set_tuning(int row_blocks, int k_splits, int prefetch);
+ * (reserved), K splits, ring depth in 512-column stages; 0 = choose automatically. */
+void pare_w4a16_set_tuning(int reserved, int k_splits, int ring_depth);
+
+
+/* ------------------------------------------------------------------------
+ * KIVI quantized KV cache.  Replaces the eager primitives and the cache
+ * bookkeeping of pare/kv_cache.py: _quantize_keys :75-104, _quantize_values
+ * :122-151, _dequantize_keys/_dequantize_values :107-119,154-156,
+ * QuantizedKVCache._append_compressed/_reconstruct :294-325.
+ *
+ * Storage of ONE layer, owned and preallocated by the caller for `cap` tokens
+ * (cap % 128 == 0); the reference grows six tensors with torch.cat instead:
+ *   k_codes [B][H][cap][D*bits/8]           uint8, packed along channels (channel c of a
+ *                                           token at bit c*bits of its row, little endian)
+ *   k_scale, k_zero [B][H][cap/group][D]    fp32, per (token group, channel); zero = group min
+ *   v_codes [B][H][cap/128][D][128*bits/8]  uint8, packed along tokens inside 128-token blocks
+ *                                           (token t of the block at bit t*bits of row d)
+ *   v_scale, v_zero [B][H][cap]             fp32, per token (min/max over all D channels)
+ * bits in {2,4,8}; group in {16,32,64,128}; D % 32 == 0, D <= 256.
+ * Codes, scales and zeros are bit-identical to the reference's (same fp32 operation order).
+ */
+
+/* Quantize n_tokens (a multiple of group) tokens of k_src / v_src [B][H][n_tokens][D]
+ * (src_dtype F16/BF16/F32, element strides stride_b/h/t, channels contiguous) and store
+ * them as compressed tokens t0 .. t0+n_tokens-1 (t0 % group == 0).  pare/kv_cache.py:236-242. */
+int pare_kivi_append(const void* k_src, const void* v_src, int src_dtype,
+                     int64_t stride_b, int64_t stride_h, int64_t stride_t,
+                     int n_tokens, int t0,
+                     uint8_t* k_codes, float* k_scale, float* k_zero,
+                     uint8_t* v_codes, float* v_scale, float* v_zero,
+                     int B, int H, int D, int bits, int group, int cap, void* stream);
+
+/* Dense reconstruction code*scale+zero of compressed tokens 0..n_comp-1 into
+ * out_k / out_v [B][H][>=n_comp][D] (out_dtype F16/BF16/F32, element strides given).
+ * pare/kv_cache.py:315-325 (the part of update()'s return value that comes from the
+ * compressed store). */
+int pare_kivi_dequant(const uint8_t* k_codes, const float* k_scale, const float* k_zero,
+                      const uint8_t* v_codes, const float* v_scale, const float* v_zero,
+                      int B, int H, int D, int bits, int group, int cap, int n_comp,
+                      void* out_k, void* out_v, int out_dtype,
+                      int64_t stride_b, int64_t stride_h, int64_t stride_t, void* stream);
+
+/* Fused dequantize + decode attention for ONE query token per sequence:
+ *   out[b][hq][:] = softmax(q[b][hq] . K^T * softmax_scale) . V   over n_comp compressed
+ * tokens followed by n_res full-precision residual tokens, grouped-query sharing
+ * (query head hq reads KV head hq / (Hq/H), Hq/H <= 8).  The reference has no such
+ * function: a caller runs scaled_dot_product_attention on update()'s dense return
+ * (pare/kv_cache.py:183-186); this call gives the same result without materialising it.
+ *   q, out        [B][Hq][D] dtype F16/BF16, element strides *_stride_b / *_stride_h
+ *   res_k, res_v  [B][H][n_res][D] same dtype, element strides res_stride_b/h/t (multiples of 8)
+ * D == 128, bits == 4 or 2.  workspace: pare_kivi_attn_workspace_bytes(), zero-filled once
+ * (same contract as the W4A16 workspace; one buffer may serve both). */
+size_t pare_kivi_attn_workspace_bytes(int B, int H, int n_comp, int n_res);
+
+int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t q_stride_h,
+                          const uint8_t* k_codes, const float* k_scale, const float* k_zero,
+                          const uint8_t* v_codes, const float* v_scale, const float* v_zero,
+                          int n_comp,
+                          const void* res_k, const void* res_v,
+                          int64_t res_stride_b, int64_t res_stride_h, int64_t res_stride_t, int n_res,
+                          void* out, int64_t out_stride_b, int64_t out_stride_h,
+                          float softmax_scale,
+                          int B, int Hq, int H, int D, int bits, int group, int cap,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* Tuning override for experiments: compressed tokens per CTA (multiple of 128, <= 1024); 0 = auto. */
+void pare_kivi_attn_set_tuning(int chunk);
+
+/* ------------------------------------------------------------------------
+ * Decode-step glue (no counterpart in the reference library: model code around the two hot
+ * kernels).  y = rmsnorm(x + delta) * weight, optionally storing x + delta; and the SwiGLU
+ * gate out = silu(gate) * up over a fused [rows][2n] gate|up projection.  dtype F16/BF16. */
+int pare_rmsnorm_residual(const void* x, const void* delta, const void* weight, void* resid_out, void* y,
+                          int rows, int n, float eps, int dtype, void* stream);
+int pare_silu_mul(const void* gate_up, void* out, int rows, int n, int64_t ld, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -98,6 +98,29 @@ struct Nibbles<__half> {
   }
 };
 
+// Exact variant for the attention kernel: the mantissa offset is removed before the product (one
+// half2 op per pair), so the accumulator never carries the 1024-per-element offset and nothing
+// large has to cancel (logits are exponentiated, so their absolute error matters).  Every
+// output is code - CENTER for all four pairs; CENTER = 8 maps the codes to -8..7, which halves
+// the magnitude of the products and with it the effect of rounding the other operand to fp16.
+template <int CENTER>
+__device__ __forceinline__ void unpack_codes_exact(uint32_t w, uint32_t (&p)[4]) {
+  const uint32_t t = w >> 8;
+  const __half2 off_lo = __float2half2_rn(1024.f + CENTER);        // exact in fp16
+  const __half2 sixteenth = __float2half2_rn(0.0625f);
+  const __half2 off_hi = __float2half2_rn(-(64.f + CENTER));
+  uint32_t r0 = and_or(w, 0x000f000fu, 0x64006400u), r1 = and_or(w, 0x00f000f0u, 0x64006400u);
+  uint32_t r2 = and_or(t, 0x000f000fu, 0x64006400u), r3 = and_or(t, 0x00f000f0u, 0x64006400u);
+  __half2 h0 = __hsub2(*reinterpret_cast<__half2*>(&r0), off_lo);
+  __half2 h1 = __hfma2(*reinterpret_cast<__half2*>(&r1), sixteenth, off_hi);
+  __half2 h2 = __hsub2(*reinterpret_cast<__half2*>(&r2), off_lo);
+  __half2 h3 = __hfma2(*reinterpret_cast<__half2*>(&r3), sixteenth, off_hi);
+  p[0] = *reinterpret_cast<uint32_t*>(&h0);
+  p[1] = *reinterpret_cast<uint32_t*>(&h1);
+  p[2] = *reinterpret_cast<uint32_t*>(&h2);
+  p[3] = *reinterpret_cast<uint32_t*>(&h3);
+}
+
 template <>
 struct Nibbles<__nv_bfloat16> {
   static constexpr float kOffsetLo = 128.f;

@@ -194,12 +194,14 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_kernel(const __grid_const
     const T* xg = reinterpret_cast<const T*>(p.x);
     const int c = lane >> 1, hsel = lane & 1;
     const int chunk_off = (c & 3) * 64 + (c >> 2) * 16;  // [word][quad] order inside a step
-    for (int pair = warp; pair < nseg * MP; pair += kConsumerWarps + 1) {
-      const int seg = pair / MP, m = pair - seg * MP;
+    // only rows m < M are staged; table entries of the unused MMA columns are never read back
+    for (int pr = warp; pr < nseg * p.M; pr += kConsumerWarps + 1) {
+      const int seg = pr / p.M, m = pr - seg * p.M;
+      const int pair = seg * MP + m;
       const int sb = max(0, (g_first + seg) * spg - st0);
       const int se = min(nst, (g_first + seg + 1) * spg - st0);
       float lo = 0.f, hi = 0.f;
-      if (m < p.M) {
+      {
         for (int st = sb; st < se; ++st) {
           const int k = k0 + st * 128 + lane * 4;
           float v[4];

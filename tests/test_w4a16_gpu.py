@@ -108,7 +108,13 @@ def test_fp16_metadata_option(cuda_lib):
     x = torch.randn(4, 1024, device="cuda", dtype=torch.float16)
     s2, z2 = ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous()
     y = w4a16_forward(x, ql.packed_weight, None, None, 128, meta_h2=pack_meta_h2(s2, z2))
-    check(y, oracle_y(ql, x), torch.float16)
+    # scales rounded to fp16 (11 significant bits): exact against the oracle fed the same rounded scales,
+    # and within a widened bound (max 5e-2) against the fp32-scale oracle
+    ref16 = ow.linear(x.float().cpu().numpy(), ql.packed_weight.cpu().numpy(),
+                      s2.half().float().cpu().numpy(), z2.cpu().numpy())
+    check(y, ref16, torch.float16)
+    mx, mean = ow.rel_err(y.float().cpu().numpy(), oracle_y(ql, x))
+    assert mx <= 5e-2 and mean <= MEAN_REL, (mx, mean)
 
 
 def test_generic_shapes_small_groups(cuda_lib):
@@ -158,8 +164,9 @@ def test_act_order_g_idx(cuda_lib):
     ref = ow.linear(x.float().cpu().numpy(), ql.packed_weight.cpu().numpy(), ql.scale.cpu().numpy().reshape(n, -1),
                     ql.zero.cpu().numpy().reshape(n, -1), g_idx=g_idx.numpy())
     check(y, ref, torch.float16)
-    ql.use_kernel = False
-    check(ql(x), ref, torch.float16)                           # eager branch agrees too
+    ql.use_kernel = False                                      # eager branch (fp16 weights, fp16 GEMM) agrees too,
+    mx, mean = ow.rel_err(ql(x).float().cpu().numpy(), ref)    # within its own, looser, rounding
+    assert mx <= 5e-2 and mean <= 2e-3, (mx, mean)
 
 
 def test_runtime_input_scale(cuda_lib):
