@@ -33,7 +33,9 @@ __global__ void rmsnorm_residual_kernel(const T* x, const T* delta, const T* wei
   __syncthreads();
   const float inv = red[0];
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = to_float<T>(from_float<T>(to_float<T>(xr[i]) + (dr ? to_float<T>(dr[i]) : 0.f)));
+    // resid_out may alias x: once it is written, read the sum back instead of adding delta twice
+    const float v = resid_out ? to_float<T>(resid_out[(size_t)row * n + i])
+                              : to_float<T>(from_float<T>(to_float<T>(xr[i]) + (dr ? to_float<T>(dr[i]) : 0.f)));
     y[(size_t)row * n + i] = from_float<T>(v * inv * to_float<T>(weight[i]));
   }
 }

@@ -1,0 +1,148 @@
+"""A decode stack made only of the hot path: W4A16 linears + KIVI attention, chained per layer.
+
+This is the measurement vehicle for "decode tok/s": every transformer block is
+``rmsnorm -> fused q|k|v linear -> KIVI append + fused decode attention -> o linear ->
+rmsnorm(+residual) -> fused gate|up linear -> SwiGLU -> down linear``, with random-init INT4
+weights of the requested shape.  The linears are ordinary :class:`QuantizedLinear` modules
+(``use_kernel=True``) and the cache an ordinary :class:`QuantizedKVCache`, i.e. the public API
+a user of the reference would call; rotary embeddings, the token embedding and the LM head are
+left out (they are not part of the path this package replaces).
+
+Tensor parallelism (one process per GPU): q|k|v and gate|up are split by output rows (whole
+heads / FFN columns per rank), o and down by input columns, the KV cache by KV head; the two
+row-parallel outputs of a block are summed with one NCCL all-reduce each.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+from torch import Tensor
+
+from pare_b200.config import QuantConfig
+from pare_b200.kernels import _lib
+from pare_b200.kv_cache import KVCacheConfig, QuantizedKVCache
+from pare_b200.layers.linear import QuantizedLinear
+
+SHAPES = {
+    # hidden, ffn, q heads, kv heads, head_dim, layers
+    "llama-3.1-8b": (4096, 14336, 32, 8, 128, 32),
+    "llama-3-70b": (8192, 28672, 64, 8, 128, 80),
+    "qwen2.5-7b": (3584, 18944, 28, 4, 128, 28),
+}
+
+
+def synthetic_linear(out_features: int, in_features: int, *, seed: int, device, group_size: int = 128,
+                     awq_fold: bool = True) -> QuantizedLinear:
+    """Random-init INT4 g128 layer built directly in packed form on ``device``.
+
+    Codes are uniform in 0..15 with zero-point 8; scales are chosen so that the dequantized
+    weights have standard deviation 0.02, multiplied per input-channel group by a
+    LogNormal(0, 0.3) factor when ``awq_fold`` (what an AWQ-quantized layer stores: the input
+    scale is folded into the weights offline, the layer at run time is a plain asymmetric one).
+    """
+    g = torch.Generator(device=device).manual_seed(seed)
+    packed = torch.randint(0, 256, (out_features, in_features // 2), dtype=torch.uint8, device=device, generator=g)
+    ng = in_features // group_size
+    scale = torch.full((out_features, ng, 1), 0.02 / 4.61, device=device)
+    scale = scale * (0.75 + 0.5 * torch.rand(out_features, ng, 1, device=device, generator=g))
+    if awq_fold:
+        scale = scale * torch.exp(0.3 * torch.randn(1, ng, 1, device=device, generator=g))
+    zero = torch.randint(6, 11, (out_features, ng, 1), device=device, generator=g).float()
+    cfg = QuantConfig(bits=4, scheme="awq", granularity="per_group", group_size=group_size)
+    layer = QuantizedLinear.from_tensors(packed, None, scale, zero, cfg, None, in_features, out_features)
+    layer.use_kernel = True
+    return layer
+
+
+class DecodeBlock(nn.Module):
+    def __init__(self, hidden: int, ffn: int, hq: int, hkv: int, d: int, *, seed: int, device, dtype,
+                 tp_world: int = 1) -> None:
+        super().__init__()
+        assert hq % tp_world == 0 and hkv % tp_world == 0 and ffn % (tp_world * 128) == 0
+        self.hq, self.hkv, self.d, self.ffn = hq // tp_world, hkv // tp_world, d, ffn // tp_world
+        self.hidden = hidden
+        self.qkv = synthetic_linear((self.hq + 2 * self.hkv) * d, hidden, seed=seed * 7 + 0, device=device)
+        self.o = synthetic_linear(hidden, self.hq * d, seed=seed * 7 + 3, device=device)
+        self.gate_up = synthetic_linear(2 * self.ffn, hidden, seed=seed * 7 + 4, device=device)
+        self.down = synthetic_linear(hidden, self.ffn, seed=seed * 7 + 6, device=device)
+        self.register_buffer("norm1", torch.ones(hidden, device=device, dtype=dtype))
+        self.register_buffer("norm2", torch.ones(hidden, device=device, dtype=dtype))
+
+
+class DecodeStack(nn.Module):
+    """``n_layers`` decode blocks over one shared :class:`QuantizedKVCache`."""
+
+    def __init__(self, shape: str | tuple, *, device="cuda", dtype=torch.bfloat16, n_layers: int | None = None,
+                 kv_config: KVCacheConfig | None = None, max_seq_len: int = 8192, tp_world: int = 1,
+                 process_group=None, seed: int = 0) -> None:
+        super().__init__()
+        hidden, ffn, hq, hkv, d, layers = SHAPES[shape] if isinstance(shape, str) else shape
+        self.hidden, self.d = hidden, d
+        self.n_layers = n_layers or layers
+        self.dtype, self.device = dtype, torch.device(device)
+        self.tp_world, self.group = tp_world, process_group
+        self.blocks = nn.ModuleList(
+            DecodeBlock(hidden, ffn, hq, hkv, d, seed=seed + i, device=self.device, dtype=dtype, tp_world=tp_world)
+            for i in range(self.n_layers))
+        self.cache = QuantizedKVCache(self.n_layers, kv_config or KVCacheConfig(), max_seq_len=max_seq_len)
+        self._code = _lib.dtype_code(dtype)
+
+    # ---- glue kernels ------------------------------------------------------------------
+    def _rmsnorm(self, x: Tensor, delta: Tensor | None, weight: Tensor, store_residual: bool) -> Tensor:
+        y = torch.empty_like(x)
+        status = _lib.lib().pare_rmsnorm_residual(
+            x.data_ptr(), _lib.ptr(delta), weight.data_ptr(), x.data_ptr() if store_residual else None, y.data_ptr(),
+            x.shape[0], x.shape[1], 1e-5, self._code, _lib.current_stream(x.device))
+        _lib.check(status, "pare_rmsnorm_residual")
+        return y
+
+    def _silu_mul(self, gate_up: Tensor, n: int) -> Tensor:
+        out = torch.empty(gate_up.shape[0], n, device=gate_up.device, dtype=gate_up.dtype)
+        status = _lib.lib().pare_silu_mul(gate_up.data_ptr(), out.data_ptr(), gate_up.shape[0], n, gate_up.stride(0),
+                                          self._code, _lib.current_stream(gate_up.device))
+        _lib.check(status, "pare_silu_mul")
+        return out
+
+    def _all_reduce(self, t: Tensor) -> Tensor:
+        if self.tp_world > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+        return t
+
+    # ---- cache set-up -----------------------------------------------------------------
+    @torch.no_grad()
+    def prefill_cache(self, batch: int, context: int, seed: int = 1) -> None:
+        """Fill every layer's cache with ``context`` synthetic tokens: N(0,1) with 1 % of the channels
+        (same channels for all tokens) scaled by 10, the stand-in for real K/V statistics."""
+        g = torch.Generator(device=self.device).manual_seed(seed)
+        blk = self.blocks[0]
+        for layer in range(self.n_layers):
+            k = torch.randn(batch, blk.hkv, context, self.d, device=self.device, generator=g)
+            v = torch.randn(batch, blk.hkv, context, self.d, device=self.device, generator=g)
+            out_ch = torch.randperm(self.d, device=self.device, generator=g)[: max(1, self.d // 100)]
+            k[..., out_ch] *= 10.0
+            self.cache.reset(layer)
+            self.cache._append(layer, k.to(self.dtype), v.to(self.dtype))
+
+    # ---- one decode step ---------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, x: Tensor) -> Tensor:
+        """``x [M, hidden]``: hidden state of the newest token of each of M sequences → same shape."""
+        m = x.shape[0]
+        resid = x.clone()
+        delta = None
+        for i, blk in enumerate(self.blocks):
+            h = self._rmsnorm(resid, delta, blk.norm1, store_residual=delta is not None)
+            qkv = blk.qkv(h)
+            d, hq, hkv = blk.d, blk.hq, blk.hkv
+            q = qkv[:, : hq * d].unflatten(1, (hq, d))
+            k = qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, 1, d))
+            v = qkv[:, (hq + hkv) * d:].unflatten(1, (hkv, 1, d))
+            attn = self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d))
+            o = self._all_reduce(blk.o(attn.reshape(m, hq * d)))
+            h2 = self._rmsnorm(resid, o, blk.norm2, store_residual=True)
+            act = self._silu_mul(blk.gate_up(h2), blk.ffn)
+            delta = self._all_reduce(blk.down(act))
+        return resid + delta
