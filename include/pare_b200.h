@@ -86,8 +86,8 @@ int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx,
                        void* stream);
 
 /* Tuning override for experiments (host state, process-wide, not thread-safe):
- * (reserved), K splits, ring depth in 512-column stages; 0 = choose automatically. */
-void pare_w4a16_set_tuning(int reserved, int k_splits, int ring_depth);
+ * (reserved), columns per CTA (multiple of 512), warps per CTA (4 or 8); 0 = choose automatically. */
+void pare_w4a16_set_tuning(int reserved, int columns_per_cta, int warps_per_cta);
 
 
 /* ------------------------------------------------------------------------

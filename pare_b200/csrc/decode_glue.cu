@@ -8,35 +8,69 @@
 namespace pare {
 namespace {
 
+// Each thread keeps its elements in registers (8 per 16-byte vector, up to kVecs vectors), so the
+// row is read once and all loads are in flight together; n must be a multiple of 8.
+constexpr int kNormThreads = 256;
+constexpr int kVecs = 8;  // rows up to 256 * 8 * 8 = 16384 elements
+
 template <typename T>
-__global__ void rmsnorm_residual_kernel(const T* x, const T* delta, const T* weight, T* resid_out, T* y, int n, float eps) {
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_residual_kernel(const T* __restrict__ x, const T* __restrict__ delta,
+                                                                        const T* __restrict__ weight, T* resid_out,
+                                                                        T* __restrict__ y, int n, float eps) {
   pdl_wait();
-  const int row = blockIdx.x;
-  const T* xr = x + (size_t)row * n;
-  const T* dr = delta ? delta + (size_t)row * n : nullptr;
+  const size_t row = (size_t)blockIdx.x * n;
+  const int nvec = n >> 3;
+  uint4 xv[kVecs], dv[kVecs];
+#pragma unroll
+  for (int j = 0; j < kVecs; ++j) {
+    const int v = threadIdx.x + j * kNormThreads;
+    if (v < nvec) {
+      xv[j] = *reinterpret_cast<const uint4*>(x + row + v * 8);
+      if (delta) dv[j] = *reinterpret_cast<const uint4*>(delta + row + v * 8);
+    }
+  }
   float ss = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = to_float<T>(xr[i]) + (dr ? to_float<T>(dr[i]) : 0.f);
-    const float r = to_float<T>(from_float<T>(v));  // the residual stream is kept in T
-    if (resid_out) resid_out[(size_t)row * n + i] = from_float<T>(v);
-    ss += r * r;
+#pragma unroll
+  for (int j = 0; j < kVecs; ++j) {
+    const int v = threadIdx.x + j * kNormThreads;
+    if (v < nvec) {
+      T* xe = reinterpret_cast<T*>(&xv[j]);
+      const T* de = reinterpret_cast<const T*>(&dv[j]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float f = to_float<T>(xe[e]);
+        if (delta) f += to_float<T>(de[e]);
+        xe[e] = from_float<T>(f);            // the residual stream is kept in T
+        const float r = to_float<T>(xe[e]);
+        ss += r * r;
+      }
+      if (resid_out) *reinterpret_cast<uint4*>(resid_out + row + v * 8) = xv[j];
+    }
   }
   __shared__ float red[32];
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
   __syncthreads();
   if (threadIdx.x < 32) {
-    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    float v = threadIdx.x < (kNormThreads >> 5) ? red[threadIdx.x] : 0.f;
     v = warp_sum(v);
     if (threadIdx.x == 0) red[0] = rsqrtf(v / n + eps);
   }
   __syncthreads();
   const float inv = red[0];
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    // resid_out may alias x: once it is written, read the sum back instead of adding delta twice
-    const float v = resid_out ? to_float<T>(resid_out[(size_t)row * n + i])
-                              : to_float<T>(from_float<T>(to_float<T>(xr[i]) + (dr ? to_float<T>(dr[i]) : 0.f)));
-    y[(size_t)row * n + i] = from_float<T>(v * inv * to_float<T>(weight[i]));
+#pragma unroll
+  for (int j = 0; j < kVecs; ++j) {
+    const int v = threadIdx.x + j * kNormThreads;
+    if (v < nvec) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(weight + v * 8);
+      const T* we = reinterpret_cast<const T*>(&wv);
+      const T* xe = reinterpret_cast<const T*>(&xv[j]);
+      uint4 ov;
+      T* oe = reinterpret_cast<T*>(&ov);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) oe[e] = from_float<T>(to_float<T>(xe[e]) * inv * to_float<T>(we[e]));
+      *reinterpret_cast<uint4*>(y + row + v * 8) = ov;
+    }
   }
 }
 
@@ -61,6 +95,7 @@ extern "C" {
 int pare_rmsnorm_residual(const void* x, const void* delta, const void* weight, void* resid_out, void* y, int rows,
                           int n, float eps, int dtype, void* stream) {
   PARE_REQUIRE(x && weight && y && rows > 0 && n > 0, PARE_ERR_SHAPE);
+  PARE_REQUIRE(n % 8 == 0 && n <= pare::kNormThreads * pare::kVecs * 8, PARE_ERR_UNSUPPORTED);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == PARE_F16)
     pare::rmsnorm_residual_kernel<__half><<<rows, 256, 0, s>>>((const __half*)x, (const __half*)delta, (const __half*)weight,
