@@ -8,6 +8,11 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
                  const void* bias, void* y, int64_t ldy, int M, int N, int K, int G, void* workspace,
                  size_t workspace_bytes, cudaStream_t stream);
 void gemv_set_tuning(int rb, int splits, int pf);
+bool gemm_supported(int M, int K, int G, const float* scale, const float* zero);
+size_t gemm_workspace_bytes(int M, int N, int K);
+int gemm_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale, const float* zero,
+                 const int32_t* col_perm, const float* input_scale, const void* bias, void* y, int64_t ldy, int M, int N,
+                 int K, int G, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 }  // namespace pare
 
 extern "C" {
@@ -30,7 +35,9 @@ const char* pare_status_string(int status) {
 
 size_t pare_w4a16_workspace_bytes(int M, int N, int K, int group_size) {
   if (M <= 0 || N <= 0 || K <= 0 || group_size <= 0) return 0;
-  return pare::gemv_workspace_bytes(M, N, K, group_size);
+  const size_t a = pare::gemv_workspace_bytes(M, N, K, group_size);
+  const size_t b = (M > 16 && K % 512 == 0 && group_size % 128 == 0) ? pare::gemm_workspace_bytes(M, N, K) : 0;
+  return a > b ? a : b;
 }
 
 int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale,
@@ -43,6 +50,9 @@ int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* p
   PARE_REQUIRE(x_dtype == PARE_F16 || x_dtype == PARE_BF16, PARE_ERR_DTYPE);
   PARE_REQUIRE(x && packed && y && (meta_h2 || (scale && zero)), PARE_ERR_SHAPE);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (pare::gemm_supported(M, K, group_size, scale, zero))  // M > 16: tensor-core tiles
+    return pare::gemm_forward(x, x_dtype, ldx, packed, scale, zero, col_perm, input_scale, bias, y, ldy, M, N, K,
+                              group_size, workspace, workspace_bytes, s);
   const size_t esz = 2;
   for (int m0 = 0; m0 < M; m0 += 16) {
     const int mc = (M - m0) < 16 ? (M - m0) : 16;

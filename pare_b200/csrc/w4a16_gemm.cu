@@ -1,0 +1,519 @@
+// W4A16 tensor-core path for M > 16 (prefill), sm_100a: dequantize to shared memory, tcgen05.mma
+// with the accumulator in tensor memory.
+//
+// Replaces the Triton tile kernel of the reference (pare/kernels/matmul_int4.py:54-176) where
+// tiles are worth it.  Orientation: the 128 rows of a weight tile sit on the MMA M axis (the 128
+// TMEM lanes), the activation rows on the MMA N axis, so a 64-row batch does not waste half of
+// every instruction:   Y^T[n][m] = sum_k W[n][k] * X[m][k].
+//
+// One CTA = 128 output rows x one tile of up to 128 activation rows x one K range.  Warp roles:
+//   warps 0-7  dequantize (two threads per weight row), then run the epilogue
+//   warp 8     producer: packed codes by row-contiguous bulk copies (cp.async.bulk, 256 B per row
+//              and stage) into a ring; activation tiles by TMA (cp.async.bulk.tensor.2d, 128B swizzle)
+//   warp 9     one elected thread issues tcgen05.mma (UMMA 128 x MT x 16, fp32 accumulate in TMEM)
+// Per 64-column block a dequantizing thread reads 16 bytes of codes, turns them into exact
+// integers in the 16-bit float type by the mantissa trick of common.cuh, multiplies by the group
+// scale and writes four 16-byte chunks of the K-major, 128B-swizzled operand tile that the MMA
+// reads through a shared-memory descriptor.  Weights therefore reach the tensor core as
+// dtype((q - zero) * scale), which is what the reference's own dequantize-then-matmul path feeds
+// its GEMM (pare/layers/linear.py:129).
+// All mbarrier waits are bounded; on expiry the CTA records PARE_ERR_TIMEOUT, stops waiting,
+// frees its tensor memory and returns.
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace pare {
+namespace {
+
+constexpr int kRows = 128;             // weight rows per CTA (UMMA M)
+constexpr int kBlockK = 64;            // columns per MMA stage: 128 bytes of 16-bit elements = one swizzle row
+constexpr int kRawK = 512;             // columns per raw (packed) stage
+constexpr int kRawPitch = kRawK / 2 + 16;   // bytes; +16 keeps the 16-byte reads of 8 rows in distinct banks
+constexpr int kRawStages = 2;
+constexpr int kStages = 4;             // operand ring depth
+constexpr int kDequantThreads = 256;
+constexpr int kGemmThreads = kDequantThreads + 64;
+constexpr uint32_t kSpin = 1u << 22;
+constexpr size_t kCounterInts = 16384;
+constexpr size_t kCounterBytes = kCounterInts * sizeof(int);
+constexpr size_t kStatusIndex = kCounterInts - 1;
+
+struct GemmParams {
+  const uint8_t* packed;
+  const float* scale;
+  const float* zero;
+  const void* bias;
+  void* y;
+  int64_t ldy;
+  int M, N, K, ngroups, group_size;
+  int mt;               // activation rows per tile (UMMA N): 32, 64 or 128
+  int kblocks_per_split;
+  int splits;
+  float* partial;       // [splits][M][N]
+  int* counters;
+};
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void bar_expect(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool bar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  `dead` is sticky per thread: after one expiry nothing waits any more.
+__device__ __forceinline__ void bar_wait(uint32_t bar, uint32_t parity, int* status, bool& dead) {
+  if (dead) return;
+#pragma unroll 1
+  for (uint32_t i = 0; i < kSpin; ++i)
+    if (bar_test(bar, parity)) return;
+  dead = true;
+  if (status) atomicExch(status, PARE_ERR_TIMEOUT);
+}
+__device__ __forceinline__ void bulk_row(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ uint4 ld_s128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void st_s128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
+// K-major operand tile, 128-byte rows, 128B swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- activations for the tensor-core path: inside every 8-column chunk the columns are stored in
+// the order 0,4,1,5,2,6,3,7 — the order in which one 32-bit word of codes unpacks into pairs — so the
+// dequantizing threads never have to re-pair registers.  (The contraction does not care about the
+// order of K as long as both operands agree.)  Applies the act-order gather and the input scale. ----
+template <typename T>
+__global__ void w4a16_gemm_prep_kernel(const T* x, int64_t ldx, const int32_t* col_perm, const float* input_scale, T* xq,
+                                       int M, int K) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)M * K) return;
+  const int m = (int)(idx / K), k = (int)(idx - (int64_t)m * K);
+  const int src = col_perm ? col_perm[k] : k;
+  float v = to_float<T>(x[(int64_t)m * ldx + src]);
+  if (input_scale) v = __fdiv_rn(v, input_scale[src]);
+  const int pos = k & 7, slot = ((pos & 3) << 1) | (pos >> 2);
+  xq[(int64_t)m * K + (k & ~7) + slot] = from_float<T>(v);
+}
+
+template <typename T>
+struct Pair;
+template <>
+struct Pair<__half> {
+  using V = __half2;
+  static constexpr uint32_t kFmt = 0;
+  // fp16 operand tiles hold 256 * w: the low term of the scale expansion (~2^-12 of the scale) would
+  // otherwise be a subnormal half with a few significant bits.  A power of two does not change any
+  // rounding (|w| < 256), and the epilogue multiplies the accumulator by 2^-8 exactly.
+  static constexpr float kPre = 256.f;
+  __device__ static V splat(float f) { return __float2half2_rn(f); }
+};
+template <>
+struct Pair<__nv_bfloat16> {
+  using V = __nv_bfloat162;
+  static constexpr uint32_t kFmt = 1;
+  static constexpr float kPre = 1.f;
+  __device__ static V splat(float f) { return __float2bfloat162_rn(f); }
+};
+
+// one 32-bit word of codes -> 8 dequantized 16-bit values (slot order 0,4,1,5,2,6,3,7) as one 16-byte chunk.
+// The scale comes as a two-term expansion hi + lo in the 16-bit type; fma(d, hi, d * lo) rounds the exact
+// product d * (hi + lo) once, so the result is the 16-bit rounding of (q - zero) * scale computed in fp32 —
+// the weight the reference's eager path feeds its GEMM.
+template <typename T>
+__device__ __forceinline__ uint4 dequant_word(uint32_t w, float z, typename Pair<T>::V s_hi, typename Pair<T>::V s_lo);
+
+template <>
+__device__ __forceinline__ uint4 dequant_word<__half>(uint32_t w, float z, __half2 s_hi, __half2 s_lo) {
+  uint32_t p[4];
+  Nibbles<__half>::unpack(w, p);  // 1024+c (pairs 0,2), 1024+16c (pairs 1,3)
+  const __half2 off_lo = __float2half2_rn(1024.f + z), off_hi = __float2half2_rn(-(64.f + z));
+  const __half2 sixteenth = __float2half2_rn(0.0625f);
+  __half2 d[4];
+  d[0] = __hsub2(*reinterpret_cast<__half2*>(&p[0]), off_lo);
+  d[1] = __hfma2(*reinterpret_cast<__half2*>(&p[1]), sixteenth, off_hi);
+  d[2] = __hsub2(*reinterpret_cast<__half2*>(&p[2]), off_lo);
+  d[3] = __hfma2(*reinterpret_cast<__half2*>(&p[3]), sixteenth, off_hi);
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 v = __hfma2(d[i], s_hi, __hmul2(d[i], s_lo));
+    o[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+template <>
+__device__ __forceinline__ uint4 dequant_word<__nv_bfloat16>(uint32_t w, float z, __nv_bfloat162 s_hi, __nv_bfloat162 s_lo) {
+  uint32_t p[4];
+  Nibbles<__nv_bfloat16>::unpack(w, p);  // 128+c for all pairs
+  const __nv_bfloat162 off = __float2bfloat162_rn(128.f + z);
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 d = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&p[i]), off);
+    const __nv_bfloat162 v = __hfma2(d, s_hi, __hmul2(d, s_lo));
+    o[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* a_ring = smem;                                   // kStages x 16 KB
+  unsigned char* b_ring = a_ring + kStages * 16384;               // kStages x 16 KB (mt <= 128 rows x 128 B)
+  unsigned char* raw = b_ring + kStages * 16384;                  // kRawStages x 128 x kRawPitch
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + kRawStages * kRows * kRawPitch);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
+  const uint32_t raw_full = s_u32(bars), raw_empty = s_u32(bars + 2), a_full = s_u32(bars + 4), b_full = s_u32(bars + 8),
+                 ab_empty = s_u32(bars + 12), acc_full = s_u32(bars + 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * kRows;
+  const int m0 = blockIdx.z * p.mt;
+  const int kb_total = p.K / kBlockK;
+  const int kb0 = blockIdx.y * p.kblocks_per_split;
+  const int nkb = min(p.kblocks_per_split, kb_total - kb0);       // multiple of 8 (host guarantees)
+  int* status = p.counters ? p.counters + kStatusIndex : nullptr;
+  bool dead = false;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kRawStages; ++i) {
+      bar_init(raw_full + i * 8, 1);
+      bar_init(raw_empty + i * 8, kDequantThreads / 32);
+    }
+    for (int i = 0; i < kStages; ++i) {
+      bar_init(a_full + i * 8, kDequantThreads / 32);
+      bar_init(b_full + i * 8, 1);
+      bar_init(ab_empty + i * 8, 1);
+    }
+    bar_init(acc_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {  // tensor memory: one power-of-two block of columns for the fp32 accumulator
+    const uint32_t ncols = p.mt < 32 ? 32 : p.mt;
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_u32(tmem_slot)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 8) {
+    // ================= producer =================
+    const int nraw = nkb / 8;
+    int rs = 0;  // raw stages issued
+    for (int kb = 0; kb < nkb; ++kb) {
+      if ((kb & 7) == 0) {  // a new raw stage: 128 rows x 256 bytes, four rows per lane
+        const int slot = rs % kRawStages;
+        bar_wait(raw_empty + slot * 8, ((rs / kRawStages) & 1) ^ 1, status, dead);
+        if (lane == 0) bar_expect(raw_full + slot * 8, kRows * (kRawK / 2));
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = lane * 4 + j;
+          const int gr = min(row0 + r, p.N - 1);
+          bulk_row(s_u32(raw) + (slot * kRows + r) * kRawPitch,
+                   p.packed + (size_t)gr * (p.K >> 1) + (size_t)(kb0 + kb) * (kBlockK / 2), kRawK / 2, raw_full + slot * 8);
+        }
+        ++rs;
+      }
+      if (lane == 0) {  // activation tile of this block
+        const int s = kb % kStages;
+        bar_wait(ab_empty + s * 8, ((kb / kStages) & 1) ^ 1, status, dead);
+        bar_expect(b_full + s * 8, p.mt * 128);
+        tma_tile(s_u32(b_ring) + s * 16384, &tm_x, (kb0 + kb) * kBlockK, m0, b_full + s * 8);
+      }
+      __syncwarp();
+    }
+    (void)nraw;
+  } else if (warp == 9) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (Pair<T>::kFmt << 7) | (Pair<T>::kFmt << 10) | ((uint32_t)(p.mt >> 3) << 17) |
+                             ((uint32_t)(kRows >> 4) << 24);
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % kStages;
+        const uint32_t par = (kb / kStages) & 1;
+        bar_wait(a_full + s * 8, par, status, dead);
+        bar_wait(b_full + s * 8, par, status, dead);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = s_u32(a_ring) + s * 16384, b_addr = s_u32(b_ring) + s * 16384;
+#pragma unroll
+        for (int j = 0; j < kBlockK / 16; ++j)
+          umma_f16(tmem_acc, umma_desc(a_addr + j * 32), umma_desc(b_addr + j * 32), idesc, (kb | j) != 0);
+        umma_commit(ab_empty + s * 8);  // frees the operand stage when these MMAs have read it
+      }
+      umma_commit(acc_full);
+    }
+    __syncwarp();
+  } else {
+    // ================= dequantize =================
+    const int r = threadIdx.x & 127, h = threadIdx.x >> 7;  // row of the tile, 32-column half of the block
+    const int gr = min(row0 + r, p.N - 1);
+    const int spg = p.group_size / 128;                     // raw-stage quarters per group
+    const uint32_t a_row = (r >> 3) * 1024 + (r & 7) * 128;
+    float sc[4], zc[4];
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int rsi = kb >> 3, slot = rsi % kRawStages;
+      if ((kb & 7) == 0) {
+        // scale / zero of the four 128-column quarters of this raw stage
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int g = ((kb0 + kb) / 2 + i) / spg;
+          sc[i] = __ldg(p.scale + (size_t)gr * p.ngroups + g);
+          zc[i] = __ldg(p.zero + (size_t)gr * p.ngroups + g);
+        }
+        bar_wait(raw_full + slot * 8, (rsi / kRawStages) & 1, status, dead);
+      }
+      const int s = kb % kStages;
+      bar_wait(ab_empty + s * 8, ((kb / kStages) & 1) ^ 1, status, dead);
+      const uint4 codes = ld_s128(s_u32(raw) + (slot * kRows + r) * kRawPitch + (kb & 7) * 32 + h * 16);
+      const int quarter = (kb & 7) >> 1;
+      const float sq = quarter == 0 ? sc[0] : (quarter == 1 ? sc[1] : (quarter == 2 ? sc[2] : sc[3]));
+      const float z = quarter == 0 ? zc[0] : (quarter == 1 ? zc[1] : (quarter == 2 ? zc[2] : zc[3]));
+      const float sp = sq * Pair<T>::kPre;
+      const typename Pair<T>::V s_hi = Pair<T>::splat(sp);
+      const typename Pair<T>::V s_lo = Pair<T>::splat(sp - to_float<T>(from_float<T>(sp)));
+      const uint32_t wv[4] = {codes.x, codes.y, codes.z, codes.w};
+      const uint32_t dst = s_u32(a_ring) + s * 16384 + a_row;
+#pragma unroll
+      for (int wi = 0; wi < 4; ++wi) {
+        const uint4 v = dequant_word<T>(wv[wi], z, s_hi, s_lo);
+        st_s128(dst + (((h * 4 + wi) ^ (r & 7)) << 4), v.x, v.y, v.z, v.w);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // make the tile visible to the MMA unit
+      __syncwarp();
+      if (lane == 0) {
+        bar_arrive(a_full + s * 8);
+        if ((kb & 7) == 7) bar_arrive(raw_empty + slot * 8);
+      }
+    }
+
+    // ================= epilogue: TMEM -> registers -> global =================
+    bar_wait(acc_full, 0, status, dead);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int q4 = warp & 3, chalf = warp >> 2;
+    const int n = row0 + q4 * 32 + lane;
+    const int cpw = p.mt / 2;  // columns per warp group
+    T* yg = reinterpret_cast<T*>(p.y);
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    const float bv = (bias && n < p.N && p.splits == 1) ? to_float<T>(bias[n]) : 0.f;
+    float* part = p.splits > 1 ? p.partial + (size_t)blockIdx.y * p.M * p.N : nullptr;
+    for (int c = chalf * cpw; c < (chalf + 1) * cpw; c += 8) {
+      uint32_t v[8];
+      const uint32_t taddr = tmem_acc + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c;
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                   : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (n < p.N && !dead) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = m0 + c + i;
+          if (m < p.M) {
+            const float f = __uint_as_float(v[i]) * (1.f / Pair<T>::kPre);
+            if (part)
+              __stcg(part + (size_t)m * p.N + n, f);
+            else
+              yg[(size_t)m * p.ldy + n] = from_float<T>(f + bv);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: everyone done with tensor memory, then free it ----
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    const uint32_t ncols = p.mt < 32 ? 32 : p.mt;
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(ncols) : "memory");
+  }
+  if (p.splits == 1) return;
+
+  // ---- K spans several CTAs: the last one to arrive adds the partial sums in split order ----
+  __threadfence();
+  __syncthreads();
+  __shared__ int s_last;
+  const int tile_id = blockIdx.z * gridDim.x + blockIdx.x;
+  if (threadIdx.x == 0) s_last = (atomicAdd(p.counters + tile_id, 1) == p.splits - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int tile_rows = min(kRows, p.N - row0), tile_m = min(p.mt, p.M - m0);
+  T* yg = reinterpret_cast<T*>(p.y);
+  const T* bias = reinterpret_cast<const T*>(p.bias);
+  for (int idx = threadIdx.x; idx < tile_rows * tile_m; idx += kGemmThreads) {
+    const int mi = idx / tile_rows, n = row0 + (idx - mi * tile_rows), m = m0 + mi;
+    float v = 0.f;
+    for (int s = 0; s < p.splits; ++s) v += __ldcg(p.partial + ((size_t)s * p.M + m) * p.N + n);
+    if (bias) v += to_float<T>(bias[n]);
+    yg[(size_t)m * p.ldy + n] = from_float<T>(v);
+  }
+  if (threadIdx.x == 0) p.counters[tile_id] = 0;
+}
+
+// ---- host side --------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+constexpr size_t kGemmSmem = 1024 + 2 * kStages * 16384 + kRawStages * kRows * kRawPitch + 25 * 8 + 64;
+
+struct GemmPlan {
+  int mt, mtiles, mpad, splits, kblocks_per_split;
+};
+
+GemmPlan gemm_plan(int M, int N, int K) {
+  GemmPlan g{};
+  g.mt = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+  g.mtiles = (M + g.mt - 1) / g.mt;
+  g.mpad = g.mtiles * g.mt;
+  const int row_tiles = (N + kRows - 1) / kRows;
+  const int raw_stages = K / kRawK;
+  int splits = (148 + row_tiles * g.mtiles - 1) / (row_tiles * g.mtiles);
+  if (splits > raw_stages) splits = raw_stages;
+  if (splits > 16) splits = 16;
+  if (splits < 1) splits = 1;
+  const int per = (raw_stages + splits - 1) / splits;
+  g.splits = (raw_stages + per - 1) / per;
+  g.kblocks_per_split = per * 8;
+  return g;
+}
+
+}  // namespace
+
+bool gemm_supported(int M, int K, int G, const float* scale, const float* zero) {
+  return M > 16 && (K % kRawK) == 0 && (G % 128) == 0 && scale != nullptr && zero != nullptr;
+}
+
+size_t gemm_workspace_bytes(int M, int N, int K) {
+  const GemmPlan g = gemm_plan(M, N, K);
+  return kCounterBytes + ((size_t)g.mpad * K * 2 + 255) / 256 * 256 + (size_t)16 * M * N * sizeof(float);
+}
+
+int gemm_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale, const float* zero,
+                 const int32_t* col_perm, const float* input_scale, const void* bias, void* y, int64_t ldy, int M, int N,
+                 int K, int G, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  const GemmPlan g = gemm_plan(M, N, K);
+  const size_t xq_bytes = ((size_t)g.mpad * K * 2 + 255) / 256 * 256;
+  const size_t need = kCounterBytes + xq_bytes + (g.splits > 1 ? (size_t)g.splits * M * N * sizeof(float) : 0);
+  PARE_REQUIRE(workspace != nullptr && workspace_bytes >= need, PARE_ERR_WORKSPACE);
+  PARE_REQUIRE(aligned16(packed), PARE_ERR_ALIGN);
+  const int row_tiles = (N + kRows - 1) / kRows;
+  PARE_REQUIRE((size_t)row_tiles * g.mtiles < kStatusIndex, PARE_ERR_UNSUPPORTED);
+  unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
+  void* xq = ws + kCounterBytes;
+
+  // 1) activations: slot order inside every 8-column chunk, gather, input scale
+  {
+    const int64_t total = (int64_t)M * K;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (x_dtype == PARE_F16)
+      w4a16_gemm_prep_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)x, ldx, col_perm, input_scale, (__half*)xq, M, K);
+    else
+      w4a16_gemm_prep_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, col_perm, input_scale,
+                                                                        (__nv_bfloat16*)xq, M, K);
+    if (cudaGetLastError() != cudaSuccess) return PARE_ERR_CUDA;
+  }
+
+  // 2) tensor map over the prepared activations [mpad][K], box 64 columns x mt rows, 128B swizzle
+  EncodeTiledFn enc = encode_fn();
+  PARE_REQUIRE(enc != nullptr, PARE_ERR_CUDA);
+  CUtensorMap tm;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)g.mpad};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)g.mt};
+  const cuuint32_t estr[2] = {1, 1};
+  PARE_REQUIRE(enc(&tm, x_dtype == PARE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xq, dims,
+                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
+               PARE_ERR_CUDA);
+
+  GemmParams p{};
+  p.packed = packed;
+  p.scale = scale;
+  p.zero = zero;
+  p.bias = bias;
+  p.y = y;
+  p.ldy = ldy;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ngroups = K / G;
+  p.group_size = G;
+  p.mt = g.mt;
+  p.kblocks_per_split = g.kblocks_per_split;
+  p.splits = g.splits;
+  p.counters = reinterpret_cast<int*>(ws);
+  p.partial = reinterpret_cast<float*>(ws + kCounterBytes + xq_bytes);
+
+  const dim3 grid(row_tiles, g.splits, g.mtiles);
+  auto launch = [&](auto kern) -> int {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem) != cudaSuccess)
+      return PARE_ERR_CUDA;
+    kern<<<grid, kGemmThreads, kGemmSmem, stream>>>(tm, p);
+    return launch_status();
+  };
+  return x_dtype == PARE_F16 ? launch(w4a16_gemm_kernel<__half>) : launch(w4a16_gemm_kernel<__nv_bfloat16>);
+}
+
+}  // namespace pare

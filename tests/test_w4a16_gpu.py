@@ -226,3 +226,65 @@ def test_error_conditions(cuda_lib):
         matmul_w4a16(torch.randn(2, 256, device="cuda"), w, ql.scale, ql.zero, 128)            # fp32
     with pytest.raises(AssertionError):
         matmul_w4a16(torch.randn(2, 128, device="cuda", dtype=torch.float16), w, ql.scale, ql.zero, 128)
+
+
+# ---- tensor-core path (M > 16, K % 512 == 0): tcgen05 tiles over dequantized shared-memory operands ----
+
+def _oracle_rounded_weights(ql, x, dtype, **kw):
+    """Reference semantics of the eager path for 16-bit inputs (pare/layers/linear.py:129):
+    the dequantized weight is cast to the activation dtype before the matmul."""
+    n = ql.out_features
+    w = ow.dequantize(ql.packed_weight.cpu().numpy(), ql.scale.cpu().numpy().reshape(n, -1),
+                      ql.zero.cpu().numpy().reshape(n, -1), kw.get("g_idx"))
+    w = torch.from_numpy(w).to(dtype).float().numpy()
+    xin = x.float().cpu().numpy()
+    if kw.get("input_scale") is not None:
+        xin = torch.from_numpy(xin / kw["input_scale"]).to(dtype).float().numpy()
+    y = xin @ w.T
+    if ql.bias is not None:
+        y = y + ql.bias.detach().to(dtype).float().cpu().numpy()
+    return y
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m", [17, 32, 64, 100, 128, 200, 256])
+@pytest.mark.parametrize("shape", [(512, 1024), (1000, 512), (4096, 4096)])
+def test_tensor_core_path_matches_oracle(shape, m, dtype, cuda_lib):
+    n, k = shape
+    ql = make_ql(n, k, seed=n + k + 1, bias=True).cuda()
+    torch.manual_seed(m)
+    x = torch.randn(m, k, device="cuda", dtype=dtype)
+    y = w4a16_forward(x, ql.packed_weight, ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous(), 128,
+                      bias=ql.bias.detach().to(dtype))
+    assert y.shape == (m, n) and y.dtype == dtype
+    # bar 1: the reference's eager semantics (weights cast to the activation dtype, fp32 accumulate).  Mean
+    # bars as everywhere else (1e-3 fp16, 2.5e-3 bf16).  The max bar is 2e-2 / 2e-1: a fraction of a percent
+    # of the weights land one ulp of the 16-bit type off the reference's cast (the scale goes through a
+    # two-term 16-bit expansion), which only shows at outputs near zero.
+    mx, mean = ow.rel_err(y.float().cpu().numpy(), _oracle_rounded_weights(ql, x, dtype))
+    assert mx <= (2e-1 if dtype == torch.bfloat16 else 2e-2) and mean <= (2.5e-3 if dtype == torch.bfloat16 else MEAN_REL), (mx, mean)
+    # bar 2: the fp32-weight oracle.  Casting the weights to the activation dtype (what the reference's eager
+    # path does too) alone costs ~6e-4 mean / 2e-2 max in fp16 and ~5e-3 mean / 1.5e-1 max in bf16 here.
+    mx, mean = ow.rel_err(y.float().cpu().numpy(), oracle_y(ql, x) - ql.bias.detach().float().cpu().numpy()
+                          + ql.bias.detach().to(dtype).float().cpu().numpy())
+    assert mx <= (2e-1 if dtype == torch.bfloat16 else 3e-2) and mean <= (6e-3 if dtype == torch.bfloat16 else 1e-3), (mx, mean)
+    y2 = w4a16_forward(x, ql.packed_weight, ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous(), 128,
+                       bias=ql.bias.detach().to(dtype))
+    assert torch.equal(y, y2)
+
+
+def test_tensor_core_path_options(cuda_lib):
+    """act-order gather, run-time input scale and per_channel groups through the tile kernel."""
+    torch.manual_seed(21)
+    n, k, m = 384, 1024, 96
+    ql = make_ql(n, k, seed=4)
+    s = torch.exp(torch.randn(k) * 0.3)
+    ql.input_scale = s
+    ql = ql.cuda()
+    ql.use_kernel = True
+    x = torch.randn(m, k, device="cuda", dtype=torch.float16)
+    check(ql(x), _oracle_rounded_weights(ql, x, torch.float16, input_scale=s.numpy()), torch.float16)
+    qc = make_ql(256, 512, seed=6, granularity="per_channel").cuda()
+    qc.use_kernel = True
+    xc = torch.randn(40, 512, device="cuda", dtype=torch.float16)
+    check(qc(xc), _oracle_rounded_weights(qc, xc, torch.float16), torch.float16)
