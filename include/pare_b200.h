@@ -162,6 +162,31 @@ int pare_rmsnorm_residual(const void* x, const void* delta, const void* weight, 
                           int rows, int n, float eps, int dtype, void* stream);
 int pare_silu_mul(const void* gate_up, void* out, int rows, int n, int64_t ld, int dtype, void* stream);
 
+/* ------------------------------------------------------------------------
+ * W4A16 decode linear without any caller-provided workspace.  No counterpart in the reference;
+ * it exists for callers that cannot allocate device memory (code running inside another
+ * runtime's callback or memory pool where cudaMalloc is forbidden or would synchronise, or code
+ * that only ever receives input and output pointers).  Same arguments and results as
+ * pare_w4a16_forward for M <= 16, minus the workspace: the scratch is a fixed 16 MiB array inside
+ * the library's device image (every GPU that loads the library holds it until the process exits).
+ *   - Layers whose scratch need (pare_w4a16_workspace_bytes) exceeds
+ *     pare_w4a16_static_scratch_bytes() are rejected with PARE_ERR_WORKSPACE; M > 16 with
+ *     PARE_ERR_UNSUPPORTED.
+ *   - Calls nothing that allocates.  The first call on each device looks up the array's device
+ *     address; make that first call outside any stream capture.
+ *   - All calls on a device share the one array: calls that may overlap on the GPU (different
+ *     streams) race; order them on one stream. */
+size_t pare_w4a16_static_scratch_bytes(void);
+
+int pare_w4a16_forward_static(const void* x, int x_dtype, int64_t ldx,
+                              const uint8_t* packed,
+                              const float* scale, const float* zero, const void* meta_h2,
+                              const int32_t* col_perm, const float* input_scale,
+                              const void* bias,
+                              void* y, int64_t ldy,
+                              int M, int N, int K, int group_size,
+                              void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,6 +43,9 @@ SIGNATURES: dict[str, tuple] = {
     "pare_kivi_attn_set_tuning": (None, [_i]),
     "pare_rmsnorm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, C.c_float, _i, _vp]),
     "pare_silu_mul": (_i, [_vp, _vp, _i, _i, _i64, _i, _vp]),
+    "pare_w4a16_static_scratch_bytes": (_sz, []),
+    "pare_w4a16_forward_static": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                                       _i, _i, _i, _i, _vp]),
 }
 
 
