@@ -1,0 +1,89 @@
+"""Tensor-parallel helpers for the hot path (one process per GPU, ``torch.distributed``).
+
+The reference has no distributed code at all; this is the sharding its layers admit:
+
+* **column parallel** (q, k, v, gate, up): rank r keeps output rows ``[r*N/W, (r+1)*N/W)`` — dim 0
+  of ``packed_weight`` / ``scale`` / ``zero`` / ``bias``.  No communication; outputs stay sharded.
+* **row parallel** (o, down): rank r keeps input columns ``[r*K/W, (r+1)*K/W)`` — dim 1 of
+  ``packed_weight`` (in bytes: half of that) and whole groups of ``scale`` / ``zero``; its input is
+  the matching slice of the activations (already sharded by the preceding column-parallel layer),
+  the partial outputs are summed with one all-reduce, the bias is added on rank 0 only.
+* **KV cache**: whole KV heads per rank together with their group of query heads; no communication
+  inside attention.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from pare_b200.layers.linear import QuantizedLinear
+
+
+def shard_range(total: int, rank: int, world: int, multiple: int = 1) -> tuple[int, int]:
+    """``[start, stop)`` of rank's equal share of ``total``; the share must be a multiple of ``multiple``."""
+    if total % world or (total // world) % multiple:
+        raise ValueError(f"cannot split {total} over {world} ranks in multiples of {multiple}")
+    per = total // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_linear(layer: QuantizedLinear, mode: str, rank: int, world: int) -> QuantizedLinear:
+    """Return rank's shard of an INT4 ``QuantizedLinear`` (``mode`` = ``"column"`` or ``"row"``)."""
+    if layer.packed_weight is None:
+        raise ValueError("only INT4 (packed) layers can be sharded")
+    n, k = layer.out_features, layer.in_features
+    cfg = layer.config
+    scale, zero = layer.scale, layer.zero
+    if mode == "column":
+        a, b = shard_range(n, rank, world)
+        if scale.dim() == 0:
+            s, z = scale, zero
+        else:
+            s, z = scale[a:b], zero[a:b]
+        shard = QuantizedLinear.from_tensors(
+            layer.packed_weight[a:b].contiguous(), None, s.contiguous(), z.contiguous(), cfg,
+            None if layer.bias is None else layer.bias.detach()[a:b], k, b - a,
+            g_idx=layer.g_idx, input_scale=layer.input_scale)
+    elif mode == "row":
+        if layer.g_idx is not None:
+            raise ValueError("row-parallel sharding of an act-order layer is not supported")
+        group = cfg.group_size if cfg.granularity == "per_group" else 2
+        a, b = shard_range(k, rank, world, multiple=group)
+        if cfg.granularity == "per_group":
+            s, z = scale[:, a // group:b // group], zero[:, a // group:b // group]
+        else:
+            s, z = scale, zero
+        shard = QuantizedLinear.from_tensors(
+            layer.packed_weight[:, a // 2:b // 2].contiguous(), None, s.contiguous(), z.contiguous(), cfg,
+            layer.bias.detach() if (layer.bias is not None and rank == 0) else None, b - a, n,
+            input_scale=None if layer.input_scale is None else layer.input_scale[a:b].contiguous())
+    else:
+        raise ValueError(f"unknown mode {mode!r}")
+    shard.use_kernel = layer.use_kernel
+    shard.kernel_meta_fp16 = layer.kernel_meta_fp16
+    return shard
+
+
+def shard_heads(n_heads: int, rank: int, world: int) -> range:
+    """The KV heads (or query heads) owned by ``rank``."""
+    a, b = shard_range(n_heads, rank, world)
+    return range(a, b)
+
+
+def row_parallel_forward(shard: QuantizedLinear, x_shard: Tensor, group=None) -> Tensor:
+    """``shard(x_shard)`` summed over the ranks of ``group`` (the exchange step of o / down)."""
+    y = shard(x_shard)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(y, group=group)
+    return y
+
+
+def gather_columns(y_shard: Tensor, group=None) -> Tensor:
+    """All-gather the outputs of a column-parallel layer along the last dim (for logits)."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return y_shard
+    parts = [torch.empty_like(y_shard) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, y_shard.contiguous(), group=group)
+    return torch.cat(parts, dim=-1)
