@@ -192,6 +192,7 @@ def dist_setup(n_gpus: int):
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
     return world, rank, local
 

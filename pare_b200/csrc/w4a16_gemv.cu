@@ -31,122 +31,12 @@
 // The mbarrier wait is bounded; on expiry the kernel records PARE_ERR_TIMEOUT in the
 // workspace status word and runs to completion without waiting again.
 
-#include "common.cuh"
+#include "gemv_common.cuh"
 
 namespace pare {
 namespace {
 
-constexpr int kTileRows = 16;
-constexpr int kMaxStepsPerWarp = 8;   // 1024 columns per warp
-constexpr int kTabCols = 16;          // activation rows per call (two MMA column blocks)
-constexpr uint32_t kSpinLimit = 1u << 22;
-
-// Workspace layout: [counters | status word][prepared activations][step table][partials fp32].  The counter region has a FIXED
-// size so the partial sums of one call can never land where another call keeps its counters;
-// the counters are the only part that must be zero between calls.
-constexpr size_t kCounterInts = 16384;
-constexpr size_t kCounterBytes = kCounterInts * sizeof(int);
-constexpr size_t kStatusIndex = kCounterInts - 1;
-
-struct GemvParams {
-  const void* x;
-  int64_t ldx;
-  const uint8_t* packed;
-  const float* scale;
-  const float* zero;
-  const uint32_t* meta_h2;
-  const int32_t* col_perm;
-  const float* input_scale;
-  const void* bias;
-  void* y;
-  int64_t ldy;
-  int M, N, K;
-  int ngroups;          // K / group_size
-  int steps_per_group;  // group_size / 128
-  int steps_per_split;  // 128-column steps per CTA
-  int splits;
-  void* xp;             // [M][K] activations in operand order (workspace)
-  float2* tabg;         // [K/128][kTabCols] (E, SX) per step and activation row (workspace)
-  float* partial;       // [splits][M][N]
-  int* counters;        // [row tiles]; counters[kStatusIndex] is the status word
-  int x_vec_ok;
-};
-
-// ---- mbarrier / bulk-copy primitives -----------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: returns false (and records the failure) instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
-#pragma unroll 1
-  for (uint32_t i = 0; i < kSpinLimit; ++i)
-    if (mbar_test(bar, parity)) return true;
-  if (status) atomicExch(status, PARE_ERR_TIMEOUT);
-  return false;
-}
-// contiguous global -> shared copy of `bytes` (multiple of 16, both addresses 16-byte aligned)
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-
-// explicit shared-space accesses through 32-bit shared addresses
-__device__ __forceinline__ uint4 lds_v4(uint32_t a) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ float4 lds_v4f(uint32_t a) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ void sts_v4(uint32_t a, uint4 v) {
-  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ void sts_v4f(uint32_t a, float x, float y, float z, float w) {
-  asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(a), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
-}
-
-// D = A * B (accumulator starts at zero: no register initialisation, no dependency on a previous value)
-template <typename T>
-__device__ __forceinline__ void mma16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1);
-template <>
-__device__ __forceinline__ void mma16816_zero<__half>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                                      uint32_t b0, uint32_t b1) {
-  const float z = 0.f;
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z));
-}
-template <>
-__device__ __forceinline__ void mma16816_zero<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                                             uint32_t a3, uint32_t b0, uint32_t b1) {
-  const float z = 0.f;
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z));
-}
+using namespace gemv;
 
 // ---- activation preparation: once per call, not per CTA ------------------------------------
 // Writes x in the operand order of the inner product (per 128-column step: [word 0..3][quad 0..3]
@@ -206,11 +96,16 @@ __global__ void __launch_bounds__(128) w4a16_prep_kernel(const GemvParams p) {
                                                     lo + hi / Nibbles<T>::kHiPrescale);
 }
 
-template <typename T, int MB, int WARPS, bool META16>
+// RB = 16-row blocks per CTA (every warp takes all of them over its share of K: the activation
+// fragments are read once per step for all RB blocks, and the per-warp prologue / epilogue is paid
+// once for RB times the work).
+template <typename T, int MB, int WARPS, bool META16, int RB>
 __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int MP = 8 * MB;
   constexpr int THREADS = WARPS * 32;
+  constexpr int kTileRows = 16 * RB;
+  constexpr int kSteps = kMaxStepsPerWarp / RB;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
@@ -229,8 +124,8 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
   unsigned char* wt = smem;
   unsigned char* xs = wt + kTileRows * pitch;
   float2* tab = reinterpret_cast<float2*>(xs + (size_t)xrows * xstride);           // [nst][kTabCols] (E, SX)
-  float* red = reinterpret_cast<float*>(tab + (size_t)nst * kTabCols);             // [WARPS][MB][32][4]
-  uint32_t* zero_blk = reinterpret_cast<uint32_t*>(red + WARPS * MB * 128);        // 256 zero bytes
+  float* red = reinterpret_cast<float*>(tab + (size_t)nst * kTabCols);             // [WARPS][RB][MB][32][4]
+  uint32_t* zero_blk = reinterpret_cast<uint32_t*>(red + WARPS * RB * MB * 128);   // 256 zero bytes
   uint64_t* bar_ptr = reinterpret_cast<uint64_t*>(zero_blk + 64);
   const uint32_t bar = smem_u32(bar_ptr);
   const uint32_t wt_u32 = smem_u32(wt), xs_u32 = smem_u32(xs), tab_u32 = smem_u32(tab);
@@ -239,8 +134,7 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
   // ---- this warp's share of the K range ----
   const int spw = (nst + WARPS - 1) / WARPS;
   const int ws = warp * spw;
-  const int nsw = max(0, min(nst, ws + spw) - ws);   // <= kMaxStepsPerWarp (host guarantees)
-  const int rA = min(row0 + gid, p.N - 1), rB = min(row0 + gid + 8, p.N - 1);
+  const int nsw = max(0, min(nst, ws + spw) - ws);   // <= kSteps (host guarantees)
 
   if (threadIdx.x == 0) {
     mbar_init(bar, 1);
@@ -259,25 +153,26 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
     }
   }
   // ---- scale / zero of this warp's steps, rows gid and gid + 8, straight into registers ----
-  float ms[kMaxStepsPerWarp][2], mz[kMaxStepsPerWarp][2];
+  float ms[kSteps][RB][2], mz[kSteps][RB][2];
 #pragma unroll
-  for (int j = 0; j < kMaxStepsPerWarp; ++j) {
+  for (int j = 0; j < kSteps; ++j) {
     if (j < nsw) {
       const int g = spg == 1 ? st0 + ws + j : (st0 + ws + j) / spg;   // group_size 128: no division
-      const size_t ia = (size_t)rA * p.ngroups + g, ib = (size_t)rB * p.ngroups + g;
-      if (META16) {
-        const uint32_t va = __ldg(p.meta_h2 + ia), vb = __ldg(p.meta_h2 + ib);
-        const __half2 ha = *reinterpret_cast<const __half2*>(&va), hb = *reinterpret_cast<const __half2*>(&vb);
-        ms[j][0] = __low2float(ha);
-        mz[j][0] = __high2float(ha);
-        ms[j][1] = __low2float(hb);
-        mz[j][1] = __high2float(hb);
-      } else {
-        ms[j][0] = __ldg(p.scale + ia);
-        mz[j][0] = __ldg(p.zero + ia);
-        ms[j][1] = __ldg(p.scale + ib);
-        mz[j][1] = __ldg(p.zero + ib);
-      }
+#pragma unroll
+      for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const size_t idx = (size_t)min(row0 + rb * 16 + gid + 8 * h, p.N - 1) * p.ngroups + g;
+          if (META16) {
+            const uint32_t v = __ldg(p.meta_h2 + idx);
+            const __half2 hv = *reinterpret_cast<const __half2*>(&v);
+            ms[j][rb][h] = __low2float(hv);
+            mz[j][rb][h] = __high2float(hv);
+          } else {
+            ms[j][rb][h] = __ldg(p.scale + idx);
+            mz[j][rb][h] = __ldg(p.zero + idx);
+          }
+        }
     }
   }
 
@@ -300,14 +195,15 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
   mbar_wait(bar, 0, status);
 
   // ---- main loop over this warp's steps ----
-  float yacc[MB][4];
+  float yacc[RB][MB][4];
 #pragma unroll
-  for (int mb = 0; mb < MB; ++mb)
+  for (int rb = 0; rb < RB; ++rb)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) yacc[mb][i] = 0.f;
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) yacc[rb][mb][i] = 0.f;
   {
     const uint32_t wa_addr = wt_u32 + gid * pitch + ws * 64 + tig * 16;
-    const uint32_t wb_addr = wa_addr + 8 * pitch;
     const uint32_t tab_addr = tab_u32 + ws * (kTabCols * 8) + tig * 16;
     uint32_t xaddr[MB], xstep[MB];
 #pragma unroll
@@ -318,43 +214,48 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
       xstep[mb] = m < p.M ? 256u : 0u;
     }
 #pragma unroll
-    for (int j = 0; j < kMaxStepsPerWarp; ++j) {
+    for (int j = 0; j < kSteps; ++j) {
       if (j < nsw) {
-        const uint4 wa4 = lds_v4(wa_addr + j * 64);
-        const uint4 wb4 = lds_v4(wb_addr + j * 64);
-        const uint32_t wa[4] = {wa4.x, wa4.y, wa4.z, wa4.w};
-        const uint32_t wb[4] = {wb4.x, wb4.y, wb4.z, wb4.w};
         uint4 xb[MB][4];
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
           for (int i = 0; i < 4; ++i) xb[mb][i] = lds_v4(xaddr[mb] + j * xstep[mb] + i * 64);
-        float d0[MB][4], d1[MB][4];
+        float4 t[MB];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t pa[4], pb[4];
-          Nibbles<T>::unpack(wa[i], pa);
-          Nibbles<T>::unpack(wb[i], pb);
+        for (int mb = 0; mb < MB; ++mb) t[mb] = lds_v4f(tab_addr + j * (kTabCols * 8) + mb * 64);  // E0 SX0 E1 SX1
 #pragma unroll
-          for (int mb = 0; mb < MB; ++mb) {
-            if (i == 0) {
-              mma16816_zero<T>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][i].x, xb[mb][i].y);
-              mma16816_zero<T>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][i].z, xb[mb][i].w);
-            } else {
-              mma16816<T>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][i].x, xb[mb][i].y);
-              mma16816<T>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][i].z, xb[mb][i].w);
+        for (int rb = 0; rb < RB; ++rb) {
+          const uint4 wa4 = lds_v4(wa_addr + rb * 16 * pitch + j * 64);
+          const uint4 wb4 = lds_v4(wa_addr + (rb * 16 + 8) * pitch + j * 64);
+          const uint32_t wa[4] = {wa4.x, wa4.y, wa4.z, wa4.w};
+          const uint32_t wb[4] = {wb4.x, wb4.y, wb4.z, wb4.w};
+          float d0[MB][4], d1[MB][4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t pa[4], pb[4];
+            Nibbles<T>::unpack(wa[i], pa);
+            Nibbles<T>::unpack(wb[i], pb);
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb) {
+              if (i == 0) {
+                mma16816_zero<T>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][i].x, xb[mb][i].y);
+                mma16816_zero<T>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][i].z, xb[mb][i].w);
+              } else {
+                mma16816<T>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][i].x, xb[mb][i].y);
+                mma16816<T>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][i].z, xb[mb][i].w);
+              }
             }
           }
-        }
-        // fold this step with its group's scale / zero (linear, so folding per step is exact for any group size)
-        const float sA = ms[j][0], zA = mz[j][0], sB = ms[j][1], zB = mz[j][1];
+          // fold this step with its group's scale / zero (linear, so folding per step is exact for any group size)
+          const float sA = ms[j][rb][0], zA = mz[j][rb][0], sB = ms[j][rb][1], zB = mz[j][rb][1];
 #pragma unroll
-        for (int mb = 0; mb < MB; ++mb) {
-          const float4 t = lds_v4f(tab_addr + j * (kTabCols * 8) + mb * 64);  // E0 SX0 E1 SX1 of columns tig*2, tig*2+1
-          yacc[mb][0] = fmaf(sA, fmaf(-zA, t.y, (d0[mb][0] + d1[mb][0]) - t.x), yacc[mb][0]);
-          yacc[mb][1] = fmaf(sA, fmaf(-zA, t.w, (d0[mb][1] + d1[mb][1]) - t.z), yacc[mb][1]);
-          yacc[mb][2] = fmaf(sB, fmaf(-zB, t.y, (d0[mb][2] + d1[mb][2]) - t.x), yacc[mb][2]);
-          yacc[mb][3] = fmaf(sB, fmaf(-zB, t.w, (d0[mb][3] + d1[mb][3]) - t.z), yacc[mb][3]);
+          for (int mb = 0; mb < MB; ++mb) {
+            yacc[rb][mb][0] = fmaf(sA, fmaf(-zA, t[mb].y, (d0[mb][0] + d1[mb][0]) - t[mb].x), yacc[rb][mb][0]);
+            yacc[rb][mb][1] = fmaf(sA, fmaf(-zA, t[mb].w, (d0[mb][1] + d1[mb][1]) - t[mb].z), yacc[rb][mb][1]);
+            yacc[rb][mb][2] = fmaf(sB, fmaf(-zB, t[mb].y, (d0[mb][2] + d1[mb][2]) - t[mb].x), yacc[rb][mb][2]);
+            yacc[rb][mb][3] = fmaf(sB, fmaf(-zB, t[mb].w, (d0[mb][3] + d1[mb][3]) - t[mb].z), yacc[rb][mb][3]);
+          }
         }
       }
     }
@@ -362,19 +263,22 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
 
   // ---- the warps' partial sums meet in shared memory ----
 #pragma unroll
-  for (int mb = 0; mb < MB; ++mb)
-    sts_v4f(smem_u32(red) + ((warp * MB + mb) * 32 + lane) * 16, yacc[mb][0], yacc[mb][1], yacc[mb][2], yacc[mb][3]);
+  for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+      sts_v4f(smem_u32(red) + (((warp * RB + rb) * MB + mb) * 32 + lane) * 16, yacc[rb][mb][0], yacc[rb][mb][1],
+              yacc[rb][mb][2], yacc[rb][mb][3]);
   __syncthreads();
 
   T* yg = reinterpret_cast<T*>(p.y);
   const T* bias = reinterpret_cast<const T*>(p.bias);
   float* part = p.splits > 1 ? p.partial + (size_t)blockIdx.y * p.M * p.N : nullptr;
-  if (threadIdx.x < 32 * MB) {
-    const int mb = threadIdx.x >> 5;
+  if (threadIdx.x < 32 * MB * RB) {   // one warp per (row block, column block)
+    const int rb = (threadIdx.x >> 5) / MB, mb = (threadIdx.x >> 5) % MB;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int w = 0; w < WARPS; ++w) {
-      const float4 v = lds_v4f(smem_u32(red) + ((w * MB + mb) * 32 + lane) * 16);
+      const float4 v = lds_v4f(smem_u32(red) + (((w * RB + rb) * MB + mb) * 32 + lane) * 16);
       acc.x += v.x;
       acc.y += v.y;
       acc.z += v.z;
@@ -383,7 +287,7 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
     const float out[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int n = row0 + gid + 8 * (i >> 1);
+      const int n = row0 + rb * 16 + gid + 8 * (i >> 1);
       const int m = mb * 8 + tig * 2 + (i & 1);
       if (n < p.N && m < p.M) {
         if (part) {
@@ -461,26 +365,41 @@ int g_tune_kc = 0, g_tune_warps = 0;
 
 struct Plan {
   bool fast;
-  int warps, splits, steps_per_split;
+  int warps, rb, splits, steps_per_split;
   size_t smem;
 };
 
 constexpr int kSmCount = 148;
-constexpr size_t kSmemCap = 100 * 1024;
+constexpr size_t kSmemCap = 110 * 1024;
 
-size_t gemv_smem(int M, int MB, int nst, int warps) {
+size_t gemv_smem(int M, int MB, int nst, int warps, int rb) {
   const int xrows = M < 8 * MB ? M : 8 * MB;
-  return (size_t)kTileRows * (nst * 64 + 64) + (size_t)xrows * (nst * 256 + 64) + (size_t)nst * kTabCols * sizeof(float2) +
-         (size_t)warps * MB * 128 * sizeof(float) + 256 + 16 + 128;
+  return (size_t)16 * rb * (nst * 64 + 64) + (size_t)xrows * (nst * 256 + 64) + (size_t)nst * kTabCols * sizeof(float2) +
+         (size_t)warps * rb * MB * 128 * sizeof(float) + 256 + 16 + 128;
 }
 
+int g_tune_rb = 0;
+int g_tune_persist = 0;   // -1 disables the persistent schedule (experiments)
+
+Plan make_plan_rb(int M, int N, int K, int G, int rb_request);
+
 Plan make_plan(int M, int N, int K, int G) {
+  Plan pl = make_plan_rb(M, N, K, G, g_tune_rb);
+  if (pl.fast && pl.rb == 2 && pl.smem > kSmemCap) pl = make_plan_rb(M, N, K, G, 1);  // tile too large with 32 rows
+  return pl;
+}
+
+Plan make_plan_rb(int M, int N, int K, int G, int rb_request) {
   Plan pl{};
   pl.fast = (K % 512 == 0) && (G % 128 == 0);  // K ranges are cut in multiples of 512 columns
   if (!pl.fast) return pl;
   const int MB = M <= 8 ? 1 : 2;
   const int chunks = K / 512;
-  const int row_tiles = (N + kTileRows - 1) / kTileRows;
+  // two 16-row blocks per CTA when that still leaves at least two CTAs per SM (big layers): half the
+  // per-warp overhead per weight.  Small layers keep 16-row CTAs for parallelism.
+  int rb = rb_request ? rb_request : (((N + 31) / 32 >= 2 * kSmCount && MB == 1) ? 2 : 1);
+  if (rb != 1 && rb != 2) rb = 1;
+  const int row_tiles = (N + 16 * rb - 1) / (16 * rb);
   // columns per CTA: bounded by the activation tile that must sit in shared memory beside the weights
   int kc = g_tune_kc ? g_tune_kc : (M <= 4 ? 4096 : (M <= 8 ? 2048 : 1024));
   // very small layers only: cut K further until there is at least one CTA per SM (going through the
@@ -497,21 +416,23 @@ Plan make_plan(int M, int N, int K, int G) {
   }
   splits = (chunks + cps - 1) / cps;
   const int nst = cps * 4;
+  const int max_steps = kMaxStepsPerWarp / rb;
   // enough CTAs to fill the machine three times over: fewer, longer warps (less per-warp overhead);
   // otherwise more warps per CTA to shorten each CTA's critical path
   int warps = g_tune_warps ? g_tune_warps : ((nst >= 16 && (long long)row_tiles * splits < 3 * kSmCount) ? 8 : 4);
   if (warps != 4 && warps != 8) warps = 4;
-  if ((nst + warps - 1) / warps > kMaxStepsPerWarp) warps = 8;
+  if ((nst + warps - 1) / warps > max_steps || rb == 2) warps = 8;
   pl.warps = warps;
+  pl.rb = rb;
   pl.splits = splits;
   pl.steps_per_split = nst;
-  pl.smem = gemv_smem(M, MB, nst, warps);
+  pl.smem = gemv_smem(M, MB, nst, warps, rb);
   return pl;
 }
 
-template <typename T, int MB, int WARPS, bool META16>
+template <typename T, int MB, int WARPS, bool META16, int RB>
 int launch_gemv(const GemvParams& p, const Plan& pl, cudaStream_t stream) {
-  auto kern = w4a16_gemv_kernel<T, MB, WARPS, META16>;
+  auto kern = w4a16_gemv_kernel<T, MB, WARPS, META16, RB>;
   static bool attr_done[64] = {};  // per instantiation and device
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return PARE_ERR_CUDA;
@@ -521,7 +442,7 @@ int launch_gemv(const GemvParams& p, const Plan& pl, cudaStream_t stream) {
     attr_done[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((p.N + kTileRows - 1) / kTileRows, pl.splits, 1);
+  cfg.gridDim = dim3((p.N + 16 * RB - 1) / (16 * RB), pl.splits, 1);
   cfg.blockDim = dim3(WARPS * 32, 1, 1);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = stream;
@@ -537,9 +458,11 @@ int launch_gemv(const GemvParams& p, const Plan& pl, cudaStream_t stream) {
 template <typename T, int MB>
 int dispatch_warps(const GemvParams& p, const Plan& pl, cudaStream_t stream) {
   const bool m16 = p.meta_h2 != nullptr;
+  if (MB == 1 && pl.rb == 2)   // 32-row CTAs always run 8 warps (4 steps x 2 row blocks per warp)
+    return m16 ? launch_gemv<T, 1, 8, true, 2>(p, pl, stream) : launch_gemv<T, 1, 8, false, 2>(p, pl, stream);
   if (pl.warps == 8)
-    return m16 ? launch_gemv<T, MB, 8, true>(p, pl, stream) : launch_gemv<T, MB, 8, false>(p, pl, stream);
-  return m16 ? launch_gemv<T, MB, 4, true>(p, pl, stream) : launch_gemv<T, MB, 4, false>(p, pl, stream);
+    return m16 ? launch_gemv<T, MB, 8, true, 1>(p, pl, stream) : launch_gemv<T, MB, 8, false, 1>(p, pl, stream);
+  return m16 ? launch_gemv<T, MB, 4, true, 1>(p, pl, stream) : launch_gemv<T, MB, 4, false, 1>(p, pl, stream);
 }
 
 template <typename T>
@@ -556,6 +479,10 @@ int launch_generic(const GemvParams& p, const uint8_t* packed, int G, cudaStream
 }
 
 }  // namespace
+
+bool gemv_persist_supported(int M, int N, int steps_per_split, int steps_per_group, int splits);
+void gemv_persist_set_warps(int w);
+int gemv_persist_launch(const gemv::GemvParams& p, int x_dtype, cudaStream_t stream);
 
 size_t prep_bytes(int M, int K) {  // prepared activations + step table, each rounded to 256 bytes
   const size_t xp = ((size_t)M * K * 2 + 255) / 256 * 256;
@@ -601,9 +528,9 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
                                : launch_generic<__nv_bfloat16>(p, packed, G, stream);
   }
   PARE_REQUIRE(aligned16(packed), PARE_ERR_ALIGN);
-  PARE_REQUIRE((size_t)(N + kTileRows - 1) / kTileRows < kStatusIndex, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE((size_t)(N + 15) / 16 < kStatusIndex, PARE_ERR_UNSUPPORTED);
   PARE_REQUIRE(pl.smem <= kSmemCap, PARE_ERR_UNSUPPORTED);
-  PARE_REQUIRE((pl.steps_per_split + pl.warps - 1) / pl.warps <= kMaxStepsPerWarp, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE((pl.steps_per_split + pl.warps - 1) / pl.warps <= kMaxStepsPerWarp / pl.rb, PARE_ERR_UNSUPPORTED);
   p.splits = pl.splits;
   p.steps_per_split = pl.steps_per_split;
   const size_t need = kCounterBytes + prep_bytes(M, K) + (pl.splits > 1 ? (size_t)pl.splits * M * N * sizeof(float) : 0);
@@ -629,13 +556,18 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
                                               : cudaLaunchKernelEx(&cfg, w4a16_prep_kernel<__nv_bfloat16>, p);
     if (e != cudaSuccess) return PARE_ERR_CUDA;
   }
-  // 2) the streaming kernel
+  // 2) the streaming kernel: persistent schedule for large layers at M <= 4, one tile per CTA otherwise
+  if (g_tune_persist >= 0 && gemv_persist_supported(M, N, pl.steps_per_split, G / 128, pl.splits))
+    return gemv_persist_launch(p, x_dtype, stream);
   return x_dtype == PARE_F16 ? dispatch_gemv<__half>(p, pl, stream) : dispatch_gemv<__nv_bfloat16>(p, pl, stream);
 }
 
 // Tuning override for experiments: columns per CTA (multiple of 512) and warps per CTA (4 or 8).
 void gemv_set_tuning(int rb, int kc, int warps) {
-  (void)rb;
+  g_tune_persist = rb < 0 ? -1 : 0;
+  gemv_persist_set_warps(warps == 8 ? 8 : 16);
+  if (rb < 0) rb = 0;
+  g_tune_rb = rb;
   g_tune_kc = kc;
   g_tune_warps = warps;
 }
