@@ -40,6 +40,12 @@ import torch  # noqa: E402
 METRIC = "decode_tok_s_llama3.1-8b_w4a16_kivi4"
 UNIT = "tok/s"
 FALLBACK_HBM_GBS = 6650.0
+# kernels of this library launched per decode block: 2 rmsnorm, 4 activation prep, 4 GEMV, attention, silu_mul
+# (the launch list also shows two torch copies per block that put the new K / V token into the cache)
+LAUNCHES_PER_BLOCK = 12
+# dram__bytes_read + dram__bytes_write of one gate|up GEMV launch (28672 x 4096, M = 1) from the ncu capture
+# summarised in profiles/w4a16_gemv_persist_gate_up_m1.md
+GATE_UP_DRAM_TRAFFIC = 66_100_000 + 540_000
 
 
 def parse_args():
@@ -53,6 +59,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--shape", default="llama-3.1-8b")
     ap.add_argument("--skip-layer-table", action="store_true")
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="for profiler captures: GPU work only")
     return ap.parse_args()
 
 
@@ -310,7 +317,7 @@ def run_ours(args) -> None:
         "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
         "e2e": {"value": args.batch * steps / sec_e2e, "unit": UNIT,
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
-        "gpu_launches": 8 * args.layers * steps,
+        "gpu_launches": LAUNCHES_PER_BLOCK * args.layers * steps,
         "clocks": clocks,
     }
     # bytes one step must move: all linears (algorithmic) + the cache
@@ -329,10 +336,14 @@ def run_ours(args) -> None:
         if key in table:
             achieved = table[key]["gbs"]
             line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                                "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_kind,
-                                "kernel": "w4a16_gemv_kernel (fused gate|up projection)",
+                                "frac": round(achieved / peak, 4),
+                                "traffic": GATE_UP_DRAM_TRAFFIC if (args.shape, args.batch) == ("llama-3.1-8b", 1) else None,
+                                "peak_source": peak_kind,
+                                "kernel": "w4a16_gemv_persist_kernel (fused gate|up projection)",
                                 "bytes_per_launch": w4a16_bytes(args.batch, blk.gate_up.out_features, blk.gate_up.in_features)}
         try:
+            if args.skip_cpu_baseline:
+                raise RuntimeError("skipped by --skip-cpu-baseline")
             csec, info = cpu_block_seconds(SHAPES[args.shape], args.batch, args.context, 3, 1)
             line["cpu_baseline"] = {"value": args.batch / (csec * args.layers), "unit": UNIT, **info}
         except Exception as exc:  # the CPU arm must never hide the GPU result
