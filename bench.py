@@ -40,9 +40,9 @@ import torch  # noqa: E402
 METRIC = "decode_tok_s_llama3.1-8b_w4a16_kivi4"
 UNIT = "tok/s"
 FALLBACK_HBM_GBS = 6650.0
-# kernels of this library launched per decode block: 2 rmsnorm, 4 activation prep, 4 GEMV, attention, silu_mul
-# (the launch list also shows two torch copies per block that put the new K / V token into the cache)
-LAUNCHES_PER_BLOCK = 12
+# kernels of this library launched per decode block: 2 rmsnorm, 4 GEMV, attention, silu_mul (activations travel
+# between them as prepared activations; the attention kernel appends the new K / V token itself)
+LAUNCHES_PER_BLOCK = 8
 # dram__bytes_read + dram__bytes_write of one gate|up GEMV launch (28672 x 4096, M = 1) from the ncu capture
 # summarised in profiles/w4a16_gemv_persist_gate_up_m1.md
 GATE_UP_DRAM_TRAFFIC = 66_100_000 + 540_000

@@ -89,6 +89,25 @@ int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx,
  * (reserved), columns per CTA (multiple of 512), warps per CTA (4 or 8); 0 = choose automatically. */
 void pare_w4a16_set_tuning(int reserved, int columns_per_cta, int warps_per_cta);
 
+/* ------------------------------------------------------------------------
+ * Prepared activations: the M <= 16 path of pare_w4a16_forward in two halves, so that the
+ * kernel which computes an activation (RMSNorm, SwiGLU, attention: below) can hand it to the
+ * next linear in the order the streaming kernel consumes it, and the per-call preparation
+ * launch disappears.  No counterpart in the reference (its Triton kernel reads x directly,
+ * pare/kernels/matmul_int4.py:99-131).  A prepared buffer is opaque, 16-byte aligned,
+ * pare_w4a16_prepared_bytes(M, K) bytes (0 if unsupported: M > 16 or K % 128 != 0), and tied to
+ * the activation dtype.  pare_w4a16_prepare fills one from a plain x (applying the act-order
+ * gather and the run-time input scale if given); pare_w4a16_forward_prepared is
+ * pare_w4a16_forward minus x / col_perm / input_scale and needs K % 512 == 0, group % 128 == 0
+ * (PARE_ERR_UNSUPPORTED otherwise: use the plain call). */
+size_t pare_w4a16_prepared_bytes(int M, int K);
+int pare_w4a16_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_perm, const float* input_scale,
+                       int M, int K, void* prepared, void* stream);
+int pare_w4a16_forward_prepared(const void* prepared, int x_dtype,
+                                const uint8_t* packed, const float* scale, const float* zero, const void* meta_h2,
+                                const void* bias, void* y, int64_t ldy, int M, int N, int K, int group_size,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
 
 /* ------------------------------------------------------------------------
  * KIVI quantized KV cache.  Replaces the eager primitives and the cache
@@ -136,7 +155,14 @@ int pare_kivi_dequant(const uint8_t* k_codes, const float* k_scale, const float*
  * (pare/kv_cache.py:183-186); this call gives the same result without materialising it.
  *   q, out        [B][Hq][D] dtype F16/BF16, element strides *_stride_b / *_stride_h
  *   res_k, res_v  [B][H][n_res][D] same dtype, element strides res_stride_b/h/t (multiples of 8)
- * D == 128, bits == 4 or 2.  workspace: pare_kivi_attn_workspace_bytes(), zero-filled once
+ *   new_k, new_v  NULL, or the newest token [B][H][D] (element strides new_stride_b/h, multiples
+ *                 of 8, 16-byte aligned): it is attended to as window position n_res-1 AND stored
+ *                 there by this call (the append of pare/kv_cache.py:229-231 for one token), so
+ *                 the caller copies nothing; positions 0..n_res-2 must already be in the window
+ *   out           may be NULL when prepared_out is given
+ *   prepared_out  NULL, or a pare_w4a16_prepared_bytes(B, Hq*D) buffer that receives the result as
+ *                 prepared activations of the next W4A16 linear (B <= 16)
+ * D == 128, bits == 4.  workspace: pare_kivi_attn_workspace_bytes(), zero-filled once
  * (same contract as the W4A16 workspace; one buffer may serve both). */
 size_t pare_kivi_attn_workspace_bytes(int B, int H, int n_comp, int n_res);
 
@@ -144,23 +170,27 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
                           const uint8_t* k_codes, const float* k_scale, const float* k_zero,
                           const uint8_t* v_codes, const float* v_scale, const float* v_zero,
                           int n_comp,
-                          const void* res_k, const void* res_v,
+                          void* res_k, void* res_v,
                           int64_t res_stride_b, int64_t res_stride_h, int64_t res_stride_t, int n_res,
-                          void* out, int64_t out_stride_b, int64_t out_stride_h,
+                          const void* new_k, const void* new_v, int64_t new_stride_b, int64_t new_stride_h,
+                          void* out, int64_t out_stride_b, int64_t out_stride_h, void* prepared_out,
                           float softmax_scale,
                           int B, int Hq, int H, int D, int bits, int group, int cap,
                           void* workspace, size_t workspace_bytes, void* stream);
 
-/* Tuning override for experiments: compressed tokens per CTA (multiple of 128, <= 1024); 0 = auto. */
+/* Tuning override for experiments: compressed tokens per CTA (multiple of 128, <= 512); 0 = auto. */
 void pare_kivi_attn_set_tuning(int chunk);
 
 /* ------------------------------------------------------------------------
  * Decode-step glue (no counterpart in the reference library: model code around the two hot
  * kernels).  y = rmsnorm(x + delta) * weight, optionally storing x + delta; and the SwiGLU
- * gate out = silu(gate) * up over a fused [rows][2n] gate|up projection.  dtype F16/BF16. */
+ * gate out = silu(gate) * up over a fused [rows][2n] gate|up projection.  dtype F16/BF16.
+ * prepared_out (NULL, or pare_w4a16_prepared_bytes(rows, n) bytes, rows <= 16, n % 128 == 0)
+ * receives the result as prepared activations of the next W4A16 linear; y / out may then be NULL. */
 int pare_rmsnorm_residual(const void* x, const void* delta, const void* weight, void* resid_out, void* y,
-                          int rows, int n, float eps, int dtype, void* stream);
-int pare_silu_mul(const void* gate_up, void* out, int rows, int n, int64_t ld, int dtype, void* stream);
+                          void* prepared_out, int rows, int n, float eps, int dtype, void* stream);
+int pare_silu_mul(const void* gate_up, void* out, void* prepared_out, int rows, int n, int64_t ld, int dtype,
+                  void* stream);
 
 /* ------------------------------------------------------------------------
  * W4A16 decode linear without any caller-provided workspace.  No counterpart in the reference;

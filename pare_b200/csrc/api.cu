@@ -1,12 +1,14 @@
 // extern "C" surface of libpare_b200: argument checks and dispatch only.
-#include "common.cuh"
+#include "prep.cuh"
 
 namespace pare {
 size_t gemv_workspace_bytes(int M, int N, int K, int G);
 int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale,
                  const float* zero, const void* meta_h2, const int32_t* col_perm, const float* input_scale,
                  const void* bias, void* y, int64_t ldy, int M, int N, int K, int G, void* workspace,
-                 size_t workspace_bytes, cudaStream_t stream);
+                 size_t workspace_bytes, cudaStream_t stream, const void* prepared);
+int gemv_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_perm, const float* input_scale, int M, int K,
+                 void* prepared, cudaStream_t stream);
 void gemv_set_tuning(int rb, int splits, int pf);
 bool gemm_supported(int M, int K, int G, const float* scale, const float* zero);
 size_t gemm_workspace_bytes(int M, int N, int K);
@@ -59,10 +61,34 @@ int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* p
     const int rc = pare::gemv_forward(reinterpret_cast<const unsigned char*>(x) + (size_t)m0 * ldx * esz, x_dtype, ldx,
                                       packed, scale, zero, meta_h2, col_perm, input_scale, bias,
                                       reinterpret_cast<unsigned char*>(y) + (size_t)m0 * ldy * esz, ldy, mc, N, K,
-                                      group_size, workspace, workspace_bytes, s);
+                                      group_size, workspace, workspace_bytes, s, nullptr);
     if (rc != PARE_OK) return rc;
   }
   return PARE_OK;
+}
+
+size_t pare_w4a16_prepared_bytes(int M, int K) {
+  if (M <= 0 || M > 16 || K <= 0 || K % 128) return 0;
+  return pare::prepared_bytes(M, K);
+}
+
+int pare_w4a16_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_perm, const float* input_scale, int M,
+                       int K, void* prepared, void* stream) {
+  PARE_REQUIRE(x && prepared && M > 0 && K > 0 && ldx >= K, PARE_ERR_SHAPE);
+  PARE_REQUIRE(x_dtype == PARE_F16 || x_dtype == PARE_BF16, PARE_ERR_DTYPE);
+  return pare::gemv_prepare(x, x_dtype, ldx, col_perm, input_scale, M, K, prepared, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int pare_w4a16_forward_prepared(const void* prepared, int x_dtype, const uint8_t* packed, const float* scale,
+                                const float* zero, const void* meta_h2, const void* bias, void* y, int64_t ldy, int M,
+                                int N, int K, int group_size, void* workspace, size_t workspace_bytes, void* stream) {
+  PARE_REQUIRE(M > 0 && N > 0 && K > 0 && group_size > 0, PARE_ERR_SHAPE);
+  PARE_REQUIRE((K % 2) == 0 && (K % group_size) == 0 && ldy >= N, PARE_ERR_SHAPE);
+  PARE_REQUIRE(M <= 16, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE(x_dtype == PARE_F16 || x_dtype == PARE_BF16, PARE_ERR_DTYPE);
+  PARE_REQUIRE(prepared && packed && y && (meta_h2 || (scale && zero)), PARE_ERR_SHAPE);
+  return pare::gemv_forward(nullptr, x_dtype, K, packed, scale, zero, meta_h2, nullptr, nullptr, bias, y, ldy, M, N, K,
+                            group_size, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream), prepared);
 }
 
 void pare_w4a16_set_tuning(int row_blocks, int k_splits, int prefetch) {

@@ -1,25 +1,34 @@
 // Elementwise glue between the two hot kernels of a decode step (RMSNorm with residual add,
 // SwiGLU gate).  Not part of the reference library (a caller's model code does these); they
 // exist so that a decode stack can be chained and captured in a CUDA graph without leaving
-// this library.  One CTA per activation row.
+// this library.  Both can write their result directly as prepared activations of the next
+// W4A16 linear (prep.cuh), which saves that linear's activation-prep launch.
 
-#include "common.cuh"
+#include "prep.cuh"
 
 namespace pare {
 namespace {
 
 // Each thread keeps its elements in registers (8 per 16-byte vector, up to kVecs vectors), so the
-// row is read once and all loads are in flight together; n must be a multiple of 8.
+// row is read once and all loads are in flight together; n must be a multiple of 8.  One CTA per row.
 constexpr int kNormThreads = 256;
 constexpr int kVecs = 8;  // rows up to 256 * 8 * 8 = 16384 elements
 
 template <typename T>
 __global__ void __launch_bounds__(kNormThreads) rmsnorm_residual_kernel(const T* __restrict__ x, const T* __restrict__ delta,
                                                                         const T* __restrict__ weight, T* resid_out,
-                                                                        T* __restrict__ y, int n, float eps) {
-  pdl_wait();
+                                                                        T* __restrict__ y, T* __restrict__ prep_xp,
+                                                                        float2* __restrict__ prep_tab, int n, float eps) {
+  pdl_launch_dependents();
   const size_t row = (size_t)blockIdx.x * n;
   const int nvec = n >> 3;
+  uint4 wv[kVecs];   // the norm weights do not depend on the previous kernel
+#pragma unroll
+  for (int j = 0; j < kVecs; ++j) {
+    const int v = threadIdx.x + j * kNormThreads;
+    if (v < nvec) wv[j] = *reinterpret_cast<const uint4*>(weight + v * 8);
+  }
+  pdl_wait();
   uint4 xv[kVecs], dv[kVecs];
 #pragma unroll
   for (int j = 0; j < kVecs; ++j) {
@@ -61,28 +70,108 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_residual_kernel(const T*
 #pragma unroll
   for (int j = 0; j < kVecs; ++j) {
     const int v = threadIdx.x + j * kNormThreads;
-    if (v < nvec) {
-      const uint4 wv = *reinterpret_cast<const uint4*>(weight + v * 8);
-      const T* we = reinterpret_cast<const T*>(&wv);
+    const bool live = v < nvec;
+    float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (live) {
+      const T* we = reinterpret_cast<const T*>(&wv[j]);
       const T* xe = reinterpret_cast<const T*>(&xv[j]);
-      uint4 ov;
-      T* oe = reinterpret_cast<T*>(&ov);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) oe[e] = from_float<T>(to_float<T>(xe[e]) * inv * to_float<T>(we[e]));
-      *reinterpret_cast<uint4*>(y + row + v * 8) = ov;
+      for (int e = 0; e < 8; ++e) o[e] = to_float<T>(xe[e]) * inv * to_float<T>(we[e]);
+      if (y) {
+        uint4 ov;
+        T* oe = reinterpret_cast<T*>(&ov);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) oe[e] = from_float<T>(o[e]);
+        *reinterpret_cast<uint4*>(y + row + v * 8) = ov;
+      }
+    }
+    if (prep_xp) {   // n % 128 == 0: the sixteen lanes of a step are live or idle together
+      const int st = v >> 4, c = v & 15;
+      float lo = 0.f, hi = 0.f;
+      if (live) prep_chunk8<T>(o, prep_xp + row + st * 128, c, lo, hi);
+      lo = half_warp_sum(lo);
+      hi = half_warp_sum(hi);
+      if (live && c == 0) prep_tab[(size_t)st * gemv::kTabCols + blockIdx.x] = prep_tab_entry<T>(lo, hi);
     }
   }
 }
 
+// thread = 8 columns of one row
 template <typename T>
-__global__ void silu_mul_kernel(const T* gate_up, T* out, int n, int64_t ld) {
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out,
+                                                       T* __restrict__ prep_xp, float2* __restrict__ prep_tab, int n,
+                                                       int64_t ld, int vec_ok) {
+  pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.y;
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  const float g = to_float<T>(gate_up[(size_t)row * ld + i]);
-  const float u = to_float<T>(gate_up[(size_t)row * ld + n + i]);
-  out[(size_t)row * n + i] = from_float<T>(g / (1.f + __expf(-g)) * u);
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = v * 8 < n;
+  float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (live) {
+    const T* g = gate_up + (size_t)row * ld + v * 8;
+    uint4 gv, uv;
+    if (vec_ok) {
+      gv = *reinterpret_cast<const uint4*>(g);
+      uv = *reinterpret_cast<const uint4*>(g + n);
+    } else {
+      T* ge = reinterpret_cast<T*>(&gv);
+      T* ue = reinterpret_cast<T*>(&uv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const bool in = v * 8 + e < n;
+        ge[e] = in ? g[e] : from_float<T>(0.f);
+        ue[e] = in ? g[n + e] : from_float<T>(0.f);
+      }
+    }
+    const T* ge = reinterpret_cast<const T*>(&gv);
+    const T* ue = reinterpret_cast<const T*>(&uv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float a = to_float<T>(ge[e]);
+      o[e] = a / (1.f + __expf(-a)) * to_float<T>(ue[e]);
+    }
+    if (out) {
+      T* dst = out + (size_t)row * n + v * 8;
+      if (vec_ok) {
+        uint4 ov;
+        T* oe = reinterpret_cast<T*>(&ov);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) oe[e] = from_float<T>(o[e]);
+        *reinterpret_cast<uint4*>(dst) = ov;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (v * 8 + e < n) dst[e] = from_float<T>(o[e]);
+      }
+    }
+  }
+  if (prep_xp) {   // n % 128 == 0
+    const int st = v >> 4, c = v & 15;
+    float lo = 0.f, hi = 0.f;
+    if (live) prep_chunk8<T>(o, prep_xp + (size_t)row * n + st * 128, c, lo, hi);
+    lo = half_warp_sum(lo);
+    hi = half_warp_sum(hi);
+    if (live && c == 0) prep_tab[(size_t)st * gemv::kTabCols + row] = prep_tab_entry<T>(lo, hi);
+  }
+}
+
+template <typename T>
+int rmsnorm_launch(const void* x, const void* delta, const void* weight, void* resid_out, void* y, void* prepared, int rows,
+                   int n, float eps, cudaStream_t s) {
+  T* xp = reinterpret_cast<T*>(prepared);
+  float2* tab = prepared ? reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(prepared) + prepared_tab_offset(rows, n)) : nullptr;
+  return launch_pdl(rmsnorm_residual_kernel<T>, dim3(rows), dim3(kNormThreads), 0, s, (const T*)x, (const T*)delta,
+                    (const T*)weight, (T*)resid_out, (T*)y, xp, tab, n, eps);
+}
+
+template <typename T>
+int silu_launch(const void* gate_up, void* out, void* prepared, int rows, int n, int64_t ld, cudaStream_t s) {
+  T* xp = reinterpret_cast<T*>(prepared);
+  float2* tab = prepared ? reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(prepared) + prepared_tab_offset(rows, n)) : nullptr;
+  const int vec_ok = (n % 8 == 0) && (ld % 8 == 0) && aligned16(gate_up) && (out == nullptr || aligned16(out));
+  const int nvec = (n + 7) / 8;
+  return launch_pdl(silu_mul_kernel<T>, dim3((nvec + 255) / 256, rows), dim3(256), 0, s, (const T*)gate_up, (T*)out, xp, tab,
+                    n, ld, vec_ok);
 }
 
 }  // namespace
@@ -92,35 +181,30 @@ extern "C" {
 
 // y = rmsnorm(x + delta) * weight; optionally stores x + delta (the new residual stream).
 // x, delta (may be NULL), resid_out (may be NULL, may alias x), y: [rows][n]; weight [n].
-int pare_rmsnorm_residual(const void* x, const void* delta, const void* weight, void* resid_out, void* y, int rows,
-                          int n, float eps, int dtype, void* stream) {
-  PARE_REQUIRE(x && weight && y && rows > 0 && n > 0, PARE_ERR_SHAPE);
+// prepared_out (may be NULL; then y must not be): the result as prepared activations of a W4A16 linear with K = n.
+int pare_rmsnorm_residual(const void* x, const void* delta, const void* weight, void* resid_out, void* y,
+                          void* prepared_out, int rows, int n, float eps, int dtype, void* stream) {
+  PARE_REQUIRE(x && weight && (y || prepared_out) && rows > 0 && n > 0, PARE_ERR_SHAPE);
   PARE_REQUIRE(n % 8 == 0 && n <= pare::kNormThreads * pare::kVecs * 8, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE(prepared_out == nullptr || (n % 128 == 0 && rows <= pare::gemv::kTabCols && pare::aligned16(prepared_out)),
+               PARE_ERR_UNSUPPORTED);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (dtype == PARE_F16)
-    pare::rmsnorm_residual_kernel<__half><<<rows, 256, 0, s>>>((const __half*)x, (const __half*)delta, (const __half*)weight,
-                                                               (__half*)resid_out, (__half*)y, n, eps);
-  else if (dtype == PARE_BF16)
-    pare::rmsnorm_residual_kernel<__nv_bfloat16><<<rows, 256, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)delta,
-                                                                      (const __nv_bfloat16*)weight, (__nv_bfloat16*)resid_out,
-                                                                      (__nv_bfloat16*)y, n, eps);
-  else
-    return PARE_ERR_DTYPE;
-  return pare::launch_status();
+  if (dtype == PARE_F16) return pare::rmsnorm_launch<__half>(x, delta, weight, resid_out, y, prepared_out, rows, n, eps, s);
+  if (dtype == PARE_BF16) return pare::rmsnorm_launch<__nv_bfloat16>(x, delta, weight, resid_out, y, prepared_out, rows, n, eps, s);
+  return PARE_ERR_DTYPE;
 }
 
 // out[r][i] = silu(gate_up[r][i]) * gate_up[r][n + i]; gate_up rows have leading dimension ld >= 2n.
-int pare_silu_mul(const void* gate_up, void* out, int rows, int n, int64_t ld, int dtype, void* stream) {
-  PARE_REQUIRE(gate_up && out && rows > 0 && n > 0 && ld >= 2 * (int64_t)n, PARE_ERR_SHAPE);
+// prepared_out (may be NULL; then out must not be): the result as prepared activations of a W4A16 linear with K = n.
+int pare_silu_mul(const void* gate_up, void* out, void* prepared_out, int rows, int n, int64_t ld, int dtype, void* stream) {
+  PARE_REQUIRE(gate_up && (out || prepared_out) && rows > 0 && n > 0 && ld >= 2 * (int64_t)n, PARE_ERR_SHAPE);
+  PARE_REQUIRE(prepared_out == nullptr ||
+                   (n % 128 == 0 && ld % 8 == 0 && rows <= pare::gemv::kTabCols && pare::aligned16(prepared_out) && pare::aligned16(gate_up)),
+               PARE_ERR_UNSUPPORTED);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const dim3 grid((n + 255) / 256, rows);
-  if (dtype == PARE_F16)
-    pare::silu_mul_kernel<__half><<<grid, 256, 0, s>>>((const __half*)gate_up, (__half*)out, n, ld);
-  else if (dtype == PARE_BF16)
-    pare::silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, n, ld);
-  else
-    return PARE_ERR_DTYPE;
-  return pare::launch_status();
+  if (dtype == PARE_F16) return pare::silu_launch<__half>(gate_up, out, prepared_out, rows, n, ld, s);
+  if (dtype == PARE_BF16) return pare::silu_launch<__nv_bfloat16>(gate_up, out, prepared_out, rows, n, ld, s);
+  return PARE_ERR_DTYPE;
 }
 
 }  // extern "C"

@@ -15,42 +15,70 @@
 // once for all of them.
 //
 // Grid: (splits, kv heads, batch).  Each split owns a chunk of compressed tokens (split-KV
-// for long contexts); one extra split owns the full-precision residual window.  Phases of a
-// CTA: (A) scores of its chunk into shared memory, (B) softmax statistics and scaled
-// probabilities in operand order (warp-shuffle reductions), (C) P.V with the V codes as the
-// MMA A operand.  Partial (max, sum, O) go to a workspace; the CTA that arrives last at the
-// per-(batch, head) counter merges them in split order and resets the counter.
+// for long contexts) or up to 64 tokens of the full-precision residual window.  A CTA first
+// puts everything it will read into shared memory with a handful of bulk async copies on one
+// mbarrier (codes, scales and zeros of a chunk are contiguous in the cache layout), so the
+// phases that follow never wait on global memory: (A) scores of its chunk, (B) softmax
+// statistics and scaled probabilities in operand order (warp-shuffle reductions), (C) P.V with
+// the V codes as the MMA A operand.  Partial (max, sum, O) go to a workspace; the CTA that
+// arrives last at the per-(batch, head) counter merges them in split order and resets the counter.
+//
+// Launched with programmatic stream serialization: the compressed cache of this step is
+// immutable, so its copies are issued before griddepcontrol.wait and overlap the tail of the
+// kernel that produces q; the residual window and q are read after the wait.  The newest
+// token can be handed in separately (new_k / new_v, e.g. straight out of the q|k|v projection):
+// the CTA that owns the last window position attends to it and stores it into the window.
+//
+// The merged output can also be written as prepared activations of the next W4A16 linear
+// (operand order + per-step sums, see prep.cuh): head h is exactly one 128-column step.
 
-#include "common.cuh"
+#include "gemv_common.cuh"
+#include "prep.cuh"
 
 namespace pare {
 namespace {
+
+using gemv::bulk_load;
+using gemv::kStatusIndex;
+using gemv::mbar_expect_tx;
+using gemv::mbar_init;
+using gemv::mbar_wait;
+using gemv::smem_u32;
 
 constexpr int kAttnWarps = 8;
 constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kD = 128;
 constexpr int kHeads = 8;
-constexpr int kMaxChunk = 1024;
+constexpr int kMaxChunk = 512;
+constexpr int kResChunk = 64;            // residual tokens per split
+constexpr int kResPitch = 320;           // bytes per staged residual row (256 + 64: conflict-free 16-byte reads down a column)
 constexpr int kMaxResidual = 512;
-constexpr size_t kCounterInts = 16384;
-constexpr size_t kCounterBytes = kCounterInts * sizeof(int);
+constexpr size_t kCounterInts = gemv::kCounterInts;
+constexpr size_t kCounterBytes = gemv::kCounterBytes;
+constexpr size_t kAttnSmemCap = 200 * 1024;
 constexpr float kNegBig = -1e30f;
 
 struct AttnParams {
   const void* q;
   int64_t q_sb, q_sh;
+  int q_vec;           // q rows can be read as 16-byte vectors
   const uint8_t* k_codes;
   const float* k_scale;
   const float* k_zero;
   const uint8_t* v_codes;
   const float* v_scale;
   const float* v_zero;
-  const void* res_k;
-  const void* res_v;
+  void* res_k;
+  void* res_v;
   int64_t r_sb, r_sh, r_st;
   int n_res;
-  void* out;
+  const void* new_k;   // newest token [B][H][D] (may be NULL: the window already holds all n_res tokens)
+  const void* new_v;
+  int64_t n_sb, n_sh;
+  void* out;           // may be NULL when prep_xp is given
   int64_t o_sb, o_sh;
+  void* prep_xp;       // prepared activations [B][Hq * 128] + table, or NULL
+  float2* prep_tab;
   float sm_scale;
   int B, Hq, H, rep, group, cap, n_comp;
   int chunk, n_csplit, n_split;
@@ -83,60 +111,146 @@ __device__ __forceinline__ uint32_t pair_to_h2<__nv_bfloat16>(uint32_t raw) {
   return h2_bits(__uint_as_float(raw << 16), __uint_as_float(raw & 0xffff0000u));
 }
 
+__device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// bytes of the operand stage of a compressed split
+__host__ __device__ inline int stage_bytes(int chunk, int group) {
+  return chunk * 64 + 2 * (chunk / group) * kD * 4 + (chunk / 128) * kD * 64 + 2 * chunk * 4;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const AttnParams p) {
-  extern __shared__ __align__(16) unsigned char smem[];
+  extern __shared__ __align__(128) unsigned char smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const size_t bh = (size_t)b * p.H + h;
   const bool is_res = (split >= p.n_csplit);
 
-  float* qf = reinterpret_cast<float*>(smem);                       // [8][128]
+  // header: mbarrier, flags, statistics | q fp32 | scores | probabilities (hi, lo) | operand stage
+  uint64_t* bar_p = reinterpret_cast<uint64_t*>(smem);
+  int* s_last = reinterpret_cast<int*>(smem + 8);
+  float* st_m = reinterpret_cast<float*>(smem + 16);                // [8]
+  float* st_l = st_m + kHeads;
+  float* st_c = st_l + kHeads;
+  float* qf = reinterpret_cast<float*>(smem + 128);                 // [8][128]
   float* S = qf + kHeads * kD;                                      // [8][s_stride]
   unsigned char* P = reinterpret_cast<unsigned char*>(S + kHeads * p.s_stride);  // [8][p_stride] fp16 hi parts
   unsigned char* P2 = P + kHeads * p.p_stride;                                   // [8][p_stride] fp16 lo parts
-  float* st_m = reinterpret_cast<float*>(P2 + kHeads * p.p_stride);  // [8]
-  float* st_l = st_m + kHeads;
-  float* st_c = st_l + kHeads;
+  unsigned char* stage = P2 + kHeads * p.p_stride;   // 128-byte aligned by construction of the strides
+  const uint32_t bar = smem_u32(bar_p);
+  int* status = p.counters + kStatusIndex;
+
+  int valid;           // tokens this CTA attends to
+  int chunk_start = 0;
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  // operand stage of a compressed split
+  const int ngr_full = p.chunk / p.group;
+  unsigned char* kc_s = stage;
+  float* ks_s = reinterpret_cast<float*>(kc_s + p.chunk * 64);
+  float* kz_s = ks_s + ngr_full * kD;
+  unsigned char* vc_s = reinterpret_cast<unsigned char*>(kz_s + ngr_full * kD);
+  float* vs_s = reinterpret_cast<float*>(vc_s + (p.chunk / 128) * kD * 64);
+  float* vz_s = vs_s + p.chunk;
+
+  if (!is_res) {
+    chunk_start = split * p.chunk;
+    valid = min(p.chunk, p.n_comp - chunk_start);
+    if (threadIdx.x == 0) {
+      // the compressed cache does not change during a decode step: fetch before the dependency wait
+      const int ngroups = valid / p.group, nblk = (valid + 127) >> 7;
+      const size_t grow = bh * (p.cap / p.group) + chunk_start / p.group;
+      mbar_expect_tx(bar, valid * 64 + 2 * ngroups * kD * 4 + nblk * kD * 64 + 2 * valid * 4);
+      bulk_load(smem_u32(kc_s), p.k_codes + (bh * p.cap + chunk_start) * 64, valid * 64, bar);
+      bulk_load(smem_u32(ks_s), p.k_scale + grow * kD, ngroups * kD * 4, bar);
+      bulk_load(smem_u32(kz_s), p.k_zero + grow * kD, ngroups * kD * 4, bar);
+      bulk_load(smem_u32(vc_s), p.v_codes + (bh * (p.cap / 128) + (chunk_start >> 7)) * (size_t)(kD * 64), nblk * kD * 64, bar);
+      bulk_load(smem_u32(vs_s), p.v_scale + bh * p.cap + chunk_start, valid * 4, bar);
+      bulk_load(smem_u32(vz_s), p.v_zero + bh * p.cap + chunk_start, valid * 4, bar);
+    }
+  }
+  pdl_wait();   // q, the newest token and the residual window may come from the previous kernels
+
+  unsigned char* rk_s = stage;
+  unsigned char* rv_s = stage + kResChunk * kResPitch;
+  if (is_res) {
+    chunk_start = (split - p.n_csplit) * kResChunk;
+    valid = min(kResChunk, p.n_res - chunk_start);
+    T* rk = reinterpret_cast<T*>(p.res_k) + (int64_t)b * p.r_sb + (int64_t)h * p.r_sh;
+    T* rv = reinterpret_cast<T*>(p.res_v) + (int64_t)b * p.r_sb + (int64_t)h * p.r_sh;
+    // the newest token, if handed in separately, is the last window position
+    const bool has_new = p.new_k != nullptr && chunk_start + valid == p.n_res;
+    const int ncopy = has_new ? valid - 1 : valid;
+    if (warp == 0) {
+      if (lane == 0) mbar_expect_tx(bar, ncopy * 2 * kD * (int)sizeof(T));
+      __syncwarp();
+      for (int i = lane; i < ncopy; i += 32) {
+        bulk_load(smem_u32(rk_s + i * kResPitch), rk + (int64_t)(chunk_start + i) * p.r_st, kD * sizeof(T), bar);
+        bulk_load(smem_u32(rv_s + i * kResPitch), rv + (int64_t)(chunk_start + i) * p.r_st, kD * sizeof(T), bar);
+      }
+    } else if (warp == 1 && has_new) {
+      const bool is_v = lane >= 16;
+      const int part = lane & 15;   // 16 bytes each
+      const T* src = reinterpret_cast<const T*>(is_v ? p.new_v : p.new_k) + (int64_t)b * p.n_sb + (int64_t)h * p.n_sh;
+      const uint4 val = *reinterpret_cast<const uint4*>(src + part * 8);
+      *reinterpret_cast<uint4*>((is_v ? rv_s : rk_s) + (valid - 1) * kResPitch + part * 16) = val;
+      *reinterpret_cast<uint4*>((is_v ? rv : rk) + (int64_t)(p.n_res - 1) * p.r_st + part * 8) = val;
+    }
+  }
 
   // ---- query rows of this KV head as fp32 (rows >= rep are zero) ----
   {
     const T* qg = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_sb + (int64_t)h * p.rep * p.q_sh;
-    for (int i = threadIdx.x; i < kHeads * kD; i += kAttnThreads) {
-      const int hh = i >> 7, c = i & 127;
-      qf[i] = hh < p.rep ? to_float<T>(qg[(int64_t)hh * p.q_sh + c]) : 0.f;
+    for (int i = threadIdx.x; i < kHeads * (kD / 8); i += kAttnThreads) {
+      const int hh = i >> 4, c8 = (i & 15) * 8;
+      float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
+      if (hh < p.rep) {
+        uint4 raw;
+        if (p.q_vec) {
+          raw = *reinterpret_cast<const uint4*>(qg + (int64_t)hh * p.q_sh + c8);
+        } else {
+          T* r = reinterpret_cast<T*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) r[j] = qg[(int64_t)hh * p.q_sh + c8 + j];
+        }
+        const T* e = reinterpret_cast<const T*>(&raw);
+        lo4 = make_float4(to_float<T>(e[0]), to_float<T>(e[1]), to_float<T>(e[2]), to_float<T>(e[3]));
+        hi4 = make_float4(to_float<T>(e[4]), to_float<T>(e[5]), to_float<T>(e[6]), to_float<T>(e[7]));
+      }
+      *reinterpret_cast<float4*>(qf + hh * kD + c8) = lo4;
+      *reinterpret_cast<float4*>(qf + hh * kD + c8 + 4) = hi4;
     }
   }
   __syncthreads();
+  mbar_wait(bar, 0, status);   // bounded; a timeout is reported through the status word
 
-  int valid;   // tokens this CTA attends to
   float o_acc[4] = {0.f, 0.f, 0.f, 0.f};   // phase C result, layout depends on the branch
 
   if (!is_res) {
-    const int chunk_start = split * p.chunk;
-    valid = min(p.chunk, p.n_comp - chunk_start);
     const int G = p.group;
     const int ngroups = valid / G;
-    const int gbase = chunk_start / G;
 
     // ================= phase A: scores =================
     for (int gl = warp; gl < ngroups; gl += kAttnWarps) {
-      const int tok0 = chunk_start + gl * G;
-      // issue the code loads of the whole group first (up to 8 tiles of 16 tokens)
-      const uint8_t* krow = p.k_codes + (bh * p.cap + tok0) * 64 + tig * 16;
-      const float* ks = p.k_scale + (bh * (p.cap / G) + gbase + gl) * kD + tig * 32;
-      const float* kz = p.k_zero + (bh * (p.cap / G) + gbase + gl) * kD + tig * 32;
+      const unsigned char* krow = kc_s + (gl * G) * 64 + tig * 16;
+      const float* ks = ks_s + gl * kD + tig * 32;
+      const float* kz = kz_s + gl * kD + tig * 32;
       // q * scale as a two-term fp16 expansion (hi + lo, ~22 bits): a single fp16 rounding of
       // this operand would move the logits by more than the reference's own fp16 cast of K^
       uint32_t xh[4][4], xl[4][4];
       float bias = 0.f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float4 s0 = __ldg(reinterpret_cast<const float4*>(ks + i * 8));
-        const float4 s1 = __ldg(reinterpret_cast<const float4*>(ks + i * 8 + 4));
-        const float4 z0 = __ldg(reinterpret_cast<const float4*>(kz + i * 8));
-        const float4 z1 = __ldg(reinterpret_cast<const float4*>(kz + i * 8 + 4));
+        const float4 s0 = *reinterpret_cast<const float4*>(ks + i * 8);
+        const float4 s1 = *reinterpret_cast<const float4*>(ks + i * 8 + 4);
+        const float4 z0 = *reinterpret_cast<const float4*>(kz + i * 8);
+        const float4 z1 = *reinterpret_cast<const float4*>(kz + i * 8 + 4);
         const float4 q0 = *reinterpret_cast<const float4*>(qf + gid * kD + tig * 32 + i * 8);
         const float4 q1 = *reinterpret_cast<const float4*>(qf + gid * kD + tig * 32 + i * 8 + 4);
         bias = fmaf(q0.x, z0.x, bias); bias = fmaf(q0.y, z0.y, bias); bias = fmaf(q0.z, z0.z, bias); bias = fmaf(q0.w, z0.w, bias);
@@ -153,8 +267,8 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       const float c1 = __shfl_sync(0xffffffffu, bias, (tig * 2 + 1) * 4);
 
       for (int tile = 0; tile < G / 16; ++tile) {
-        const uint4 wa4 = ld_stream_v4(krow + (size_t)(tile * 16 + gid) * 64);
-        const uint4 wb4 = ld_stream_v4(krow + (size_t)(tile * 16 + gid + 8) * 64);
+        const uint4 wa4 = *reinterpret_cast<const uint4*>(krow + (tile * 16 + gid) * 64);
+        const uint4 wb4 = *reinterpret_cast<const uint4*>(krow + (tile * 16 + gid + 8) * 64);
         const uint32_t wa[4] = {wa4.x, wa4.y, wa4.z, wa4.w};
         const uint32_t wb[4] = {wb4.x, wb4.y, wb4.z, wb4.w};
         float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -188,15 +302,13 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       m = warp_max(m);
       float l = 0.f, z = 0.f;
       unsigned char* prow = P + warp * p.p_stride;
-      const float* vs = p.v_scale + bh * p.cap + chunk_start;
-      const float* vz = p.v_zero + bh * p.cap + chunk_start;
       for (int t = lane; t < nblk * 128; t += 32) {
         float pv = 0.f;
         if (t < valid) {
           const float e = __expf(srow[t] - m);
           l += e;
-          const float sc = __ldg(vs + t);
-          z = fmaf(e, fmaf(8.f, sc, __ldg(vz + t)), z);   // value codes are centred at 8 in phase C
+          const float sc = vs_s[t];
+          z = fmaf(e, fmaf(8.f, sc, vz_s[t]), z);   // value codes are centred at 8 in phase C
           pv = e * sc;
         }
         // operand layout of a 128-token block: [word 0..3][quad 0..3] chunks of 8 halves, slots 0,4,1,5,2,6,3,7
@@ -221,16 +333,13 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
     // ================= phase C: O^T[c][h] = sum_t code_v[t][c] * P'[t][h] =================
     {
       const int row = warp * 16 + gid;  // channel
-      const uint8_t* vbase = p.v_codes + ((bh * (p.cap / 128) + (chunk_start >> 7)) * kD + row) * 64 + tig * 16;
+      const unsigned char* vbase = vc_s + row * 64 + tig * 16;
       float o0[4] = {0.f, 0.f, 0.f, 0.f}, o1[4] = {0.f, 0.f, 0.f, 0.f};
-      uint4 va = ld_stream_v4(vbase), vb = ld_stream_v4(vbase + 8 * 64);
       for (int blk = 0; blk < nblk; ++blk) {
+        const uint4 va = *reinterpret_cast<const uint4*>(vbase + blk * (kD * 64));
+        const uint4 vb = *reinterpret_cast<const uint4*>(vbase + blk * (kD * 64) + 8 * 64);
         const uint32_t wa[4] = {va.x, va.y, va.z, va.w};
         const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
-        if (blk + 1 < nblk) {
-          va = ld_stream_v4(vbase + (size_t)(blk + 1) * kD * 64);
-          vb = ld_stream_v4(vbase + (size_t)(blk + 1) * kD * 64 + 8 * 64);
-        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           uint4 pf = make_uint4(0u, 0u, 0u, 0u), pl = make_uint4(0u, 0u, 0u, 0u);
@@ -261,18 +370,15 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       }
     }
   } else {
-    // ================= residual window: dense fp16/bf16 tokens =================
-    valid = p.n_res;
-    const T* rk = reinterpret_cast<const T*>(p.res_k) + (int64_t)b * p.r_sb + (int64_t)h * p.r_sh;
-    const T* rv = reinterpret_cast<const T*>(p.res_v) + (int64_t)b * p.r_sb + (int64_t)h * p.r_sh;
+    // ================= residual window: dense fp16/bf16 tokens from the stage =================
     for (int tile = warp; tile * 16 < valid; tile += kAttnWarps) {
       const int tA = min(tile * 16 + gid, valid - 1), tB = min(tile * 16 + gid + 8, valid - 1);
       float d0[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int c0 = (j * 4 + tig) * 8;
-        const uint4 ka = *reinterpret_cast<const uint4*>(rk + (int64_t)tA * p.r_st + c0);
-        const uint4 kb = *reinterpret_cast<const uint4*>(rk + (int64_t)tB * p.r_st + c0);
+        const uint4 ka = *reinterpret_cast<const uint4*>(rk_s + tA * kResPitch + c0 * 2);
+        const uint4 kb = *reinterpret_cast<const uint4*>(rk_s + tB * kResPitch + c0 * 2);
         const float4 q0 = *reinterpret_cast<const float4*>(qf + gid * kD + c0);
         const float4 q1 = *reinterpret_cast<const float4*>(qf + gid * kD + c0 + 4);
         mma16816<__half>(d0, pair_to_h2<T>(ka.x), pair_to_h2<T>(kb.x), pair_to_h2<T>(ka.y), pair_to_h2<T>(kb.y),
@@ -317,7 +423,7 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
 #pragma unroll
       for (int hh = 0; hh < kHeads; ++hh) acc[hh] = 0.f;
       for (int t = tb; t < te; ++t) {
-        const float v = to_float<T>(rv[(int64_t)t * p.r_st + c]);
+        const float v = to_float<T>(*reinterpret_cast<const T*>(rv_s + t * kResPitch + c * 2));
 #pragma unroll
         for (int hh = 0; hh < kHeads; ++hh) acc[hh] = fmaf(S[hh * p.s_stride + t], v, acc[hh]);
       }
@@ -343,38 +449,117 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
   // ================= merge of the splits by the last CTA of this (batch, head) =================
   __threadfence();
   __syncthreads();
-  __shared__ int s_last;
-  if (threadIdx.x == 0) s_last = (atomicAdd(p.counters + bh, 1) == p.n_split - 1);
+  if (threadIdx.x == 0) *s_last = (atomicAdd(p.counters + bh, 1) == p.n_split - 1);
   __syncthreads();
-  if (!s_last) return;
+  if (!*s_last) return;
   __threadfence();
-  T* og = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_sb + (int64_t)h * p.rep * p.o_sh;
   const float* pm = p.part_ml + bh * p.n_split * (size_t)(kHeads * 2);
   const float* po = p.part_o + bh * p.n_split * (size_t)(kHeads * kD);
-  for (int i = threadIdx.x; i < p.rep * kD; i += kAttnThreads) {
-    const int hh = i >> 7, c = i & 127;
+  // statistics of all splits -> shared memory (one load per thread), then weights per (split, head)
+  float* w_s = reinterpret_cast<float*>(stage);   // [n_split][8]: max, then weight (the operand stage is free by now)
+  float* l_s = w_s + p.n_split * kHeads;          // [n_split][8]: sum
+  for (int i = threadIdx.x; i < p.n_split * kHeads; i += kAttnThreads) {
+    const int hh = i & 7;
+    w_s[i] = hh < p.rep ? __ldcg(pm + i * 2) : kNegBig;
+    l_s[i] = hh < p.rep ? __ldcg(pm + i * 2 + 1) : 0.f;
+  }
+  __syncthreads();
+  if (threadIdx.x < kHeads) {
+    const int hh = threadIdx.x;
     float M = kNegBig;
-    for (int s = 0; s < p.n_split; ++s) M = fmaxf(M, __ldcg(pm + (s * kHeads + hh) * 2));
-    float L = 0.f, acc = 0.f;
+    for (int s = 0; s < p.n_split; ++s) M = fmaxf(M, w_s[s * kHeads + hh]);
+    float L = 0.f;
     for (int s = 0; s < p.n_split; ++s) {
-      const float w = __expf(__ldcg(pm + (s * kHeads + hh) * 2) - M);
-      L = fmaf(w, __ldcg(pm + (s * kHeads + hh) * 2 + 1), L);
-      acc = fmaf(w, __ldcg(po + (size_t)s * (kHeads * kD) + hh * kD + c), acc);
+      const float w = __expf(w_s[s * kHeads + hh] - M);
+      w_s[s * kHeads + hh] = w;
+      L = fmaf(w, l_s[s * kHeads + hh], L);
     }
-    og[(int64_t)hh * p.o_sh + c] = from_float<T>(acc / L);
+    st_l[hh] = L;
+  }
+  __syncthreads();
+  {
+    // thread = (head, 8 channels); all threads run the loop so the half-warp sums below are whole
+    const int hh = threadIdx.x >> 4, c = threadIdx.x & 15;
+    const bool active = hh < p.rep;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (active) {
+      const float* src = po + hh * kD + c * 8;
+#pragma unroll 4
+      for (int s = 0; s < p.n_split; ++s) {
+        const float w = w_s[s * kHeads + hh];
+        const float4 a0 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)s * (kHeads * kD)));
+        const float4 a1 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)s * (kHeads * kD) + 4));
+        acc[0] = fmaf(w, a0.x, acc[0]); acc[1] = fmaf(w, a0.y, acc[1]); acc[2] = fmaf(w, a0.z, acc[2]); acc[3] = fmaf(w, a0.w, acc[3]);
+        acc[4] = fmaf(w, a1.x, acc[4]); acc[5] = fmaf(w, a1.y, acc[5]); acc[6] = fmaf(w, a1.z, acc[6]); acc[7] = fmaf(w, a1.w, acc[7]);
+      }
+      const float L = st_l[hh];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = acc[e] / L;
+    }
+    if (active && p.out) {
+      T* og = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_sb + (int64_t)(h * p.rep + hh) * p.o_sh + c * 8;
+      uint4 ov;
+      T* oe = reinterpret_cast<T*>(&ov);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) oe[e] = from_float<T>(acc[e]);
+      if (p.o_sh % 8 == 0 && p.o_sb % 8 == 0 && aligned16_dev(p.out)) {
+        *reinterpret_cast<uint4*>(og) = ov;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) og[e] = oe[e];
+      }
+    }
+    if (p.prep_xp) {
+      // query head (h * rep + hh) is step (h * rep + hh) of activation row b of the next linear
+      const int K = p.Hq * kD, st = h * p.rep + hh;
+      float lo = 0.f, hi = 0.f;
+      if (active) prep_chunk8<T>(acc, reinterpret_cast<T*>(p.prep_xp) + (size_t)b * K + st * kD, c, lo, hi);
+      lo = half_warp_sum(lo);
+      hi = half_warp_sum(hi);
+      if (active && c == 0) p.prep_tab[(size_t)st * gemv::kTabCols + b] = prep_tab_entry<T>(lo, hi);
+    }
   }
   if (threadIdx.x == 0) p.counters[bh] = 0;
 }
 
 int g_attn_chunk = 0;
 
-int pick_chunk(int B, int H, int n_comp) {
-  if (g_attn_chunk) return g_attn_chunk;
-  const long long want = ((long long)n_comp * B * H + 443) / 444;  // ~3 CTAs per SM
-  int chunk = (int)((want + 127) / 128 * 128);
-  if (chunk < 256) chunk = 256;
-  if (chunk > kMaxChunk) chunk = kMaxChunk;
+int pick_chunk(int B, int H, int n_comp, int group) {
+  int chunk;
+  if (g_attn_chunk) {
+    chunk = g_attn_chunk;
+  } else {
+    // about two CTAs per SM; chunks of at most 256 tokens keep three CTAs resident per SM, which is what
+    // overlaps one CTA's copies with another's arithmetic once the grid is larger than the machine
+    const long long want = ((long long)n_comp * B * H + 295) / 296;
+    chunk = (int)((want + 127) / 128 * 128);
+    if (chunk < 128) chunk = 128;
+    if (chunk > 256) chunk = 256;
+    while (chunk < kMaxChunk && (n_comp + chunk - 1) / chunk > 96) chunk += 128;   // bound the merge
+  }
+  if (chunk % group) chunk = (chunk + group - 1) / group * group;
   return chunk;
+}
+
+struct AttnPlan {
+  int chunk, n_csplit, n_rsplit, n_split, s_stride, p_stride;
+  size_t smem;
+};
+
+AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group) {
+  AttnPlan a;
+  a.chunk = pick_chunk(B, H, n_comp, group);
+  a.n_csplit = (n_comp + a.chunk - 1) / a.chunk;
+  a.n_rsplit = (n_res + kResChunk - 1) / kResChunk;
+  a.n_split = a.n_csplit + a.n_rsplit;
+  const int span = a.chunk > 128 ? a.chunk : 128;
+  a.s_stride = span + 4;
+  a.p_stride = (span / 128) * 256 + 64;
+  if (a.p_stride < 512) a.p_stride = 512;   // the residual branch reuses the buffer for an [8][128] fp32 reduction
+  const int st = stage_bytes(a.chunk, group), rs = 2 * kResChunk * kResPitch;
+  a.smem = 128 + (size_t)kHeads * kD * sizeof(float) + (size_t)kHeads * a.s_stride * sizeof(float) +
+           2 * (size_t)kHeads * a.p_stride + (size_t)(st > rs ? st : rs);
+  return a;
 }
 
 }  // namespace
@@ -384,8 +569,8 @@ extern "C" {
 
 size_t pare_kivi_attn_workspace_bytes(int B, int H, int n_comp, int n_res) {
   if (B <= 0 || H <= 0 || n_comp < 0 || n_res < 0) return 0;
-  const int chunk = 128;  // smallest chunk any plan uses -> upper bound on the split count
-  const size_t n_split = (size_t)(n_comp + chunk - 1) / chunk + 1;
+  // smallest chunk any plan uses -> upper bound on the split count
+  const size_t n_split = (size_t)(n_comp + 127) / 128 + (size_t)(n_res + pare::kResChunk - 1) / pare::kResChunk + 1;
   return pare::kCounterBytes + (size_t)B * H * n_split * (pare::kHeads * pare::kD + pare::kHeads * 2) * sizeof(float);
 }
 
@@ -393,10 +578,11 @@ void pare_kivi_attn_set_tuning(int chunk) { pare::g_attn_chunk = chunk; }
 
 int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t q_stride_h, const uint8_t* k_codes,
                           const float* k_scale, const float* k_zero, const uint8_t* v_codes, const float* v_scale,
-                          const float* v_zero, int n_comp, const void* res_k, const void* res_v, int64_t res_stride_b,
-                          int64_t res_stride_h, int64_t res_stride_t, int n_res, void* out, int64_t out_stride_b,
-                          int64_t out_stride_h, float softmax_scale, int B, int Hq, int H, int D, int bits, int group,
-                          int cap, void* workspace, size_t workspace_bytes, void* stream) {
+                          const float* v_zero, int n_comp, void* res_k, void* res_v, int64_t res_stride_b,
+                          int64_t res_stride_h, int64_t res_stride_t, int n_res, const void* new_k, const void* new_v,
+                          int64_t new_stride_b, int64_t new_stride_h, void* out, int64_t out_stride_b,
+                          int64_t out_stride_h, void* prepared_out, float softmax_scale, int B, int Hq, int H, int D,
+                          int bits, int group, int cap, void* workspace, size_t workspace_bytes, void* stream) {
   using namespace pare;
   PARE_REQUIRE(B > 0 && Hq > 0 && H > 0 && Hq % H == 0, PARE_ERR_SHAPE);
   PARE_REQUIRE(D == kD && bits == 4, PARE_ERR_UNSUPPORTED);
@@ -406,47 +592,66 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
   PARE_REQUIRE(n_comp >= 0 && n_res >= 0 && n_comp + n_res > 0, PARE_ERR_SHAPE);
   PARE_REQUIRE(n_comp % group == 0 && n_comp <= cap && cap % 128 == 0, PARE_ERR_SHAPE);
   PARE_REQUIRE(n_res <= kMaxResidual, PARE_ERR_UNSUPPORTED);
-  PARE_REQUIRE(q && out && (n_comp == 0 || (k_codes && k_scale && k_zero && v_codes && v_scale && v_zero)), PARE_ERR_SHAPE);
+  PARE_REQUIRE(q && (out || prepared_out) && (n_comp == 0 || (k_codes && k_scale && k_zero && v_codes && v_scale && v_zero)),
+               PARE_ERR_SHAPE);
   PARE_REQUIRE(n_res == 0 || (res_k && res_v), PARE_ERR_SHAPE);
-  PARE_REQUIRE((size_t)B * H < kCounterInts, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE((new_k == nullptr) == (new_v == nullptr), PARE_ERR_SHAPE);
+  PARE_REQUIRE(new_k == nullptr || n_res > 0, PARE_ERR_SHAPE);
+  PARE_REQUIRE((size_t)B * H < kStatusIndex, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE(prepared_out == nullptr || B <= gemv::kTabCols, PARE_ERR_UNSUPPORTED);
   if (n_res > 0) {
     PARE_REQUIRE(aligned16(res_k) && aligned16(res_v), PARE_ERR_ALIGN);
     PARE_REQUIRE(res_stride_b % 8 == 0 && res_stride_h % 8 == 0 && res_stride_t % 8 == 0, PARE_ERR_ALIGN);
   }
-  if (n_comp > 0) PARE_REQUIRE(aligned16(k_codes) && aligned16(v_codes) && aligned16(k_scale) && aligned16(k_zero), PARE_ERR_ALIGN);
+  if (new_k) {
+    PARE_REQUIRE(aligned16(new_k) && aligned16(new_v) && new_stride_b % 8 == 0 && new_stride_h % 8 == 0, PARE_ERR_ALIGN);
+  }
+  if (prepared_out) PARE_REQUIRE(aligned16(prepared_out), PARE_ERR_ALIGN);
+  if (n_comp > 0)
+    PARE_REQUIRE(aligned16(k_codes) && aligned16(v_codes) && aligned16(k_scale) && aligned16(k_zero) && aligned16(v_scale) &&
+                     aligned16(v_zero),
+                 PARE_ERR_ALIGN);
+
+  const AttnPlan plan = make_attn_plan(B, H, n_comp, n_res, group);
+  PARE_REQUIRE(plan.chunk % 128 == 0 && plan.chunk % group == 0 && plan.chunk <= kMaxChunk, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE(plan.smem <= kAttnSmemCap && (size_t)plan.n_split * 2 * kHeads * sizeof(float) <= 2 * kResChunk * kResPitch, PARE_ERR_UNSUPPORTED);
 
   AttnParams p{};
   p.q = q; p.q_sb = q_stride_b; p.q_sh = q_stride_h;
+  p.q_vec = aligned16(q) && q_stride_b % 8 == 0 && q_stride_h % 8 == 0;
   p.k_codes = k_codes; p.k_scale = k_scale; p.k_zero = k_zero;
   p.v_codes = v_codes; p.v_scale = v_scale; p.v_zero = v_zero;
   p.res_k = res_k; p.res_v = res_v; p.r_sb = res_stride_b; p.r_sh = res_stride_h; p.r_st = res_stride_t; p.n_res = n_res;
+  p.new_k = new_k; p.new_v = new_v; p.n_sb = new_stride_b; p.n_sh = new_stride_h;
   p.out = out; p.o_sb = out_stride_b; p.o_sh = out_stride_h;
+  if (prepared_out) {
+    p.prep_xp = prepared_out;
+    p.prep_tab = reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(prepared_out) + prepared_tab_offset(B, Hq * kD));
+  }
   p.sm_scale = softmax_scale;
   p.B = B; p.Hq = Hq; p.H = H; p.rep = Hq / H; p.group = group; p.cap = cap; p.n_comp = n_comp;
-  p.chunk = pick_chunk(B, H, n_comp);
-  PARE_REQUIRE(p.chunk % 128 == 0 && p.chunk >= 128 && p.chunk <= kMaxChunk, PARE_ERR_UNSUPPORTED);
-  p.n_csplit = (n_comp + p.chunk - 1) / p.chunk;
-  p.n_split = p.n_csplit + (n_res > 0 ? 1 : 0);
-  const int span = p.chunk > ((n_res + 127) / 128 * 128) ? p.chunk : ((n_res + 127) / 128 * 128);
-  p.s_stride = span + 4;
-  p.p_stride = (span / 128) * 256 + 64;
-  if (p.p_stride * kHeads < (int)(kHeads * kD * sizeof(float))) p.p_stride = kD * sizeof(float);  // residual reduction buffer
+  p.chunk = plan.chunk; p.n_csplit = plan.n_csplit; p.n_split = plan.n_split;
+  p.s_stride = plan.s_stride; p.p_stride = plan.p_stride;
   const size_t need = kCounterBytes + (size_t)B * H * p.n_split * (kHeads * kD + kHeads * 2) * sizeof(float);
   PARE_REQUIRE(workspace && workspace_bytes >= need, PARE_ERR_WORKSPACE);
   p.counters = reinterpret_cast<int*>(workspace);
   p.part_o = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + kCounterBytes);
   p.part_ml = p.part_o + (size_t)B * H * p.n_split * kHeads * kD;
 
-  const size_t smem = (size_t)kHeads * kD * sizeof(float) + (size_t)kHeads * p.s_stride * sizeof(float) +
-                      2 * (size_t)kHeads * p.p_stride + 3 * kHeads * sizeof(float) + 16;
-  const dim3 grid(p.n_split, H, B);
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   auto launch = [&](auto kern) -> int {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess) return PARE_ERR_CUDA;
-    kern<<<grid, kAttnThreads, smem, s>>>(p);
-    return launch_status();
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmemCap) != cudaSuccess) return PARE_ERR_CUDA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.n_split, H, B);
+    cfg.blockDim = dim3(kAttnThreads, 1, 1);
+    cfg.dynamicSmemBytes = plan.smem;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess ? PARE_OK : PARE_ERR_CUDA;
   };
-  PARE_REQUIRE(smem <= 96 * 1024, PARE_ERR_UNSUPPORTED);
   return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half>) : launch(kivi_decode_attn_kernel<__nv_bfloat16>);
 }
 

@@ -32,6 +32,7 @@
 // workspace status word and runs to completion without waiting again.
 
 #include "gemv_common.cuh"
+#include "prep.cuh"
 
 namespace pare {
 namespace {
@@ -502,7 +503,7 @@ size_t gemv_workspace_bytes(int M, int N, int K, int G) {
 int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale,
                  const float* zero, const void* meta_h2, const int32_t* col_perm, const float* input_scale,
                  const void* bias, void* y, int64_t ldy, int M, int N, int K, int G, void* workspace,
-                 size_t workspace_bytes, cudaStream_t stream) {
+                 size_t workspace_bytes, cudaStream_t stream, const void* prepared) {
   GemvParams p{};
   p.x = x;
   p.ldx = ldx;
@@ -523,6 +524,7 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   p.x_vec_ok = ((reinterpret_cast<uintptr_t>(x) & 7u) == 0 && (ldx % 4) == 0) ? 1 : 0;
 
   Plan pl = make_plan(M, N, K, G);
+  if (prepared) PARE_REQUIRE(pl.fast && col_perm == nullptr && input_scale == nullptr && aligned16(prepared), PARE_ERR_UNSUPPORTED);
   if (!pl.fast) {
     return x_dtype == PARE_F16 ? launch_generic<__half>(p, packed, G, stream)
                                : launch_generic<__nv_bfloat16>(p, packed, G, stream);
@@ -534,6 +536,7 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   p.splits = pl.splits;
   p.steps_per_split = pl.steps_per_split;
   const size_t need = kCounterBytes + prep_bytes(M, K) + (pl.splits > 1 ? (size_t)pl.splits * M * N * sizeof(float) : 0);
+  static_assert(sizeof(float2) == 8, "table entry");
   PARE_REQUIRE(workspace != nullptr && workspace_bytes >= need, PARE_ERR_WORKSPACE);
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   p.counters = reinterpret_cast<int*>(ws);
@@ -541,8 +544,12 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   p.tabg = reinterpret_cast<float2*>(ws + kCounterBytes + ((size_t)M * K * 2 + 255) / 256 * 256);
   p.partial = reinterpret_cast<float*>(ws + kCounterBytes + prep_bytes(M, K));
 
+  if (prepared) {   // the producer of the activations already wrote them in operand order
+    p.xp = const_cast<void*>(prepared);
+    p.tabg = reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(p.xp) + prepared_tab_offset(M, K));
+  }
   // 1) activations into operand order (one warp per row and 128-column step)
-  {
+  if (!prepared) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((M * (K / 128) + 3) / 4, 1, 1);
     cfg.blockDim = dim3(128, 1, 1);
@@ -560,6 +567,34 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   if (g_tune_persist >= 0 && gemv_persist_supported(M, N, pl.steps_per_split, G / 128, pl.splits))
     return gemv_persist_launch(p, x_dtype, stream);
   return x_dtype == PARE_F16 ? dispatch_gemv<__half>(p, pl, stream) : dispatch_gemv<__nv_bfloat16>(p, pl, stream);
+}
+
+// Activation prep alone, into a caller-owned prepared buffer (prepared_bytes(M, K) bytes).
+int gemv_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_perm, const float* input_scale, int M, int K,
+                 void* prepared, cudaStream_t stream) {
+  PARE_REQUIRE(M > 0 && M <= kTabCols && K > 0 && K % 128 == 0 && aligned16(prepared), PARE_ERR_UNSUPPORTED);
+  GemvParams p{};
+  p.x = x;
+  p.ldx = ldx;
+  p.col_perm = col_perm;
+  p.input_scale = input_scale;
+  p.M = M;
+  p.K = K;
+  p.x_vec_ok = ((reinterpret_cast<uintptr_t>(x) & 7u) == 0 && (ldx % 4) == 0) ? 1 : 0;
+  p.xp = prepared;
+  p.tabg = reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(prepared) + prepared_tab_offset(M, K));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((M * (K / 128) + 3) / 4, 1, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = x_dtype == PARE_F16 ? cudaLaunchKernelEx(&cfg, w4a16_prep_kernel<__half>, p)
+                                            : cudaLaunchKernelEx(&cfg, w4a16_prep_kernel<__nv_bfloat16>, p);
+  return e == cudaSuccess ? PARE_OK : PARE_ERR_CUDA;
 }
 
 // Tuning override for experiments: columns per CTA (multiple of 512) and warps per CTA (4 or 8).

@@ -23,6 +23,7 @@ from torch import Tensor
 
 from pare_b200.config import QuantConfig
 from pare_b200.kernels import _lib
+from pare_b200.kernels.matmul_int4 import PreparedActivations
 from pare_b200.kv_cache import KVCacheConfig, QuantizedKVCache
 from pare_b200.layers.linear import QuantizedLinear
 
@@ -89,22 +90,37 @@ class DecodeStack(nn.Module):
             for i in range(self.n_layers))
         self.cache = QuantizedKVCache(self.n_layers, kv_config or KVCacheConfig(), max_seq_len=max_seq_len)
         self._code = _lib.dtype_code(dtype)
+        self._prep_cache: dict[int, tuple] = {}
 
     # ---- glue kernels ------------------------------------------------------------------
-    def _rmsnorm(self, x: Tensor, delta: Tensor | None, weight: Tensor, store_residual: bool) -> Tensor:
-        y = torch.empty_like(x)
+    def _rmsnorm(self, x: Tensor, delta: Tensor | None, weight: Tensor, store_residual: bool, prepared=None):
+        """rmsnorm(x + delta) * weight as a tensor, or into ``prepared`` (then returns None)."""
+        y = None if prepared is not None else torch.empty_like(x)
         status = _lib.lib().pare_rmsnorm_residual(
-            x.data_ptr(), _lib.ptr(delta), weight.data_ptr(), x.data_ptr() if store_residual else None, y.data_ptr(),
+            x.data_ptr(), _lib.ptr(delta), weight.data_ptr(), x.data_ptr() if store_residual else None, _lib.ptr(y),
+            prepared.data_ptr() if prepared is not None else None,
             x.shape[0], x.shape[1], 1e-5, self._code, _lib.current_stream(x.device))
         _lib.check(status, "pare_rmsnorm_residual")
         return y
 
-    def _silu_mul(self, gate_up: Tensor, n: int) -> Tensor:
-        out = torch.empty(gate_up.shape[0], n, device=gate_up.device, dtype=gate_up.dtype)
-        status = _lib.lib().pare_silu_mul(gate_up.data_ptr(), out.data_ptr(), gate_up.shape[0], n, gate_up.stride(0),
+    def _silu_mul(self, gate_up: Tensor, n: int, prepared=None):
+        out = None if prepared is not None else torch.empty(gate_up.shape[0], n, device=gate_up.device, dtype=gate_up.dtype)
+        status = _lib.lib().pare_silu_mul(gate_up.data_ptr(), _lib.ptr(out),
+                                          prepared.data_ptr() if prepared is not None else None,
+                                          gate_up.shape[0], n, gate_up.stride(0),
                                           self._code, _lib.current_stream(gate_up.device))
         _lib.check(status, "pare_silu_mul")
         return out
+
+    def _prepared(self, m: int):
+        """Per-batch-size hand-over buffers between the kernels of a block (hidden, attention, FFN widths)."""
+        bufs = self._prep_cache.get(m)
+        if bufs is None:
+            blk = self.blocks[0]
+            mk = lambda k: PreparedActivations(m, k, self.dtype, self.device)  # noqa: E731
+            bufs = (mk(self.hidden), mk(blk.hq * blk.d), mk(self.hidden), mk(blk.ffn))
+            self._prep_cache[m] = bufs
+        return bufs
 
     def _all_reduce(self, t: Tensor) -> Tensor:
         if self.tp_world > 1:
@@ -129,20 +145,39 @@ class DecodeStack(nn.Module):
     # ---- one decode step ---------------------------------------------------------------
     @torch.no_grad()
     def forward(self, x: Tensor) -> Tensor:
-        """``x [M, hidden]``: hidden state of the newest token of each of M sequences → same shape."""
+        """``x [M, hidden]``: hidden state of the newest token of each of M sequences → same shape.
+
+        For M <= 16 every activation goes from the kernel that computes it to the next linear as
+        prepared activations (8 launches per block: 2 RMSNorm, 4 linears, attention, SwiGLU; the new
+        K / V token is appended by the attention kernel).  Larger M takes plain tensors.
+        """
         m = x.shape[0]
         resid = x.clone()
         delta = None
+        blk0 = self.blocks[0]
+        fused = all(l.supports_prepared(m) for l in (blk0.qkv, blk0.o, blk0.gate_up, blk0.down))
+        if fused:
+            p_h1, p_attn, p_h2, p_act = self._prepared(m)
         for i, blk in enumerate(self.blocks):
-            h = self._rmsnorm(resid, delta, blk.norm1, store_residual=delta is not None)
-            qkv = blk.qkv(h)
             d, hq, hkv = blk.d, blk.hq, blk.hkv
+            if fused:
+                self._rmsnorm(resid, delta, blk.norm1, store_residual=delta is not None, prepared=p_h1)
+                qkv = blk.qkv.forward_prepared(p_h1)
+            else:
+                qkv = blk.qkv(self._rmsnorm(resid, delta, blk.norm1, store_residual=delta is not None))
             q = qkv[:, : hq * d].unflatten(1, (hq, d))
             k = qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, 1, d))
             v = qkv[:, (hq + hkv) * d:].unflatten(1, (hkv, 1, d))
-            attn = self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d))
-            o = self._all_reduce(blk.o(attn.reshape(m, hq * d)))
-            h2 = self._rmsnorm(resid, o, blk.norm2, store_residual=True)
-            act = self._silu_mul(blk.gate_up(h2), blk.ffn)
-            delta = self._all_reduce(blk.down(act))
+            if fused:
+                self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d), prepared_out=p_attn)
+                o = self._all_reduce(blk.o.forward_prepared(p_attn))
+                self._rmsnorm(resid, o, blk.norm2, store_residual=True, prepared=p_h2)
+                self._silu_mul(blk.gate_up.forward_prepared(p_h2), blk.ffn, prepared=p_act)
+                delta = self._all_reduce(blk.down.forward_prepared(p_act))
+            else:
+                attn = self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d))
+                o = self._all_reduce(blk.o(attn.reshape(m, hq * d)))
+                h2 = self._rmsnorm(resid, o, blk.norm2, store_residual=True)
+                act = self._silu_mul(blk.gate_up(h2), blk.ffn)
+                delta = self._all_reduce(blk.down(act))
         return resid + delta

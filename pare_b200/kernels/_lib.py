@@ -31,6 +31,10 @@ SIGNATURES: dict[str, tuple] = {
     "pare_w4a16_forward": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                 _i, _i, _i, _i, _vp, _sz, _vp]),
     "pare_w4a16_set_tuning": (None, [_i, _i, _i]),
+    "pare_w4a16_prepared_bytes": (_sz, [_i, _i]),
+    "pare_w4a16_prepare": (_i, [_vp, _i, _i64, _vp, _vp, _i, _i, _vp, _vp]),
+    "pare_w4a16_forward_prepared": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                                         _i, _i, _i, _i, _vp, _sz, _vp]),
     "pare_kivi_append": (_i, [_vp, _vp, _i, _i64, _i64, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
                               _i, _i, _i, _i, _i, _i, _vp]),
     "pare_kivi_dequant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
@@ -38,11 +42,12 @@ SIGNATURES: dict[str, tuple] = {
     "pare_kivi_attn_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "pare_kivi_decode_attn": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i,
                                    _vp, _vp, _i64, _i64, _i64, _i,
-                                   _vp, _i64, _i64, C.c_float,
+                                   _vp, _vp, _i64, _i64,
+                                   _vp, _i64, _i64, _vp, C.c_float,
                                    _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "pare_kivi_attn_set_tuning": (None, [_i]),
-    "pare_rmsnorm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, C.c_float, _i, _vp]),
-    "pare_silu_mul": (_i, [_vp, _vp, _i, _i, _i64, _i, _vp]),
+    "pare_rmsnorm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, C.c_float, _i, _vp]),
+    "pare_silu_mul": (_i, [_vp, _vp, _vp, _i, _i, _i64, _i, _vp]),
     "pare_w4a16_static_scratch_bytes": (_sz, []),
     "pare_w4a16_forward_static": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                        _i, _i, _i, _i, _vp]),

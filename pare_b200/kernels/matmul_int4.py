@@ -104,6 +104,59 @@ def w4a16_forward(
     return y
 
 
+class PreparedActivations:
+    """Activations of a W4A16 linear in the order its decode kernel consumes them.
+
+    An opaque device buffer for ``rows <= 16`` activation rows of ``k`` columns (``k % 128 == 0``)
+    of ``dtype``.  Kernels that compute an activation (RMSNorm, SwiGLU, the fused decode
+    attention) can write into it directly; :func:`prepare` fills it from a plain tensor.
+    """
+
+    def __init__(self, rows: int, k: int, dtype: torch.dtype, device) -> None:
+        nbytes = _lib.lib().pare_w4a16_prepared_bytes(rows, k)
+        if nbytes == 0:
+            raise ValueError(f"prepared activations need rows <= 16 and k % 128 == 0 (got {rows} x {k})")
+        self.rows, self.k, self.dtype = rows, k, dtype
+        self.buffer = torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+    def data_ptr(self) -> int:
+        return self.buffer.data_ptr()
+
+
+def prepare(x: Tensor, *, col_perm: Tensor | None = None, input_scale: Tensor | None = None,
+            out: PreparedActivations | None = None) -> PreparedActivations:
+    """Put ``x [M, K]`` (M <= 16) into operand order (what every M <= 16 ``w4a16_forward`` does first)."""
+    assert x.is_cuda and x.dim() == 2 and x.stride(1) == 1
+    m, k = x.shape
+    prep = out if out is not None else PreparedActivations(m, k, x.dtype, x.device)
+    assert (prep.rows, prep.k, prep.dtype) == (m, k, x.dtype)
+    status = _lib.lib().pare_w4a16_prepare(x.data_ptr(), _lib.dtype_code(x.dtype), x.stride(0), _lib.ptr(col_perm),
+                                           _lib.ptr(input_scale), m, k, prep.data_ptr(), _lib.current_stream(x.device))
+    _lib.check(status, "pare_w4a16_prepare")
+    return prep
+
+
+def w4a16_forward_prepared(prep: PreparedActivations, packed_weight: Tensor, scale: Tensor | None, zero: Tensor | None,
+                           group_size: int, *, bias: Tensor | None = None, meta_h2: Tensor | None = None,
+                           out: Tensor | None = None) -> Tensor:
+    """:func:`w4a16_forward` for activations that already are in operand order."""
+    n, k_half = packed_weight.shape
+    assert prep.k == 2 * k_half and packed_weight.dtype == torch.uint8 and packed_weight.is_contiguous()
+    m, k = prep.rows, prep.k
+    if bias is not None and bias.dtype != prep.dtype:
+        bias = bias.to(prep.dtype)
+    dev = packed_weight.device
+    y = out if out is not None else torch.empty(m, n, device=dev, dtype=prep.dtype)
+    L = _lib.lib()
+    ws = _lib.workspace(dev, L.pare_w4a16_workspace_bytes(m, n, k, group_size))
+    status = L.pare_w4a16_forward_prepared(
+        prep.data_ptr(), _lib.dtype_code(prep.dtype), packed_weight.data_ptr(),
+        _lib.ptr(scale), _lib.ptr(zero), _lib.ptr(meta_h2), _lib.ptr(bias),
+        y.data_ptr(), y.stride(0), m, n, k, group_size, ws.data_ptr(), ws.numel(), _lib.current_stream(dev))
+    _lib.check(status, "pare_w4a16_forward_prepared")
+    return y
+
+
 # kernel-layout tensor (as passed by reference-style callers) -> storage layout, cached per tensor
 # object: keyed by id() (tensors do not hash/compare as dict keys) and dropped when it dies
 _storage_cache: dict[int, tuple[int, int, Tensor]] = {}

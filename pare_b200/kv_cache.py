@@ -189,8 +189,11 @@ class QuantizedKVCache:
             self._stores[layer_idx] = st
         return st
 
-    def _append(self, layer_idx: int, new_k: Tensor, new_v: Tensor) -> _LayerStore:
-        """Append tokens to the residual window and compress what overflows it."""
+    def _append(self, layer_idx: int, new_k: Tensor, new_v: Tensor, defer_single: bool = False):
+        """Append tokens to the residual window and compress what overflows it.
+
+        With ``defer_single`` returns ``(store, deferred)``: when one token arrives and nothing has
+        to be compressed, the copy into the window is left to the attention kernel (``deferred``)."""
         if new_k.shape != new_v.shape or new_k.dim() != 4:
             raise ValueError("new_k / new_v must both be [B, H, new_tokens, D]")
         st = self._store(layer_idx, new_k)
@@ -201,7 +204,13 @@ class QuantizedKVCache:
         n_c, r_after = plan_update(st.r_len, n_new, cfg.residual_length, cfg.group_size)
         total = st.r_len + n_new
 
-        if total <= st.r_cap:
+        deferred = (defer_single and n_new == 1 and n_c == 0 and total <= st.r_cap
+                    and new_k.data_ptr() % 16 == 0 and new_v.data_ptr() % 16 == 0
+                    and all(t.stride(3) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 for t in (new_k, new_v))
+                    and new_k.stride() == new_v.stride())
+        if deferred:
+            pass
+        elif total <= st.r_cap:
             st.res_k[:, :, st.r_len:total] = new_k
             st.res_v[:, :, st.r_len:total] = new_v
             src_k, src_v = st.res_k, st.res_v
@@ -231,7 +240,7 @@ class QuantizedKVCache:
         self._compressed[layer_idx] = _CompressedKV(st) if st.n_comp > 0 else None
         self._residual_k[layer_idx] = st.res_k[:, :, : st.r_len]
         self._residual_v[layer_idx] = st.res_v[:, :, : st.r_len]
-        return st
+        return (st, deferred) if defer_single else st
 
     # ------------------------------------------------------------------ public API
     def update(self, layer_idx: int, new_k: Tensor, new_v: Tensor) -> tuple[Tensor, Tensor]:
@@ -253,35 +262,53 @@ class QuantizedKVCache:
         full_v[:, :, st.n_comp:] = st.res_v[:, :, : st.r_len]
         return full_k, full_v
 
-    def attend(self, layer_idx: int, q: Tensor, new_k: Tensor, new_v: Tensor, scale: float | None = None) -> Tensor:
+    def attend(self, layer_idx: int, q: Tensor, new_k: Tensor, new_v: Tensor, scale: float | None = None,
+               prepared_out=None) -> Tensor | None:
         """Append one step's keys / values, then attention of ``q`` over the whole cache.
 
         ``q`` is ``[B, Hq, 1, D]`` (or ``[B, Hq, D]``) with ``Hq`` a multiple of the KV heads
         (grouped-query attention, at most 8 query heads per KV head).  Equivalent to
         ``softmax(q K^T * scale) V`` on the tensors :meth:`update` would return, computed from
         the packed cache without reconstructing it.  Returns a tensor shaped like ``q``.
+
+        A single new token that needs no compression in this step is not copied by the host
+        side at all: the attention kernel reads it where it is and stores it into the residual
+        window itself.  With ``prepared_out`` (a ``PreparedActivations`` of ``B`` rows and
+        ``Hq * D`` columns) the result is written as prepared activations of the next linear
+        instead, and ``None`` is returned.
         """
-        st = self._append(layer_idx, new_k, new_v)
-        if q.dtype != st.dtype or q.dtype not in (torch.float16, torch.bfloat16):
-            raise ValueError("attend() needs q in the cache dtype, float16 or bfloat16")
+        if q.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError("attend() needs q in float16 or bfloat16")
+        st, fused_new = self._append(layer_idx, new_k, new_v, defer_single=True)
+        if q.dtype != st.dtype:
+            raise ValueError("attend() needs q in the cache dtype")
         q3 = q.reshape(q.shape[0], q.shape[1], q.shape[-1])
         if q3.stride(-1) != 1:
             q3 = q3.contiguous()
         B, Hq, D = q3.shape
-        out = torch.empty(B, Hq, D, device=q.device, dtype=q.dtype)
+        out = None if prepared_out is not None else torch.empty(B, Hq, D, device=q.device, dtype=q.dtype)
+        if prepared_out is not None and (prepared_out.rows, prepared_out.k, prepared_out.dtype) != (B, Hq * D, q.dtype):
+            raise ValueError("prepared_out does not match the attention output")
+        nk = nv = None
+        if fused_new:
+            nk, nv = new_k[:, :, 0], new_v[:, :, 0]     # [B, H, D] views
+            if nk.stride(-1) != 1 or nv.stride() != nk.stride():
+                nk, nv = nk.contiguous(), nv.contiguous()
         L = _lib.lib()
         ws = _lib.workspace(st.device, L.pare_kivi_attn_workspace_bytes(B, st.H, st.n_comp, st.r_len))
         status = L.pare_kivi_decode_attn(
             q3.data_ptr(), _lib.dtype_code(q.dtype), q3.stride(0), q3.stride(1),
             *st.cache_args(), st.n_comp,
             st.res_k.data_ptr(), st.res_v.data_ptr(), st.res_k.stride(0), st.res_k.stride(1), st.res_k.stride(2), st.r_len,
-            out.data_ptr(), out.stride(0), out.stride(1),
+            _lib.ptr(nk), _lib.ptr(nv), nk.stride(0) if fused_new else 0, nk.stride(1) if fused_new else 0,
+            _lib.ptr(out), out.stride(0) if out is not None else 0, out.stride(1) if out is not None else 0,
+            prepared_out.data_ptr() if prepared_out is not None else None,
             float(scale if scale is not None else 1.0 / math.sqrt(D)),
             B, Hq, st.H, D, self.config.bits, self.config.group_size, st.cap,
             ws.data_ptr(), ws.numel(), _lib.current_stream(st.device),
         )
         _lib.check(status, "pare_kivi_decode_attn")
-        return out.reshape(q.shape)
+        return None if out is None else out.reshape(q.shape)
 
     def reset(self, layer_idx: int | None = None) -> None:
         """Forget one layer or all layers (buffers are released and reallocated on next use)."""

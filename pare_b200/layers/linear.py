@@ -172,6 +172,27 @@ class QuantizedLinear(nn.Module):
         )
         return y.to(out_dtype).reshape(*shape[:-1], self.out_features)
 
+    def supports_prepared(self, rows: int) -> bool:
+        """True if :meth:`forward_prepared` can serve ``rows`` activation rows of this layer."""
+        return (self.use_kernel and self.config.dtype == QuantDtype.INT4 and not self.quantize_inputs
+                and self.g_idx is None and self.input_scale is None and rows <= 16
+                and self.in_features % 512 == 0 and self._kernel_group_size() % 128 == 0)
+
+    def forward_prepared(self, prep) -> Tensor:
+        """Forward for activations handed over as :class:`PreparedActivations` (decode, rows <= 16):
+        the producing kernel wrote them in operand order, so no preparation launch is needed."""
+        from pare_b200.kernels.matmul_int4 import w4a16_forward_prepared
+
+        if not self.supports_prepared(prep.rows):
+            raise ValueError("this layer cannot take prepared activations (act-order, input scale, shape or row count)")
+        if not hasattr(self, "_packed_weight_kernel"):
+            self._prepare_kernel_buffers()
+        use_h2 = self.kernel_meta_fp16
+        return w4a16_forward_prepared(
+            prep, self._packed_weight_kernel,
+            None if use_h2 else self._scale_kernel, None if use_h2 else self._zero_kernel,
+            self._kernel_group_size(), bias=self.bias, meta_h2=self._meta_h2_kernel if use_h2 else None)
+
     # -- alternate constructors ----------------------------------------------
     @classmethod
     def from_tensors(

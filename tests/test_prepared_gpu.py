@@ -1,0 +1,168 @@
+"""Prepared activations (GPU): the hand-over format between the kernels of a decode step.
+
+What is checked, and how tightly:
+  * ``prepare`` + ``w4a16_forward_prepared`` is the M <= 16 path of ``w4a16_forward`` cut in two:
+    bit-identical outputs;
+  * RMSNorm / SwiGLU / attention writing prepared activations directly: the operand-order
+    activations are bit-identical to ``prepare(plain output)``; the per-step sums are added in a
+    different order (fp32), so they agree to 1e-5 relative and the linear's output to the oracle
+    bars of test_w4a16_gpu.py (max rel <= 1e-2, mean <= 1e-3 fp16 / 2.5e-3 bf16);
+  * a decode stack through the fused path vs the same stack through plain tensors: max rel <= 1e-2
+    of the output scale, mean <= 1e-3 (fp16).
+"""
+
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import w4a16 as ow
+from pare_b200.decode import DecodeStack
+from pare_b200.kernels import _lib, w4a16_forward
+from pare_b200.kernels.matmul_int4 import PreparedActivations, prepare, w4a16_forward_prepared
+from pare_b200.kv_cache import KVCacheConfig, QuantizedKVCache
+
+pytestmark = pytest.mark.gpu
+
+
+def _layer(n, k, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    packed = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+    scale = torch.rand(n, k // 128, device="cuda", generator=g) * 0.01 + 0.001
+    zero = torch.randint(0, 16, (n, k // 128), device="cuda", generator=g).float()
+    return packed, scale, zero
+
+
+def _split(prep):
+    """(operand-order activations as int16, table as float32 [steps, 16, 2]) of a prepared buffer."""
+    m, k = prep.rows, prep.k
+    off = (m * k * 2 + 255) // 256 * 256
+    xp = prep.buffer[: m * k * 2].view(torch.int16).reshape(m, k)
+    tab = prep.buffer[off: off + (k // 128) * 16 * 8].view(torch.float32).reshape(k // 128, 16, 2)[:, :m]
+    return xp, tab
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (4, 28672, 4096), (16, 512, 1024), (3, 4096, 14336), (1, 9472, 3584)])
+def test_prepared_forward_is_the_plain_forward(m, n, k, dtype, cuda_lib):
+    packed, scale, zero = _layer(n, k, seed=n + k)
+    x = torch.randn(m, k, device="cuda").to(dtype)
+    y_plain = w4a16_forward(x, packed, scale, zero, 128)
+    y_prep = w4a16_forward_prepared(prepare(x), packed, scale, zero, 128)
+    assert torch.equal(y_plain, y_prep)
+
+
+def test_prepared_rejects_what_it_cannot_do(cuda_lib):
+    with pytest.raises(ValueError):
+        PreparedActivations(17, 1024, torch.float16, "cuda")
+    with pytest.raises(ValueError):
+        PreparedActivations(1, 1000, torch.float16, "cuda")
+    packed, scale, zero = _layer(256, 640)          # K % 512 != 0: only the any-shape kernel serves it
+    x = torch.randn(1, 640, device="cuda").half()
+    with pytest.raises(_lib.KernelLibraryError):
+        w4a16_forward_prepared(prepare(x), packed, scale, zero, 128)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,n", [(1, 4096), (4, 3584), (16, 1024)])
+def test_rmsnorm_writes_prepared(rows, n, dtype, cuda_lib):
+    L, code = cuda_lib, _lib.dtype_code(dtype)
+    x = torch.randn(rows, n, device="cuda").to(dtype)
+    delta = torch.randn(rows, n, device="cuda").to(dtype)
+    w = (1 + 0.1 * torch.randn(n, device="cuda")).to(dtype)
+    y = torch.empty_like(x)
+    r1, r2 = torch.empty_like(x), torch.empty_like(x)
+    s = _lib.current_stream(x.device)
+    _lib.check(L.pare_rmsnorm_residual(x.data_ptr(), delta.data_ptr(), w.data_ptr(), r1.data_ptr(), y.data_ptr(), None,
+                                       rows, n, 1e-5, code, s), "rmsnorm")
+    prep = PreparedActivations(rows, n, dtype, "cuda")
+    _lib.check(L.pare_rmsnorm_residual(x.data_ptr(), delta.data_ptr(), w.data_ptr(), r2.data_ptr(), None, prep.data_ptr(),
+                                       rows, n, 1e-5, code, s), "rmsnorm")
+    # the plain result against a torch fp32 reference of the same op (tolerance: one rounding of the output dtype)
+    h = (x.float() + delta.float()).to(dtype).float()
+    ref = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + 1e-5) * w.float()
+    assert torch.allclose(y.float(), ref, rtol=2 ** -7 if dtype == torch.bfloat16 else 2 ** -10, atol=1e-3)
+    assert torch.equal(r1, r2) and torch.equal(r1.float(), h)
+    xp_a, tab_a = _split(prep)
+    xp_b, tab_b = _split(prepare(y))
+    assert torch.equal(xp_a, xp_b)
+    assert torch.allclose(tab_a, tab_b, rtol=1e-5, atol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,n", [(1, 14336), (4, 1024)])
+def test_silu_mul_writes_prepared(rows, n, dtype, cuda_lib):
+    L, code = cuda_lib, _lib.dtype_code(dtype)
+    gu = torch.randn(rows, 2 * n, device="cuda").to(dtype)
+    out = torch.empty(rows, n, device="cuda", dtype=dtype)
+    s = _lib.current_stream(gu.device)
+    _lib.check(L.pare_silu_mul(gu.data_ptr(), out.data_ptr(), None, rows, n, 2 * n, code, s), "silu")
+    prep = PreparedActivations(rows, n, dtype, "cuda")
+    _lib.check(L.pare_silu_mul(gu.data_ptr(), None, prep.data_ptr(), rows, n, 2 * n, code, s), "silu")
+    ref = torch.nn.functional.silu(gu[:, :n].float()) * gu[:, n:].float()
+    assert torch.allclose(out.float(), ref, rtol=2 ** -7 if dtype == torch.bfloat16 else 2 ** -10, atol=1e-3)
+    xp_a, tab_a = _split(prep)
+    xp_b, tab_b = _split(prepare(out))
+    assert torch.equal(xp_a, xp_b)
+    assert torch.allclose(tab_a, tab_b, rtol=1e-5, atol=1e-3)
+
+
+def test_silu_mul_ragged_width(cuda_lib):
+    """Widths that are not a multiple of 8 take the scalar path (no prepared output there)."""
+    n = 1003
+    gu = torch.randn(2, 2 * n + 3, device="cuda").half()[:, : 2 * n]
+    out = torch.empty(2, n, device="cuda", dtype=torch.float16)
+    _lib.check(cuda_lib.pare_silu_mul(gu.data_ptr(), out.data_ptr(), None, 2, n, gu.stride(0), _lib.F16,
+                                      _lib.current_stream(gu.device)), "silu")
+    ref = torch.nn.functional.silu(gu[:, :n].float()) * gu[:, n:].float()
+    assert torch.allclose(out.float(), ref, rtol=2 ** -10, atol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_attention_writes_prepared_and_appends(dtype, cuda_lib):
+    bsz, hkv, hq, ctx, d = 2, 2, 8, 700, 128
+    g = torch.Generator().manual_seed(11)
+    k = torch.randn(bsz, hkv, ctx, d, generator=g).to(dtype).cuda()
+    v = torch.randn(bsz, hkv, ctx, d, generator=g).to(dtype).cuda()
+    q = torch.randn(bsz, hq, 1, d, generator=g).to(dtype).cuda()
+    outs = []
+    for fused in (False, True):
+        cache = QuantizedKVCache(1, KVCacheConfig(bits=4, group_size=32, residual_length=128), max_seq_len=1024)
+        cache.update(0, k[:, :, :-1], v[:, :, :-1])
+        if fused:
+            prep = PreparedActivations(bsz, hq * d, dtype, "cuda")
+            assert cache.attend(0, q, k[:, :, -1:], v[:, :, -1:], prepared_out=prep) is None
+            outs.append(prep)
+        else:
+            outs.append(cache.attend(0, q, k[:, :, -1:], v[:, :, -1:]))
+        # the newest token is in the window whichever way it got there
+        assert torch.equal(cache._residual_k[0][:, :, -1], k[:, :, -1])
+        assert torch.equal(cache._residual_v[0][:, :, -1], v[:, :, -1])
+    xp_a, tab_a = _split(outs[1])
+    xp_b, tab_b = _split(prepare(outs[0].reshape(bsz, hq * d)))
+    assert torch.equal(xp_a, xp_b)
+    assert torch.allclose(tab_a, tab_b, rtol=1e-5, atol=1e-3)
+
+
+def test_decode_stack_fused_equals_plain(cuda_lib, monkeypatch):
+    """Two blocks of a small Llama-shaped stack, M = 2: hand-over through prepared activations vs plain tensors."""
+    shape = (1024, 2048, 8, 2, 128, 2)
+
+    def run(fused):
+        torch.manual_seed(0)
+        stack = DecodeStack(shape, dtype=torch.float16, max_seq_len=512, seed=3)
+        if not fused:
+            for blk in stack.blocks:
+                for lin in (blk.qkv, blk.o, blk.gate_up, blk.down):
+                    monkeypatch.setattr(lin, "supports_prepared", lambda rows: False)
+        stack.prefill_cache(2, 224)
+        x = torch.randn(2, 1024, generator=torch.Generator().manual_seed(5)).half().cuda()
+        y = None
+        for _ in range(3):
+            y = stack(x)
+        return y.float().cpu().numpy()
+
+    a, b = run(True), run(False)
+    mx, mean = ow.rel_err(a, b)
+    assert mx <= 1e-2 and mean <= 1e-3, (mx, mean)
+    assert np.isfinite(a).all()
