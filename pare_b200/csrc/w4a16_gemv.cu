@@ -481,8 +481,11 @@ int launch_generic(const GemvParams& p, const uint8_t* packed, int G, cudaStream
 
 }  // namespace
 
-bool gemv_persist_supported(int M, int N, int steps_per_split, int steps_per_group, int splits);
-void gemv_persist_set_warps(int w);
+bool gemv_persist_supported(int M, int N, int K, int G);
+size_t gemv_persist_partial_floats(int M, int N, int K);
+void gemv_persist_set_min_items(int n);
+void gemv_persist_set_depth(int d);
+void gemv_persist_set_epilogue_warps(int n);
 int gemv_persist_launch(const gemv::GemvParams& p, int x_dtype, cudaStream_t stream);
 
 size_t prep_bytes(int M, int K) {  // prepared activations + step table, each rounded to 256 bytes
@@ -496,7 +499,8 @@ size_t gemv_workspace_bytes(int M, int N, int K, int G) {
   size_t splits = 1;
   if (K % 512 == 0 && G % 128 == 0) splits = (size_t)(K / 512);  // upper bound on any plan
   if (splits > 64) splits = 64;
-  return kCounterBytes + prep_bytes(m, K) + splits * (size_t)m * N * sizeof(float);
+  // split-K partial sums of either schedule (the persistent one adds at most one 32-row block per SM)
+  return kCounterBytes + prep_bytes(m, K) + (splits * (size_t)m * N + (size_t)kSmCount * 32 * m) * sizeof(float);
 }
 
 // Called by pare_w4a16_forward for every chunk of at most 16 activation rows.
@@ -535,7 +539,10 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   PARE_REQUIRE((pl.steps_per_split + pl.warps - 1) / pl.warps <= kMaxStepsPerWarp / pl.rb, PARE_ERR_UNSUPPORTED);
   p.splits = pl.splits;
   p.steps_per_split = pl.steps_per_split;
-  const size_t need = kCounterBytes + prep_bytes(M, K) + (pl.splits > 1 ? (size_t)pl.splits * M * N * sizeof(float) : 0);
+  const bool persist = g_tune_persist >= 0 && gemv_persist_supported(M, N, K, G);
+  const size_t need = kCounterBytes + prep_bytes(M, K) +
+                      (persist ? gemv_persist_partial_floats(M, N, K) * sizeof(float)
+                               : (pl.splits > 1 ? (size_t)pl.splits * M * N * sizeof(float) : 0));
   static_assert(sizeof(float2) == 8, "table entry");
   PARE_REQUIRE(workspace != nullptr && workspace_bytes >= need, PARE_ERR_WORKSPACE);
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
@@ -564,8 +571,7 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
     if (e != cudaSuccess) return PARE_ERR_CUDA;
   }
   // 2) the streaming kernel: persistent schedule for large layers at M <= 4, one tile per CTA otherwise
-  if (g_tune_persist >= 0 && gemv_persist_supported(M, N, pl.steps_per_split, G / 128, pl.splits))
-    return gemv_persist_launch(p, x_dtype, stream);
+  if (persist) return gemv_persist_launch(p, x_dtype, stream);
   return x_dtype == PARE_F16 ? dispatch_gemv<__half>(p, pl, stream) : dispatch_gemv<__nv_bfloat16>(p, pl, stream);
 }
 
@@ -600,7 +606,10 @@ int gemv_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_per
 // Tuning override for experiments: columns per CTA (multiple of 512) and warps per CTA (4 or 8).
 void gemv_set_tuning(int rb, int kc, int warps) {
   g_tune_persist = rb < 0 ? -1 : 0;
-  gemv_persist_set_warps(warps == 8 ? 8 : 16);
+  gemv_persist_set_min_items(rb >= 100 ? rb : 96);   // experiments: rb >= 100 sets the persistent schedule's threshold,
+  gemv_persist_set_depth(rb >= 100 ? warps : 0);      // and `warps` its ring depth
+  gemv_persist_set_epilogue_warps(rb >= 100 ? kc : 0);   // and `kc` its epilogue warps
+  if (rb >= 100) { rb = 0; warps = 0; kc = 0; }
   if (rb < 0) rb = 0;
   g_tune_rb = rb;
   g_tune_kc = kc;
