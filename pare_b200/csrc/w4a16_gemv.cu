@@ -485,7 +485,6 @@ bool gemv_persist_supported(int M, int N, int K, int G);
 size_t gemv_persist_partial_floats(int M, int N, int K);
 void gemv_persist_set_min_items(int n);
 void gemv_persist_set_depth(int d);
-void gemv_persist_set_epilogue_warps(int n);
 int gemv_persist_launch(const gemv::GemvParams& p, int x_dtype, cudaStream_t stream);
 
 size_t prep_bytes(int M, int K) {  // prepared activations + step table, each rounded to 256 bytes
@@ -608,7 +607,6 @@ void gemv_set_tuning(int rb, int kc, int warps) {
   g_tune_persist = rb < 0 ? -1 : 0;
   gemv_persist_set_min_items(rb >= 100 ? rb : 96);   // experiments: rb >= 100 sets the persistent schedule's threshold,
   gemv_persist_set_depth(rb >= 100 ? warps : 0);      // and `warps` its ring depth
-  gemv_persist_set_epilogue_warps(rb >= 100 ? kc : 0);   // and `kc` its epilogue warps
   if (rb >= 100) { rb = 0; warps = 0; kc = 0; }
   if (rb < 0) rb = 0;
   g_tune_rb = rb;

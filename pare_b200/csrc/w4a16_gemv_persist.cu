@@ -32,17 +32,19 @@ namespace {
 using namespace gemv;
 
 constexpr int kMaxDepth = 4;           // ring slots (2..4, as many as fit)
-constexpr int kRowsPerTile = 32;
+constexpr int kMaxRows = 32;           // rows of a tile: 32, or 16 when two blocks of activation rows are in play
 constexpr int kCW = 16;                // consumer warps
-constexpr int kStepsPW = 2;            // 128-column steps per consumer warp and slice
-constexpr int kSliceSteps = kCW * kStepsPW;
-constexpr int kThreads = (kCW + 3) * 32;   // consumers + producer + two epilogue warps
+constexpr int kEpi = 2;                // epilogue warps
+constexpr int kThreads = (kCW + 1 + kEpi) * 32;   // consumers + producer + epilogue warps
 constexpr int kGrid = 148;
 
 struct StreamPlan {
   int n_tiles;    // row tiles
   int n_slices;   // K slices
-  int sps;        // steps per slice (even, <= 32)
+  int sps;        // 128-column steps per slice (a multiple of spw, <= 16 * spw)
+  int spw;        // steps per consumer warp and slice
+  int rows;       // rows per tile (16 or 32)
+  int red_bufs;   // exchange buffers (2, or 1 when shared memory is short)
   int gs;         // CTAs per slice
   int q;          // whole items per CTA
   int n_full;     // q * gs: items of a slice handed out whole
@@ -51,7 +53,6 @@ struct StreamPlan {
   int units;      // contributions per slice: n_full + pieces
   int depth;      // ring slots
   int compact;    // M <= 2: the exchange area keeps only the two activation columns in use
-  int n_epi;      // epilogue warps (1 or 2)
   int flags;      // experiments: 1 = sleeping waits for producer / epilogue
 };
 
@@ -107,9 +108,12 @@ __device__ __forceinline__ Item item_of(const StreamPlan& pl, int bl, int i) {
   return it;
 }
 
-template <typename T, bool META16, int N_EPI>
-__global__ void __launch_bounds__((kCW + 1 + N_EPI) * 32, 1) w4a16_gemv_persist_kernel(const GemvParams p, const StreamPlan pl) {
+// SPW = 128-column steps per consumer warp and slice, RB = 16-row blocks per tile, MB = blocks of 8
+// activation rows (M <= 8 MB).
+template <typename T, bool META16, int SPW, int RB, int MB>
+__global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const GemvParams p, const StreamPlan pl) {
   extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int R = 16 * RB;   // rows per tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   const int steps_total = p.K >> 7;
@@ -121,13 +125,14 @@ __global__ void __launch_bounds__((kCW + 1 + N_EPI) * 32, 1) w4a16_gemv_persist_
 
   const int pitch = pl.sps * 64 + 64;        // == 64 (mod 128)
   const int xstride = pl.sps * 256 + 64;
-  const int red_lanes = pl.compact ? 8 : 32;                 // float4 entries per (warp, row block)
-  const int red_buf = kCW * 2 * red_lanes * 16;              // bytes of one exchange buffer
+  const int red_lanes = pl.compact ? 8 : 32;                 // float4 entries per (warp, row block, activation block)
+  const int red_buf = kCW * RB * MB * red_lanes * 16;        // bytes of one exchange buffer
+  const int nred = pl.red_bufs;
   unsigned char* ring = smem;                                                     // [depth][32][pitch]
-  unsigned char* xs = ring + depth * kRowsPerTile * pitch;                        // [M][xstride]
+  unsigned char* xs = ring + depth * R * pitch;                        // [M][xstride]
   float2* tab = reinterpret_cast<float2*>(xs + (size_t)p.M * xstride);            // [sps][kTabCols]
   unsigned char* red = reinterpret_cast<unsigned char*>(tab + (size_t)pl.sps * kTabCols);   // [2][kCW][2][red_lanes] float4
-  uint32_t* zero_blk = reinterpret_cast<uint32_t*>(red + 2 * red_buf);            // 256 zero bytes
+  uint32_t* zero_blk = reinterpret_cast<uint32_t*>(red + nred * red_buf);            // 256 zero bytes
   uint64_t* bars = reinterpret_cast<uint64_t*>(zero_blk + 64);                    // full[4] empty[4] red_full[2] red_empty[2]
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kMaxDepth);
   const uint32_t rfull0 = smem_u32(bars + 2 * kMaxDepth), rempty0 = smem_u32(bars + 2 * kMaxDepth + 2);
@@ -155,14 +160,14 @@ __global__ void __launch_bounds__((kCW + 1 + N_EPI) * 32, 1) w4a16_gemv_persist_
     int slot = 0, ph = 0;
     for (int i = 0; i < n_items; ++i) {
       const Item it = item_of(pl, bl, i);
-      const int lo = min(it.w_lo * kStepsPW, sps_this), hi = min(it.w_hi * kStepsPW, sps_this);
+      const int lo = min(it.w_lo * SPW, sps_this), hi = min(it.w_hi * SPW, sps_this);
       const int bytes = (hi - lo) * 64;
       wait_relaxed(empty0 + slot * 8, ph ^ 1, status, dead, pl.flags & 1);
-      if (lane == 0) mbar_expect_tx(full0 + slot * 8, kRowsPerTile * bytes);
+      if (lane == 0) mbar_expect_tx(full0 + slot * 8, R * bytes);
       __syncwarp();
-      if (bytes > 0) {
-        const int r = it.tile * kRowsPerTile + lane;
-        bulk_load(ring_u32 + (slot * kRowsPerTile + lane) * pitch + lo * 64,
+      if (bytes > 0 && lane < R) {
+        const int r = it.tile * R + lane;
+        bulk_load(ring_u32 + (slot * R + lane) * pitch + lo * 64,
                   p.packed + (size_t)r * (p.K >> 1) + (size_t)(s0 + lo) * 64, bytes, full0 + slot * 8);
       }
       if (++slot == depth) { slot = 0; ph ^= 1; }
@@ -177,48 +182,65 @@ __global__ void __launch_bounds__((kCW + 1 + N_EPI) * 32, 1) w4a16_gemv_persist_
     pdl_wait();   // outputs, workspace partials and counters may still be in use by the previous kernel
     T* yg = reinterpret_cast<T*>(p.y);
     const T* bias = reinterpret_cast<const T*>(p.bias);
-    const int n_active = sps_this / kStepsPW;   // consumer warps with a share of this slice
-    for (int i = warp - kCW - 1; i < n_items; i += N_EPI) {
+    const int n_active = sps_this / SPW;   // consumer warps with a share of this slice
+    // one epilogue warp per exchange buffer, so that each sees every phase of its buffer's barriers
+    if (warp - kCW - 1 >= nred) return;
+    const int par = warp - kCW - 1;
+    int rph = 0;
+    for (int i = par; i < n_items; i += nred, rph ^= 1) {
       const Item it = item_of(pl, bl, i);
-      const int par = i & 1;
-      wait_relaxed(rfull0 + par * 8, (i >> 1) & 1, status, dead, pl.flags & 1);
+      wait_relaxed(rfull0 + par * 8, rph, status, dead, pl.flags & 1);
       const uint32_t red_base = red_u32 + par * red_buf;
       const int w_hi = min(it.w_hi, n_active);
       // full layout: lane (gid, tig) holds rows gid, gid+8 x activation rows 2 tig, 2 tig + 1 of row block rb
       // compact layout (M <= 2): lane l < 16 holds (rb = l >> 3, gid = l & 7): rows gid, gid+8 x activation rows 0, 1
-      float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
-      if (pl.compact) {
-        if (lane < 16)
+      float4 acc[RB][MB];
+#pragma unroll
+      for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) acc[rb][mb] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (pl.compact) {   // MB == 1
+        if (lane < 8 * RB)
           for (int w = it.w_lo; w < w_hi; ++w) {
-            const float4 v = lds_v4f(red_base + (w * 16 + lane) * 16);
-            acc[0].x += v.x; acc[0].y += v.y; acc[0].z += v.z; acc[0].w += v.w;
+            const float4 v = lds_v4f(red_base + (w * (8 * RB) + lane) * 16);
+            acc[0][0].x += v.x; acc[0][0].y += v.y; acc[0][0].z += v.z; acc[0][0].w += v.w;
           }
       } else {
         for (int w = it.w_lo; w < w_hi; ++w) {
 #pragma unroll
-          for (int rb = 0; rb < 2; ++rb) {
-            const float4 v = lds_v4f(red_base + ((w * 2 + rb) * 32 + lane) * 16);
-            acc[rb].x += v.x; acc[rb].y += v.y; acc[rb].z += v.z; acc[rb].w += v.w;
-          }
+          for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb) {
+              const float4 v = lds_v4f(red_base + (((w * RB + rb) * MB + mb) * 32 + lane) * 16);
+              acc[rb][mb].x += v.x; acc[rb][mb].y += v.y; acc[rb][mb].z += v.z; acc[rb][mb].w += v.w;
+            }
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(rempty0 + par * 8);   // the exchange buffer may be overwritten
 
-      // (local row, activation row) of the values this lane holds: out[k], k = 0..7
-      float out[8] = {acc[0].x, acc[0].y, acc[0].z, acc[0].w, acc[1].x, acc[1].y, acc[1].z, acc[1].w};
-      const int nvals = pl.compact ? (lane < 16 ? 4 : 0) : 8;
+      // (local row, activation row) of the values this lane holds: out[k], k = (rb * MB + mb) * 4 + e
+      constexpr int NV = 4 * RB * MB;
+      float out[NV];
+#pragma unroll
+      for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          const int k0 = (rb * MB + mb) * 4;
+          out[k0] = acc[rb][mb].x; out[k0 + 1] = acc[rb][mb].y; out[k0 + 2] = acc[rb][mb].z; out[k0 + 3] = acc[rb][mb].w;
+        }
+      const int nvals = pl.compact ? (lane < 8 * RB ? 4 : 0) : NV;
       auto row_of = [&](int k) {
-        return pl.compact ? (lane >> 3) * 16 + (lane & 7) + 8 * ((k >> 1) & 1) : (k >> 2) * 16 + gid + 8 * ((k >> 1) & 1);
+        return pl.compact ? (lane >> 3) * 16 + (lane & 7) + 8 * ((k >> 1) & 1) : (k / (4 * MB)) * 16 + gid + 8 * ((k >> 1) & 1);
       };
-      auto m_of = [&](int k) { return pl.compact ? (k & 1) : tig * 2 + (k & 1); };
+      auto m_of = [&](int k) { return pl.compact ? (k & 1) : ((k >> 2) % MB) * 8 + tig * 2 + (k & 1); };
 
       // contributions that meet in this row tile: one per K slice, P per slice for a left-over tile
       const int contrib = pl.n_slices * (it.tile >= pl.n_full ? pl.P : 1);
-      const int row0 = it.tile * kRowsPerTile;
+      const int row0 = it.tile * R;
       if (contrib == 1) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < NV; ++k) {
           const int n = row0 + row_of(k), m = m_of(k);
           if (k < nvals && m < p.M) {
             float v = out[k];
@@ -227,11 +249,11 @@ __global__ void __launch_bounds__((kCW + 1 + N_EPI) * 32, 1) w4a16_gemv_persist_
           }
         }
       } else {
-        float* mine = p.partial + ((size_t)slice * pl.units + it.unit) * p.M * kRowsPerTile;
+        float* mine = p.partial + ((size_t)slice * pl.units + it.unit) * p.M * R;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < NV; ++k) {
           const int m = m_of(k);
-          if (k < nvals && m < p.M) __stcg(mine + m * kRowsPerTile + row_of(k), out[k]);
+          if (k < nvals && m < p.M) __stcg(mine + m * R + row_of(k), out[k]);
         }
         __threadfence();
         __syncwarp();
@@ -246,34 +268,35 @@ __global__ void __launch_bounds__((kCW + 1 + N_EPI) * 32, 1) w4a16_gemv_persist_
           const int per_slice = it.tile < pl.n_full ? 1 : pl.P;   // a power of two
           const int lg = 31 - __clz(per_slice);
           const int u0 = it.tile < pl.n_full ? it.tile : pl.n_full + (it.tile - pl.n_full) * pl.P;
-          // MI activation rows x eight contributions in flight at a time
+          // MI activation rows x C contributions in flight at a time
           auto final_rows = [&](auto mi_tag) {
             constexpr int MI = decltype(mi_tag)::value;
+            constexpr int C = MI <= 4 ? 8 : 4;   // contributions per batch: 32 loads in flight at most
             for (int m0 = 0; m0 < p.M; m0 += MI) {
               float v[MI];
 #pragma unroll
               for (int mi = 0; mi < MI; ++mi) v[mi] = 0.f;
-              for (int c0 = 0; c0 < contrib; c0 += 8) {
-                float t[MI][8];
+              for (int c0 = 0; c0 < contrib; c0 += C) {
+                float t[MI][C];
 #pragma unroll
                 for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
-                  for (int c = 0; c < 8; ++c) {
+                  for (int c = 0; c < C; ++c) {
                     const int cc = c0 + c, m = m0 + mi;
                     const int sl = cc >> lg, kp = cc & (per_slice - 1);
-                    t[mi][c] = (cc < contrib && m < p.M)
-                                   ? __ldcg(p.partial + (((size_t)sl * pl.units + u0 + kp) * p.M + m) * kRowsPerTile + lane)
+                    t[mi][c] = (cc < contrib && m < p.M && lane < R)
+                                   ? __ldcg(p.partial + (((size_t)sl * pl.units + u0 + kp) * p.M + m) * R + lane)
                                    : 0.f;
                   }
 #pragma unroll
                 for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
-                  for (int c = 0; c < 8; ++c) v[mi] += t[mi][c];
+                  for (int c = 0; c < C; ++c) v[mi] += t[mi][c];
               }
 #pragma unroll
               for (int mi = 0; mi < MI; ++mi) {
                 const int m = m0 + mi;
-                if (m < p.M) {
+                if (m < p.M && lane < R) {
                   float r = v[mi];
                   if (bias) r += to_float<T>(bias[n]);
                   yg[(size_t)m * p.ldy + n] = from_float<T>(r);
@@ -283,7 +306,8 @@ __global__ void __launch_bounds__((kCW + 1 + N_EPI) * 32, 1) w4a16_gemv_persist_
           };
           if (p.M == 1) final_rows(std::integral_constant<int, 1>{});
           else if (p.M == 2) final_rows(std::integral_constant<int, 2>{});
-          else final_rows(std::integral_constant<int, 4>{});
+          else if (p.M <= 4) final_rows(std::integral_constant<int, 4>{});
+          else final_rows(std::integral_constant<int, 8>{});
           __syncwarp();
           if (lane == 0) p.counters[it.tile] = 0;
         }
@@ -294,26 +318,37 @@ __global__ void __launch_bounds__((kCW + 1 + N_EPI) * 32, 1) w4a16_gemv_persist_
 
   // ================= consumers =================
   // scale / zero of this warp's two consecutive groups for rows (rb*16 + gid + 8h) of an item
-  float ms[kStepsPW][2][2], mz[kStepsPW][2][2];
-  const bool has_share = (warp + 1) * kStepsPW <= sps_this;
+  float ms[SPW][RB][2], mz[SPW][RB][2];
+  const bool has_share = (warp + 1) * SPW <= sps_this;
   auto warp_active = [&](const Item& it) { return has_share && warp >= it.w_lo && warp < it.w_hi; };
   auto load_meta = [&](const Item& it) {
-    const int g0 = s0 + warp * kStepsPW;
+    const int g0 = s0 + warp * SPW;
 #pragma unroll
-    for (int rb = 0; rb < 2; ++rb)
+    for (int rb = 0; rb < RB; ++rb)
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const size_t idx = (size_t)(it.tile * kRowsPerTile + rb * 16 + gid + 8 * h) * p.ngroups + g0;
-        if (META16) {
-          const uint2 t2 = __ldg(reinterpret_cast<const uint2*>(p.meta_h2 + idx));
-          const __half2 h0 = *reinterpret_cast<const __half2*>(&t2.x), h1 = *reinterpret_cast<const __half2*>(&t2.y);
-          ms[0][rb][h] = __low2float(h0); mz[0][rb][h] = __high2float(h0);
-          ms[1][rb][h] = __low2float(h1); mz[1][rb][h] = __high2float(h1);
+        const size_t idx = (size_t)(it.tile * R + rb * 16 + gid + 8 * h) * p.ngroups + g0;
+        if (SPW == 2) {
+          if (META16) {
+            const uint2 t2 = __ldg(reinterpret_cast<const uint2*>(p.meta_h2 + idx));
+            const __half2 h0 = *reinterpret_cast<const __half2*>(&t2.x), h1 = *reinterpret_cast<const __half2*>(&t2.y);
+            ms[0][rb][h] = __low2float(h0); mz[0][rb][h] = __high2float(h0);
+            ms[SPW - 1][rb][h] = __low2float(h1); mz[SPW - 1][rb][h] = __high2float(h1);
+          } else {
+            const float2 a = __ldg(reinterpret_cast<const float2*>(p.scale + idx));
+            const float2 c = __ldg(reinterpret_cast<const float2*>(p.zero + idx));
+            ms[0][rb][h] = a.x; ms[SPW - 1][rb][h] = a.y;
+            mz[0][rb][h] = c.x; mz[SPW - 1][rb][h] = c.y;
+          }
         } else {
-          const float2 a = __ldg(reinterpret_cast<const float2*>(p.scale + idx));
-          const float2 c = __ldg(reinterpret_cast<const float2*>(p.zero + idx));
-          ms[0][rb][h] = a.x; ms[1][rb][h] = a.y;
-          mz[0][rb][h] = c.x; mz[1][rb][h] = c.y;
+          if (META16) {
+            const uint32_t t1 = __ldg(p.meta_h2 + idx);
+            const __half2 h0 = *reinterpret_cast<const __half2*>(&t1);
+            ms[0][rb][h] = __low2float(h0); mz[0][rb][h] = __high2float(h0);
+          } else {
+            ms[0][rb][h] = __ldg(p.scale + idx);
+            mz[0][rb][h] = __ldg(p.zero + idx);
+          }
         }
       }
   };
@@ -336,50 +371,70 @@ __global__ void __launch_bounds__((kCW + 1 + N_EPI) * 32, 1) w4a16_gemv_persist_
 
   // Offsets into the shared array (plain C++ loads from it compile to ld.shared and, unlike asm, leave
   // the compiler free to software-pipeline the four independent (step, row block) units of an item).
-  const int w_off = gid * pitch + warp * (kStepsPW * 64) + tig * 16;
-  const int tab_off = (int)(reinterpret_cast<unsigned char*>(tab) - smem) + warp * (kStepsPW * kTabCols * 8) + tig * 16;
-  const int x_off = (gid < p.M ? (int)(xs - smem) + gid * xstride + warp * (kStepsPW * 256)
-                               : (int)(reinterpret_cast<unsigned char*>(zero_blk) - smem)) + tig * 16;
-  const int xstep = gid < p.M ? 256 : 0;
+  const int w_off = gid * pitch + warp * (SPW * 64) + tig * 16;
+  const int tab_off = (int)(reinterpret_cast<unsigned char*>(tab) - smem) + warp * (SPW * kTabCols * 8) + tig * 16;
+  int x_off[MB], xstep[MB];
+#pragma unroll
+  for (int mb = 0; mb < MB; ++mb) {
+    const int m = mb * 8 + gid;   // rows beyond M read a block of zeros that does not advance with the step
+    x_off[mb] = (m < p.M ? (int)(xs - smem) + m * xstride + warp * (SPW * 256)
+                         : (int)(reinterpret_cast<unsigned char*>(zero_blk) - smem)) + tig * 16;
+    xstep[mb] = m < p.M ? 256 : 0;
+  }
 
-  int slot = 0, ph = 0;
+  int slot = 0, ph = 0, par = 0, rph = 0;
   for (int i = 0; i < n_items; ++i) {
-    const int par = i & 1;
     wait_or_die(full0 + slot * 8, ph, status, dead);
-    const unsigned char* stage = smem + slot * kRowsPerTile * pitch + w_off;
-    float yacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const unsigned char* stage = smem + slot * R * pitch + w_off;
+    float yacc[RB][MB][4];
+#pragma unroll
+    for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) yacc[rb][mb][e] = 0.f;
     if (active) {   // warp-uniform; one basic block for the whole item
 #pragma unroll
-      for (int j = 0; j < kStepsPW; ++j) {
-        uint4 xb[4];
+      for (int j = 0; j < SPW; ++j) {
+        uint4 xb[MB][4];
+        float4 tt[MB];   // E0 SX0 E1 SX1 of activation rows mb*8 + 2 tig, + 1
 #pragma unroll
-        for (int q = 0; q < 4; ++q) xb[q] = *reinterpret_cast<const uint4*>(smem + x_off + j * xstep + q * 64);
-        const float4 tt = *reinterpret_cast<const float4*>(smem + tab_off + j * (kTabCols * 8));  // E0 SX0 E1 SX1
+        for (int mb = 0; mb < MB; ++mb) {
 #pragma unroll
-        for (int rb = 0; rb < 2; ++rb) {
+          for (int q = 0; q < 4; ++q) xb[mb][q] = *reinterpret_cast<const uint4*>(smem + x_off[mb] + j * xstep[mb] + q * 64);
+          tt[mb] = *reinterpret_cast<const float4*>(smem + tab_off + j * (kTabCols * 8) + mb * 64);
+        }
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb) {
           const uint4 wa4 = *reinterpret_cast<const uint4*>(stage + rb * 16 * pitch + j * 64);
           const uint4 wb4 = *reinterpret_cast<const uint4*>(stage + (rb * 16 + 8) * pitch + j * 64);
           const uint32_t wa[4] = {wa4.x, wa4.y, wa4.z, wa4.w};
           const uint32_t wb[4] = {wb4.x, wb4.y, wb4.z, wb4.w};
-          float d0[4], d1[4];
+          float d0[MB][4], d1[MB][4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint32_t pa[4], pb[4];
             Nibbles<T>::unpack(wa[q], pa);
             Nibbles<T>::unpack(wb[q], pb);
-            if (q == 0) {
-              mma16816_zero<T>(d0, pa[0], pb[0], pa[1], pb[1], xb[q].x, xb[q].y);
-              mma16816_zero<T>(d1, pa[2], pb[2], pa[3], pb[3], xb[q].z, xb[q].w);
-            } else {
-              mma16816<T>(d0, pa[0], pb[0], pa[1], pb[1], xb[q].x, xb[q].y);
-              mma16816<T>(d1, pa[2], pb[2], pa[3], pb[3], xb[q].z, xb[q].w);
+#pragma unroll
+            for (int mb = 0; mb < MB; ++mb) {
+              if (q == 0) {
+                mma16816_zero<T>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][q].x, xb[mb][q].y);
+                mma16816_zero<T>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][q].z, xb[mb][q].w);
+              } else {
+                mma16816<T>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][q].x, xb[mb][q].y);
+                mma16816<T>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][q].z, xb[mb][q].w);
+              }
             }
           }
           const float sA = ms[j][rb][0], zA = mz[j][rb][0], sB = ms[j][rb][1], zB = mz[j][rb][1];
-          yacc[rb][0] = fmaf(sA, fmaf(-zA, tt.y, (d0[0] + d1[0]) - tt.x), yacc[rb][0]);
-          yacc[rb][1] = fmaf(sA, fmaf(-zA, tt.w, (d0[1] + d1[1]) - tt.z), yacc[rb][1]);
-          yacc[rb][2] = fmaf(sB, fmaf(-zB, tt.y, (d0[2] + d1[2]) - tt.x), yacc[rb][2]);
-          yacc[rb][3] = fmaf(sB, fmaf(-zB, tt.w, (d0[3] + d1[3]) - tt.z), yacc[rb][3]);
+#pragma unroll
+          for (int mb = 0; mb < MB; ++mb) {
+            yacc[rb][mb][0] = fmaf(sA, fmaf(-zA, tt[mb].y, (d0[mb][0] + d1[mb][0]) - tt[mb].x), yacc[rb][mb][0]);
+            yacc[rb][mb][1] = fmaf(sA, fmaf(-zA, tt[mb].w, (d0[mb][1] + d1[mb][1]) - tt[mb].z), yacc[rb][mb][1]);
+            yacc[rb][mb][2] = fmaf(sB, fmaf(-zB, tt[mb].y, (d0[mb][2] + d1[mb][2]) - tt[mb].x), yacc[rb][mb][2]);
+            yacc[rb][mb][3] = fmaf(sB, fmaf(-zB, tt[mb].w, (d0[mb][3] + d1[mb][3]) - tt[mb].z), yacc[rb][mb][3]);
+          }
         }
       }
     }
@@ -393,42 +448,55 @@ __global__ void __launch_bounds__((kCW + 1 + N_EPI) * 32, 1) w4a16_gemv_persist_
       if (active) load_meta(cur);
     }
     // ---- partial sums to the exchange buffer `par`; the epilogue warp takes it from there ----
-    wait_or_die(rempty0 + par * 8, ((i >> 1) & 1) ^ 1, status, dead);
+    wait_or_die(rempty0 + par * 8, rph ^ 1, status, dead);
     if (was_active) {
       const uint32_t red_base = red_u32 + par * red_buf;
-      if (pl.compact) {
+      if (pl.compact) {   // MB == 1
         if (tig == 0) {
-          sts_v4f(red_base + ((warp * 2 + 0) * 8 + gid) * 16, yacc[0][0], yacc[0][1], yacc[0][2], yacc[0][3]);
-          sts_v4f(red_base + ((warp * 2 + 1) * 8 + gid) * 16, yacc[1][0], yacc[1][1], yacc[1][2], yacc[1][3]);
+#pragma unroll
+          for (int rb = 0; rb < RB; ++rb)
+            sts_v4f(red_base + ((warp * RB + rb) * 8 + gid) * 16, yacc[rb][0][0], yacc[rb][0][1], yacc[rb][0][2], yacc[rb][0][3]);
         }
       } else {
-        sts_v4f(red_base + ((warp * 2 + 0) * 32 + lane) * 16, yacc[0][0], yacc[0][1], yacc[0][2], yacc[0][3]);
-        sts_v4f(red_base + ((warp * 2 + 1) * 32 + lane) * 16, yacc[1][0], yacc[1][1], yacc[1][2], yacc[1][3]);
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+          for (int mb = 0; mb < MB; ++mb)
+            sts_v4f(red_base + (((warp * RB + rb) * MB + mb) * 32 + lane) * 16, yacc[rb][mb][0], yacc[rb][mb][1], yacc[rb][mb][2],
+                    yacc[rb][mb][3]);
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(rfull0 + par * 8);
+    if (++par == nred) { par = 0; rph ^= 1; }
   }
 }
 
 constexpr size_t kPersistSmemCap = 220 * 1024;
+constexpr int kStepsPW = 2;   // steps per consumer warp and slice: slices of up to 4096 columns
 
-size_t persist_smem(int M, int sps, int depth) {
-  const size_t red = (size_t)2 * kCW * 2 * (M <= 2 ? 8 : 32) * 16;
-  return (size_t)depth * kRowsPerTile * (sps * 64 + 64) + (size_t)M * (sps * 256 + 64) + (size_t)sps * kTabCols * sizeof(float2) + red +
-         256 + (2 * kMaxDepth + 4) * 8 + 128;
+size_t persist_smem(int M, int sps, int depth, int rows, int red_bufs) {
+  const int mb = M <= 8 ? 1 : 2;
+  const size_t red = (size_t)red_bufs * kCW * (rows / 16) * mb * (M <= 2 ? 8 : 32) * 16;
+  return (size_t)depth * rows * (sps * 64 + 64) + (size_t)M * (sps * 256 + 64) + (size_t)sps * kTabCols * sizeof(float2) + red + 256 +
+         (2 * kMaxDepth + 4) * 8 + 128;
 }
 
 int g_persist_depth = 0;   // 0 = as deep as fits
-int g_persist_epi = 0;     // 0 = automatic
-int g_persist_flags = 3;
+int g_persist_flags = 1;
 
+// Tile height and exchange buffers by the number of activation rows: 32-row tiles while one block of
+// eight activation rows is enough (two exchange buffers if they fit, else one), 16-row tiles for
+// nine to sixteen rows (two blocks: the activations take twice the shared memory, the tile half).
 StreamPlan make_stream_plan(int M, int N, int K) {
   StreamPlan pl{};
   const int steps = K >> 7;
-  pl.n_tiles = N / kRowsPerTile;
-  pl.n_slices = (steps + kSliceSteps - 1) / kSliceSteps;
-  pl.sps = ((steps + pl.n_slices - 1) / pl.n_slices + 1) & ~1;
+  const int slice_steps = kCW * kStepsPW;
+  pl.spw = kStepsPW;
+  pl.rows = M <= 8 ? 32 : 16;
+  pl.n_tiles = N / pl.rows;
+  pl.n_slices = (steps + slice_steps - 1) / slice_steps;
+  pl.sps = ((steps + pl.n_slices - 1) / pl.n_slices + 1) & ~1;   // even: K % 512 == 0 keeps every slice whole
   pl.n_slices = (steps + pl.sps - 1) / pl.sps;
   pl.gs = kGrid / pl.n_slices;
   if (pl.gs < 1) pl.gs = 1;
@@ -445,60 +513,66 @@ StreamPlan make_stream_plan(int M, int N, int K) {
   pl.units = pl.n_full + pl.pieces;
   pl.compact = M <= 2 ? 1 : 0;
   pl.flags = g_persist_flags;
-  pl.n_epi = g_persist_epi ? g_persist_epi : 2;
+  pl.red_bufs = persist_smem(M, pl.sps, 2, pl.rows, 2) <= kPersistSmemCap ? 2 : 1;
   pl.depth = 2;
   const int want = g_persist_depth ? g_persist_depth : kMaxDepth;
-  while (pl.depth < want && pl.depth < pl.q + (pl.pieces ? 1 : 0) && persist_smem(M, pl.sps, pl.depth + 1) <= kPersistSmemCap) ++pl.depth;
+  while (pl.depth < want && pl.depth < pl.q + (pl.pieces ? 1 : 0) &&
+         persist_smem(M, pl.sps, pl.depth + 1, pl.rows, pl.red_bufs) <= kPersistSmemCap)
+    ++pl.depth;
   return pl;
 }
+
+template <typename X>
+struct TypeTag {
+  using type = X;
+};
 
 }  // namespace
 
 int g_persist_min_items = 96;
 
-void gemv_persist_set_min_items(int n) { g_persist_min_items = n >= 100 ? 96 : n; g_persist_flags = n >= 100 ? (n - 100) & 3 : 3; }
+void gemv_persist_set_min_items(int n) { g_persist_min_items = n >= 100 ? 96 : n; g_persist_flags = n >= 100 ? (n - 100) & 1 : 1; }
 void gemv_persist_set_depth(int d) { g_persist_depth = d; }
-void gemv_persist_set_epilogue_warps(int n) { g_persist_epi = (n == 1 || n == 2) ? n : 0; }
 
 // Layers the persistent schedule serves: 128-column groups, whole 32-row tiles, activations that fit in
 // shared memory next to the weight ring, and enough items to occupy the machine.
 bool gemv_persist_supported(int M, int N, int K, int G) {
-  if (G != 128 || M > 8 || (K % 512) != 0 || (N % kRowsPerTile) != 0 || N <= 0) return false;
+  if (G != 128 || M > 16 || (K % 512) != 0 || (N % kMaxRows) != 0 || N <= 0) return false;
   const StreamPlan pl = make_stream_plan(M, N, K);
   if (pl.n_slices > kGrid) return false;
-  if ((long long)pl.n_tiles * pl.n_slices < g_persist_min_items) return false;
+  if ((long long)(N / kMaxRows) * pl.n_slices < g_persist_min_items) return false;
   // One whole item per CTA plus a piece of another is all ramp and cross-CTA reduction: such layers are
   // faster as independent tiles (measured: 6144 x 4096 takes 8.1 us here, 6.4 us there).
-  if (pl.n_slices == 1 && pl.q == 1 && pl.pieces > 0) return false;
+  if (M <= 4 && pl.n_slices == 1 && pl.q == 1 && pl.pieces > 0) return false;
   if ((size_t)pl.n_tiles >= kStatusIndex) return false;
-  return persist_smem(M, pl.sps, 2) <= kPersistSmemCap;
+  return persist_smem(M, pl.sps, 2, pl.rows, pl.red_bufs) <= kPersistSmemCap;
 }
 
-// fp32 words of workspace behind the prepared activations: one [M][32] block per contribution
+// fp32 words of workspace behind the prepared activations: one [M][rows] block per contribution
 size_t gemv_persist_partial_floats(int M, int N, int K) {
   const StreamPlan pl = make_stream_plan(M, N, K);
-  return (size_t)pl.n_slices * pl.units * M * kRowsPerTile;
+  return (size_t)pl.n_slices * pl.units * M * pl.rows;
 }
 
 int gemv_persist_launch(const gemv::GemvParams& p, int x_dtype, cudaStream_t stream) {
   using namespace gemv;
   const StreamPlan pl = make_stream_plan(p.M, p.N, p.K);
-  const size_t smem = persist_smem(p.M, pl.sps, pl.depth);
+  const size_t smem = persist_smem(p.M, pl.sps, pl.depth, pl.rows, pl.red_bufs);
   auto launch = [&](auto kern) -> int {
     // set on every launch: the kernels share one function-pointer type, so a per-lambda flag would not do
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPersistSmemCap) != cudaSuccess)
       return PARE_ERR_CUDA;
-    return launch_pdl(kern, dim3(pl.n_slices * pl.gs), dim3((kCW + 1 + pl.n_epi) * 32), smem, stream, p, pl);
+    return launch_pdl(kern, dim3(pl.n_slices * pl.gs), dim3(kThreads), smem, stream, p, pl);
+  };
+  auto pick = [&](auto t_tag, auto m16_tag) -> int {
+    using TT = typename decltype(t_tag)::type;
+    constexpr bool M16 = decltype(m16_tag)::value;
+    return pl.rows == 32 ? launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 2, 1>)
+                         : launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 1, 2>);
   };
   const bool m16 = p.meta_h2 != nullptr;
-  if (pl.n_epi == 2) {
-    if (x_dtype == PARE_F16)
-      return m16 ? launch(w4a16_gemv_persist_kernel<__half, true, 2>) : launch(w4a16_gemv_persist_kernel<__half, false, 2>);
-    return m16 ? launch(w4a16_gemv_persist_kernel<__nv_bfloat16, true, 2>) : launch(w4a16_gemv_persist_kernel<__nv_bfloat16, false, 2>);
-  }
-  if (x_dtype == PARE_F16)
-    return m16 ? launch(w4a16_gemv_persist_kernel<__half, true, 1>) : launch(w4a16_gemv_persist_kernel<__half, false, 1>);
-  return m16 ? launch(w4a16_gemv_persist_kernel<__nv_bfloat16, true, 1>) : launch(w4a16_gemv_persist_kernel<__nv_bfloat16, false, 1>);
+  if (x_dtype == PARE_F16) return m16 ? pick(TypeTag<__half>{}, std::true_type{}) : pick(TypeTag<__half>{}, std::false_type{});
+  return m16 ? pick(TypeTag<__nv_bfloat16>{}, std::true_type{}) : pick(TypeTag<__nv_bfloat16>{}, std::false_type{});
 }
 
 }  // namespace pare
