@@ -250,7 +250,12 @@ def time_events(fn, steps: int, warmup: int, world: int) -> float:
 def layer_table(stack, peak: float, batches=(1, 4, 16)) -> dict:
     """us/layer and fraction of the HBM peak for each fused projection of the stack, timed alone:
     one CUDA graph of n_layers launches over the n_layers DISTINCT weight sets (hundreds of MB, so
-    nothing is served from L2), average duration per launch from CUDA events."""
+    nothing is served from L2), average duration per launch from CUDA events.  ``us_per_layer`` is the
+    public ``QuantizedLinear.forward`` (activation preparation launch + streaming kernel); ``us_kernel``
+    the streaming kernel alone on prepared activations, which is what runs inside the decode stack
+    (there the producer of the activation writes them prepared)."""
+    from pare_b200.kernels.matmul_int4 import prepare
+
     table = {}
     kinds = {"qkv": lambda b: b.qkv, "o": lambda b: b.o, "gate_up": lambda b: b.gate_up, "down": lambda b: b.down}
     for name, pick in kinds.items():
@@ -258,17 +263,29 @@ def layer_table(stack, peak: float, batches=(1, 4, 16)) -> dict:
         n, k = layers[0].out_features, layers[0].in_features
         for m in batches:
             x = torch.randn(m, k, device=stack.device, dtype=stack.dtype)
+            prep = prepare(x) if layers[0].supports_prepared(m) else None
 
-            def run():
+            def run_public():
                 for layer in layers:
                     layer(x)
-            g, _ = capture(run)
-            reps = 20
-            sec = time_events(g.replay, reps, 3, 1)
-            us = sec / (reps * len(layers)) * 1e6
+
+            def run_kernel():
+                for layer in layers:
+                    layer.forward_prepared(prep)
+
+            entry = {}
+            for key, fn in (("us_per_layer", run_public), ("us_kernel", run_kernel if prep is not None else None)):
+                if fn is None:
+                    continue
+                g, _ = capture(fn)
+                reps = 20
+                sec = time_events(g.replay, reps, 3, 1)
+                entry[key] = round(sec / (reps * len(layers)) * 1e6, 3)
+                del g
+            us = entry.get("us_kernel", entry["us_per_layer"])
             gbs = w4a16_bytes(m, n, k) / us / 1e3
-            table[f"{name}_{n}x{k}_m{m}"] = {"us_per_layer": round(us, 3), "gbs": round(gbs, 1), "frac_hbm": round(gbs / peak, 4)}
-            del g
+            entry.update({"gbs": round(gbs, 1), "frac_hbm": round(gbs / peak, 4)})
+            table[f"{name}_{n}x{k}_m{m}"] = entry
     return table
 
 

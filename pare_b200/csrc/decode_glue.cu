@@ -17,8 +17,8 @@ constexpr int kVecs = 8;  // rows up to 256 * 8 * 8 = 16384 elements
 template <typename T>
 __global__ void __launch_bounds__(kNormThreads) rmsnorm_residual_kernel(const T* __restrict__ x, const T* __restrict__ delta,
                                                                         const T* __restrict__ weight, T* resid_out,
-                                                                        T* __restrict__ y, T* __restrict__ prep_xp,
-                                                                        float2* __restrict__ prep_tab, int n, float eps) {
+                                                                        T* __restrict__ y, __half* __restrict__ prep_xp,
+                                                                        float4* __restrict__ prep_tab, int n, float eps) {
   pdl_launch_dependents();
   const size_t row = (size_t)blockIdx.x * n;
   const int nvec = n >> 3;
@@ -87,11 +87,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_residual_kernel(const T*
     }
     if (prep_xp) {   // n % 128 == 0: the sixteen lanes of a step are live or idle together
       const int st = v >> 4, c = v & 15;
-      float lo = 0.f, hi = 0.f;
-      if (live) prep_chunk8<T>(o, prep_xp + row + st * 128, c, lo, hi);
-      lo = half_warp_sum(lo);
-      hi = half_warp_sum(hi);
-      if (live && c == 0) prep_tab[(size_t)st * gemv::kTabCols + blockIdx.x] = prep_tab_entry<T>(lo, hi);
+      prep_store_step<T>(o, live, prep_xp + row + st * 128, c, prep_tab + (size_t)st * gemv::kTabCols + blockIdx.x);
     }
   }
 }
@@ -99,7 +95,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_residual_kernel(const T*
 // thread = 8 columns of one row
 template <typename T>
 __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out,
-                                                       T* __restrict__ prep_xp, float2* __restrict__ prep_tab, int n,
+                                                       __half* __restrict__ prep_xp, float4* __restrict__ prep_tab, int n,
                                                        int64_t ld, int vec_ok) {
   pdl_launch_dependents();
   pdl_wait();
@@ -147,27 +143,23 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gat
   }
   if (prep_xp) {   // n % 128 == 0
     const int st = v >> 4, c = v & 15;
-    float lo = 0.f, hi = 0.f;
-    if (live) prep_chunk8<T>(o, prep_xp + (size_t)row * n + st * 128, c, lo, hi);
-    lo = half_warp_sum(lo);
-    hi = half_warp_sum(hi);
-    if (live && c == 0) prep_tab[(size_t)st * gemv::kTabCols + row] = prep_tab_entry<T>(lo, hi);
+    prep_store_step<T>(o, live, prep_xp + (size_t)row * n + st * 128, c, prep_tab + (size_t)st * gemv::kTabCols + row);
   }
 }
 
 template <typename T>
 int rmsnorm_launch(const void* x, const void* delta, const void* weight, void* resid_out, void* y, void* prepared, int rows,
                    int n, float eps, cudaStream_t s) {
-  T* xp = reinterpret_cast<T*>(prepared);
-  float2* tab = prepared ? reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(prepared) + prepared_tab_offset(rows, n)) : nullptr;
+  __half* xp = reinterpret_cast<__half*>(prepared);
+  float4* tab = prepared ? reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(prepared) + prepared_tab_offset(rows, n)) : nullptr;
   return launch_pdl(rmsnorm_residual_kernel<T>, dim3(rows), dim3(kNormThreads), 0, s, (const T*)x, (const T*)delta,
                     (const T*)weight, (T*)resid_out, (T*)y, xp, tab, n, eps);
 }
 
 template <typename T>
 int silu_launch(const void* gate_up, void* out, void* prepared, int rows, int n, int64_t ld, cudaStream_t s) {
-  T* xp = reinterpret_cast<T*>(prepared);
-  float2* tab = prepared ? reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(prepared) + prepared_tab_offset(rows, n)) : nullptr;
+  __half* xp = reinterpret_cast<__half*>(prepared);
+  float4* tab = prepared ? reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(prepared) + prepared_tab_offset(rows, n)) : nullptr;
   const int vec_ok = (n % 8 == 0) && (ld % 8 == 0) && aligned16(gate_up) && (out == nullptr || aligned16(out));
   const int nvec = (n + 7) / 8;
   return launch_pdl(silu_mul_kernel<T>, dim3((nvec + 255) / 256, rows), dim3(256), 0, s, (const T*)gate_up, (T*)out, xp, tab,

@@ -36,8 +36,8 @@ struct GemvParams {
   int steps_per_group;  // group_size / 128
   int steps_per_split;  // 128-column steps per CTA
   int splits;
-  void* xp;             // [M][K] activations in operand order (workspace)
-  float2* tabg;         // [K/128][kTabCols] (E, SX) per step and activation row (workspace)
+  void* xp;             // [M][K] fp16 activations in operand order (workspace)
+  float4* tabg;         // [K/128][kTabCols] (E, SX, g, -) per step and activation row (workspace)
   float* partial;       // [splits][M][N]
   int* counters;        // [row tiles]; counters[kStatusIndex] is the status word
   int x_vec_ok;

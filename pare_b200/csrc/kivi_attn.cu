@@ -78,7 +78,7 @@ struct AttnParams {
   void* out;           // may be NULL when prep_xp is given
   int64_t o_sb, o_sh;
   void* prep_xp;       // prepared activations [B][Hq * 128] + table, or NULL
-  float2* prep_tab;
+  float4* prep_tab;
   float sm_scale;
   int B, Hq, H, rep, group, cap, n_comp;
   int chunk, n_csplit, n_split;
@@ -512,11 +512,8 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
     if (p.prep_xp) {
       // query head (h * rep + hh) is step (h * rep + hh) of activation row b of the next linear
       const int K = p.Hq * kD, st = h * p.rep + hh;
-      float lo = 0.f, hi = 0.f;
-      if (active) prep_chunk8<T>(acc, reinterpret_cast<T*>(p.prep_xp) + (size_t)b * K + st * kD, c, lo, hi);
-      lo = half_warp_sum(lo);
-      hi = half_warp_sum(hi);
-      if (active && c == 0) p.prep_tab[(size_t)st * gemv::kTabCols + b] = prep_tab_entry<T>(lo, hi);
+      prep_store_step<T>(acc, active, reinterpret_cast<__half*>(p.prep_xp) + (size_t)b * K + st * kD, c,
+                         p.prep_tab + (size_t)st * gemv::kTabCols + b);
     }
   }
   if (threadIdx.x == 0) p.counters[bh] = 0;
@@ -626,7 +623,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
   p.out = out; p.o_sb = out_stride_b; p.o_sh = out_stride_h;
   if (prepared_out) {
     p.prep_xp = prepared_out;
-    p.prep_tab = reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(prepared_out) + prepared_tab_offset(B, Hq * kD));
+    p.prep_tab = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(prepared_out) + prepared_tab_offset(B, Hq * kD));
   }
   p.sm_scale = softmax_scale;
   p.B = B; p.Hq = Hq; p.H = H; p.rep = Hq / H; p.group = group; p.cap = cap; p.n_comp = n_comp;

@@ -40,61 +40,42 @@ namespace {
 using namespace gemv;
 
 // ---- activation preparation: once per call, not per CTA ------------------------------------
-// Writes x in the operand order of the inner product (per 128-column step: [word 0..3][quad 0..3]
-// chunks of 8 elements in slot order 0,4,1,5,2,6,3,7, odd code positions pre-divided by 16 for
-// fp16) and, per (step, row), E = what the mantissa offsets add to the accumulator and SX = the
-// plain sum of x (warp-shuffle reductions).  The act-order column gather and the run-time input
-// scale are applied here.  One warp per (row m, step).
+// Writes x as fp16 in the operand order of the inner product with its per-step table (prep.cuh).
+// The act-order column gather and the run-time input scale are applied here.  One half warp per
+// (row m, 128-column step), eight columns per thread.
 template <typename T>
 __global__ void __launch_bounds__(128) w4a16_prep_kernel(const GemvParams p) {
   pdl_launch_dependents();
   pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int item = (blockIdx.x * 128 + threadIdx.x) >> 4;   // (row, step)
+  const int c = threadIdx.x & 15;
   const int steps = p.K >> 7;
-  if (item >= p.M * steps) return;
-  const int m = item / steps, st = item - m * steps;
+  const bool live = item < p.M * steps;
+  const int m = live ? item / steps : 0, st = live ? item - m * steps : 0;
   const T* xg = reinterpret_cast<const T*>(p.x);
-  const int k = st * 128 + lane * 4;
-  float v[4];
-  if (p.col_perm == nullptr && p.x_vec_ok) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(xg + (size_t)m * p.ldx + k);
-    const T* e = reinterpret_cast<const T*>(&raw);
+  const int k = st * 128 + c * 8;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (live) {
+    if (p.col_perm == nullptr && p.x_vec_ok) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(xg + (size_t)m * p.ldx + k);
+      const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = to_float<T>(e[i]);
-    if (p.input_scale) {
+      for (int i = 0; i < 8; ++i) v[i] = to_float<T>(e[i]);
+      if (p.input_scale) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = __fdiv_rn(v[i], __ldg(p.input_scale + k + i));
-    }
-  } else {
+        for (int i = 0; i < 8; ++i) v[i] = __fdiv_rn(v[i], __ldg(p.input_scale + k + i));
+      }
+    } else {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int src = p.col_perm ? __ldg(p.col_perm + k + i) : k + i;
-      v[i] = to_float<T>(xg[(size_t)m * p.ldx + src]);
-      if (p.input_scale) v[i] = __fdiv_rn(v[i], __ldg(p.input_scale + src));
+      for (int i = 0; i < 8; ++i) {
+        const int src = p.col_perm ? __ldg(p.col_perm + k + i) : k + i;
+        v[i] = to_float<T>(xg[(size_t)m * p.ldx + src]);
+        if (p.input_scale) v[i] = __fdiv_rn(v[i], __ldg(p.input_scale + src));
+      }
     }
   }
-  // round to the operand type first (the activation the oracle sees), then apply the exact
-  // power-of-two prescale of the odd code positions
-  T b[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float r = to_float<T>(from_float<T>(v[i]));
-    b[i] = from_float<T>((i & 1) ? r * Nibbles<T>::kHiPrescale : r);
-  }
-  float lo = to_float<T>(b[0]) + to_float<T>(b[2]);
-  float hi = to_float<T>(b[1]) + to_float<T>(b[3]);
-  const int c = lane >> 1, hsel = lane & 1;
-  T* dst = reinterpret_cast<T*>(p.xp) + (size_t)m * p.K + st * 128 + ((c & 3) * 4 + (c >> 2)) * 8;
-  dst[0 + hsel] = b[0];
-  dst[2 + hsel] = b[1];
-  dst[4 + hsel] = b[2];
-  dst[6 + hsel] = b[3];
-  lo = warp_sum(lo);
-  hi = warp_sum(hi);
-  if (lane == 0)
-    p.tabg[(size_t)st * kTabCols + m] = make_float2(Nibbles<T>::kOffsetLo * lo + Nibbles<T>::kOffsetHi * hi,
-                                                    lo + hi / Nibbles<T>::kHiPrescale);
+  prep_store_step<T>(v, live, reinterpret_cast<__half*>(p.xp) + (size_t)m * p.K + st * 128, c,
+                     p.tabg + (size_t)st * kTabCols + m);
 }
 
 // RB = 16-row blocks per CTA (every warp takes all of them over its share of K: the activation
@@ -124,8 +105,9 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
   const int xstride = nst * 256 + 64;    // bytes per activation row; == 64 (mod 128)
   unsigned char* wt = smem;
   unsigned char* xs = wt + kTileRows * pitch;
-  float2* tab = reinterpret_cast<float2*>(xs + (size_t)xrows * xstride);           // [nst][kTabCols] (E, SX)
-  float* red = reinterpret_cast<float*>(tab + (size_t)nst * kTabCols);             // [WARPS][RB][MB][32][4]
+  float4* tab = reinterpret_cast<float4*>(xs + (size_t)xrows * xstride);           // [nst][kTabCols] (E, SX, g, -)
+  const int mcols = (xrows + 1) & ~1;   // table columns kept in shared memory: activation rows in use, rounded up to a pair
+  float* red = reinterpret_cast<float*>(tab + (size_t)nst * mcols);                // [WARPS][RB][MB][32][4]
   uint32_t* zero_blk = reinterpret_cast<uint32_t*>(red + WARPS * RB * MB * 128);   // 256 zero bytes
   uint64_t* bar_ptr = reinterpret_cast<uint64_t*>(zero_blk + 64);
   const uint32_t bar = smem_u32(bar_ptr);
@@ -190,7 +172,12 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
       for (int v = threadIdx.x; v < vec_per_row; v += THREADS) sts_v4(xs_u32 + m * xstride + v * 16, __ldcg(src + v));
     }
     const uint4* tg = reinterpret_cast<const uint4*>(p.tabg + (size_t)st0 * kTabCols);
-    for (int i = threadIdx.x; i < nst * (kTabCols / 2); i += THREADS) sts_v4(tab_u32 + i * 16, __ldcg(tg + i));
+    // only the table columns of activation rows in use; threads whose rows are beyond them read
+    // whatever follows (always inside this CTA's shared memory) and their results are discarded
+    for (int i = threadIdx.x; i < nst * mcols; i += THREADS) {
+      const int st = i / mcols, c = i - st * mcols;
+      sts_v4(tab_u32 + i * 16, __ldcg(tg + st * kTabCols + c));
+    }
   }
   __syncthreads();
   mbar_wait(bar, 0, status);
@@ -205,7 +192,7 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
       for (int i = 0; i < 4; ++i) yacc[rb][mb][i] = 0.f;
   {
     const uint32_t wa_addr = wt_u32 + gid * pitch + ws * 64 + tig * 16;
-    const uint32_t tab_addr = tab_u32 + ws * (kTabCols * 8) + tig * 16;
+    const uint32_t tab_addr = tab_u32 + ws * (mcols * 16) + tig * 32;
     uint32_t xaddr[MB], xstep[MB];
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) {
@@ -222,9 +209,12 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
         for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
           for (int i = 0; i < 4; ++i) xb[mb][i] = lds_v4(xaddr[mb] + j * xstep[mb] + i * 64);
-        float4 t[MB];
+        float4 t0[MB], t1[MB];   // (E, SX, g, -) of activation rows mb*8 + 2 tig and + 1
 #pragma unroll
-        for (int mb = 0; mb < MB; ++mb) t[mb] = lds_v4f(tab_addr + j * (kTabCols * 8) + mb * 64);  // E0 SX0 E1 SX1
+        for (int mb = 0; mb < MB; ++mb) {
+          t0[mb] = lds_v4f(tab_addr + j * (mcols * 16) + mb * 128);
+          t1[mb] = lds_v4f(tab_addr + j * (mcols * 16) + mb * 128 + 16);
+        }
 #pragma unroll
         for (int rb = 0; rb < RB; ++rb) {
           const uint4 wa4 = lds_v4(wa_addr + rb * 16 * pitch + j * 64);
@@ -235,16 +225,16 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint32_t pa[4], pb[4];
-            Nibbles<T>::unpack(wa[i], pa);
-            Nibbles<T>::unpack(wb[i], pb);
+            Nibbles<__half>::unpack(wa[i], pa);
+            Nibbles<__half>::unpack(wb[i], pb);
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
               if (i == 0) {
-                mma16816_zero<T>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][i].x, xb[mb][i].y);
-                mma16816_zero<T>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][i].z, xb[mb][i].w);
+                mma16816_zero<__half>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][i].x, xb[mb][i].y);
+                mma16816_zero<__half>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][i].z, xb[mb][i].w);
               } else {
-                mma16816<T>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][i].x, xb[mb][i].y);
-                mma16816<T>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][i].z, xb[mb][i].w);
+                mma16816<__half>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][i].x, xb[mb][i].y);
+                mma16816<__half>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][i].z, xb[mb][i].w);
               }
             }
           }
@@ -252,10 +242,10 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
           const float sA = ms[j][rb][0], zA = mz[j][rb][0], sB = ms[j][rb][1], zB = mz[j][rb][1];
 #pragma unroll
           for (int mb = 0; mb < MB; ++mb) {
-            yacc[rb][mb][0] = fmaf(sA, fmaf(-zA, t[mb].y, (d0[mb][0] + d1[mb][0]) - t[mb].x), yacc[rb][mb][0]);
-            yacc[rb][mb][1] = fmaf(sA, fmaf(-zA, t[mb].w, (d0[mb][1] + d1[mb][1]) - t[mb].z), yacc[rb][mb][1]);
-            yacc[rb][mb][2] = fmaf(sB, fmaf(-zB, t[mb].y, (d0[mb][2] + d1[mb][2]) - t[mb].x), yacc[rb][mb][2]);
-            yacc[rb][mb][3] = fmaf(sB, fmaf(-zB, t[mb].w, (d0[mb][3] + d1[mb][3]) - t[mb].z), yacc[rb][mb][3]);
+            yacc[rb][mb][0] = fmaf(sA * t0[mb].z, fmaf(-zA, t0[mb].y, (d0[mb][0] + d1[mb][0]) - t0[mb].x), yacc[rb][mb][0]);
+            yacc[rb][mb][1] = fmaf(sA * t1[mb].z, fmaf(-zA, t1[mb].y, (d0[mb][1] + d1[mb][1]) - t1[mb].x), yacc[rb][mb][1]);
+            yacc[rb][mb][2] = fmaf(sB * t0[mb].z, fmaf(-zB, t0[mb].y, (d0[mb][2] + d1[mb][2]) - t0[mb].x), yacc[rb][mb][2]);
+            yacc[rb][mb][3] = fmaf(sB * t1[mb].z, fmaf(-zB, t1[mb].y, (d0[mb][3] + d1[mb][3]) - t1[mb].x), yacc[rb][mb][3]);
           }
         }
       }
@@ -375,7 +365,7 @@ constexpr size_t kSmemCap = 110 * 1024;
 
 size_t gemv_smem(int M, int MB, int nst, int warps, int rb) {
   const int xrows = M < 8 * MB ? M : 8 * MB;
-  return (size_t)16 * rb * (nst * 64 + 64) + (size_t)xrows * (nst * 256 + 64) + (size_t)nst * kTabCols * sizeof(float2) +
+  return (size_t)16 * rb * (nst * 64 + 64) + (size_t)xrows * (nst * 256 + 64) + (size_t)nst * ((xrows + 1) & ~1) * sizeof(float4) +
          (size_t)warps * rb * MB * 128 * sizeof(float) + 256 + 16 + 128;
 }
 
@@ -489,7 +479,7 @@ int gemv_persist_launch(const gemv::GemvParams& p, int x_dtype, cudaStream_t str
 
 size_t prep_bytes(int M, int K) {  // prepared activations + step table, each rounded to 256 bytes
   const size_t xp = ((size_t)M * K * 2 + 255) / 256 * 256;
-  const size_t tab = ((size_t)(K / 128 + 1) * kTabCols * sizeof(float2) + 255) / 256 * 256;
+  const size_t tab = ((size_t)(K / 128 + 1) * kTabCols * sizeof(float4) + 255) / 256 * 256;
   return xp + tab;
 }
 
@@ -524,7 +514,7 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   p.K = K;
   p.ngroups = K / G;
   p.steps_per_group = G / 128;
-  p.x_vec_ok = ((reinterpret_cast<uintptr_t>(x) & 7u) == 0 && (ldx % 4) == 0) ? 1 : 0;
+  p.x_vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (ldx % 8) == 0) ? 1 : 0;
 
   Plan pl = make_plan(M, N, K, G);
   if (prepared) PARE_REQUIRE(pl.fast && col_perm == nullptr && input_scale == nullptr && aligned16(prepared), PARE_ERR_UNSUPPORTED);
@@ -542,22 +532,21 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   const size_t need = kCounterBytes + prep_bytes(M, K) +
                       (persist ? gemv_persist_partial_floats(M, N, K) * sizeof(float)
                                : (pl.splits > 1 ? (size_t)pl.splits * M * N * sizeof(float) : 0));
-  static_assert(sizeof(float2) == 8, "table entry");
   PARE_REQUIRE(workspace != nullptr && workspace_bytes >= need, PARE_ERR_WORKSPACE);
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   p.counters = reinterpret_cast<int*>(ws);
   p.xp = ws + kCounterBytes;
-  p.tabg = reinterpret_cast<float2*>(ws + kCounterBytes + ((size_t)M * K * 2 + 255) / 256 * 256);
+  p.tabg = reinterpret_cast<float4*>(ws + kCounterBytes + ((size_t)M * K * 2 + 255) / 256 * 256);
   p.partial = reinterpret_cast<float*>(ws + kCounterBytes + prep_bytes(M, K));
 
   if (prepared) {   // the producer of the activations already wrote them in operand order
     p.xp = const_cast<void*>(prepared);
-    p.tabg = reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(p.xp) + prepared_tab_offset(M, K));
+    p.tabg = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(p.xp) + prepared_tab_offset(M, K));
   }
   // 1) activations into operand order (one warp per row and 128-column step)
   if (!prepared) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((M * (K / 128) + 3) / 4, 1, 1);
+    cfg.gridDim = dim3((M * (K / 128) + 7) / 8, 1, 1);
     cfg.blockDim = dim3(128, 1, 1);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -585,11 +574,11 @@ int gemv_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_per
   p.input_scale = input_scale;
   p.M = M;
   p.K = K;
-  p.x_vec_ok = ((reinterpret_cast<uintptr_t>(x) & 7u) == 0 && (ldx % 4) == 0) ? 1 : 0;
+  p.x_vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (ldx % 8) == 0) ? 1 : 0;
   p.xp = prepared;
-  p.tabg = reinterpret_cast<float2*>(reinterpret_cast<unsigned char*>(prepared) + prepared_tab_offset(M, K));
+  p.tabg = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(prepared) + prepared_tab_offset(M, K));
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((M * (K / 128) + 3) / 4, 1, 1);
+  cfg.gridDim = dim3((M * (K / 128) + 7) / 8, 1, 1);
   cfg.blockDim = dim3(128, 1, 1);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

@@ -130,8 +130,9 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
   const int nred = pl.red_bufs;
   unsigned char* ring = smem;                                                     // [depth][32][pitch]
   unsigned char* xs = ring + depth * R * pitch;                        // [M][xstride]
-  float2* tab = reinterpret_cast<float2*>(xs + (size_t)p.M * xstride);            // [sps][kTabCols]
-  unsigned char* red = reinterpret_cast<unsigned char*>(tab + (size_t)pl.sps * kTabCols);   // [2][kCW][2][red_lanes] float4
+  float4* tab = reinterpret_cast<float4*>(xs + (size_t)p.M * xstride);            // [sps][kTabCols] (E, SX, g, -)
+  const int mcols = (p.M + 1) & ~1;   // table columns kept in shared memory: activation rows in use, rounded up to a pair
+  unsigned char* red = reinterpret_cast<unsigned char*>(tab + (size_t)pl.sps * mcols);   // [2][kCW][2][red_lanes] float4
   uint32_t* zero_blk = reinterpret_cast<uint32_t*>(red + nred * red_buf);            // 256 zero bytes
   uint64_t* bars = reinterpret_cast<uint64_t*>(zero_blk + 64);                    // full[4] empty[4] red_full[2] red_empty[2]
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kMaxDepth);
@@ -365,14 +366,19 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
       for (int v = threadIdx.x; v < vec_per_row; v += kCW * 32) sts_v4(xs_u32 + m * xstride + v * 16, __ldcg(src + v));
     }
     const uint4* tg = reinterpret_cast<const uint4*>(p.tabg + (size_t)s0 * kTabCols);
-    for (int i = threadIdx.x; i < sps_this * (kTabCols / 2); i += kCW * 32) sts_v4(tab_u32 + i * 16, __ldcg(tg + i));
+    // only the table columns of activation rows in use; threads whose rows are beyond them read
+    // whatever follows (always inside this CTA's shared memory) and their results are discarded
+    for (int i = threadIdx.x; i < sps_this * mcols; i += kCW * 32) {
+      const int st = i / mcols, c = i - st * mcols;
+      sts_v4(tab_u32 + i * 16, __ldcg(tg + st * kTabCols + c));
+    }
   }
   named_sync(1, kCW * 32);
 
   // Offsets into the shared array (plain C++ loads from it compile to ld.shared and, unlike asm, leave
   // the compiler free to software-pipeline the four independent (step, row block) units of an item).
   const int w_off = gid * pitch + warp * (SPW * 64) + tig * 16;
-  const int tab_off = (int)(reinterpret_cast<unsigned char*>(tab) - smem) + warp * (SPW * kTabCols * 8) + tig * 16;
+  const int tab_off = (int)(reinterpret_cast<unsigned char*>(tab) - smem) + warp * (SPW * mcols * 16) + tig * 32;
   int x_off[MB], xstep[MB];
 #pragma unroll
   for (int mb = 0; mb < MB; ++mb) {
@@ -397,12 +403,13 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
 #pragma unroll
       for (int j = 0; j < SPW; ++j) {
         uint4 xb[MB][4];
-        float4 tt[MB];   // E0 SX0 E1 SX1 of activation rows mb*8 + 2 tig, + 1
+        float4 t0[MB], t1[MB];   // (E, SX, g, -) of activation rows mb*8 + 2 tig and + 1
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) xb[mb][q] = *reinterpret_cast<const uint4*>(smem + x_off[mb] + j * xstep[mb] + q * 64);
-          tt[mb] = *reinterpret_cast<const float4*>(smem + tab_off + j * (kTabCols * 8) + mb * 64);
+          t0[mb] = *reinterpret_cast<const float4*>(smem + tab_off + j * (mcols * 16) + mb * 128);
+          t1[mb] = *reinterpret_cast<const float4*>(smem + tab_off + j * (mcols * 16) + mb * 128 + 16);
         }
 #pragma unroll
         for (int rb = 0; rb < RB; ++rb) {
@@ -414,26 +421,26 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint32_t pa[4], pb[4];
-            Nibbles<T>::unpack(wa[q], pa);
-            Nibbles<T>::unpack(wb[q], pb);
+            Nibbles<__half>::unpack(wa[q], pa);
+            Nibbles<__half>::unpack(wb[q], pb);
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
               if (q == 0) {
-                mma16816_zero<T>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][q].x, xb[mb][q].y);
-                mma16816_zero<T>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][q].z, xb[mb][q].w);
+                mma16816_zero<__half>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][q].x, xb[mb][q].y);
+                mma16816_zero<__half>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][q].z, xb[mb][q].w);
               } else {
-                mma16816<T>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][q].x, xb[mb][q].y);
-                mma16816<T>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][q].z, xb[mb][q].w);
+                mma16816<__half>(d0[mb], pa[0], pb[0], pa[1], pb[1], xb[mb][q].x, xb[mb][q].y);
+                mma16816<__half>(d1[mb], pa[2], pb[2], pa[3], pb[3], xb[mb][q].z, xb[mb][q].w);
               }
             }
           }
           const float sA = ms[j][rb][0], zA = mz[j][rb][0], sB = ms[j][rb][1], zB = mz[j][rb][1];
 #pragma unroll
           for (int mb = 0; mb < MB; ++mb) {
-            yacc[rb][mb][0] = fmaf(sA, fmaf(-zA, tt[mb].y, (d0[mb][0] + d1[mb][0]) - tt[mb].x), yacc[rb][mb][0]);
-            yacc[rb][mb][1] = fmaf(sA, fmaf(-zA, tt[mb].w, (d0[mb][1] + d1[mb][1]) - tt[mb].z), yacc[rb][mb][1]);
-            yacc[rb][mb][2] = fmaf(sB, fmaf(-zB, tt[mb].y, (d0[mb][2] + d1[mb][2]) - tt[mb].x), yacc[rb][mb][2]);
-            yacc[rb][mb][3] = fmaf(sB, fmaf(-zB, tt[mb].w, (d0[mb][3] + d1[mb][3]) - tt[mb].z), yacc[rb][mb][3]);
+            yacc[rb][mb][0] = fmaf(sA * t0[mb].z, fmaf(-zA, t0[mb].y, (d0[mb][0] + d1[mb][0]) - t0[mb].x), yacc[rb][mb][0]);
+            yacc[rb][mb][1] = fmaf(sA * t1[mb].z, fmaf(-zA, t1[mb].y, (d0[mb][1] + d1[mb][1]) - t1[mb].x), yacc[rb][mb][1]);
+            yacc[rb][mb][2] = fmaf(sB * t0[mb].z, fmaf(-zB, t0[mb].y, (d0[mb][2] + d1[mb][2]) - t0[mb].x), yacc[rb][mb][2]);
+            yacc[rb][mb][3] = fmaf(sB * t1[mb].z, fmaf(-zB, t1[mb].y, (d0[mb][3] + d1[mb][3]) - t1[mb].x), yacc[rb][mb][3]);
           }
         }
       }
@@ -472,13 +479,13 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
   }
 }
 
-constexpr size_t kPersistSmemCap = 220 * 1024;
+constexpr size_t kPersistSmemCap = 224 * 1024;   // of the 227 KB a block may opt in to
 constexpr int kStepsPW = 2;   // steps per consumer warp and slice: slices of up to 4096 columns
 
 size_t persist_smem(int M, int sps, int depth, int rows, int red_bufs) {
   const int mb = M <= 8 ? 1 : 2;
   const size_t red = (size_t)red_bufs * kCW * (rows / 16) * mb * (M <= 2 ? 8 : 32) * 16;
-  return (size_t)depth * rows * (sps * 64 + 64) + (size_t)M * (sps * 256 + 64) + (size_t)sps * kTabCols * sizeof(float2) + red + 256 +
+  return (size_t)depth * rows * (sps * 64 + 64) + (size_t)M * (sps * 256 + 64) + (size_t)sps * ((M + 1) & ~1) * sizeof(float4) + red + 256 +
          (2 * kMaxDepth + 4) * 8 + 128;
 }
 
@@ -541,9 +548,10 @@ bool gemv_persist_supported(int M, int N, int K, int G) {
   const StreamPlan pl = make_stream_plan(M, N, K);
   if (pl.n_slices > kGrid) return false;
   if ((long long)(N / kMaxRows) * pl.n_slices < g_persist_min_items) return false;
-  // One whole item per CTA plus a piece of another is all ramp and cross-CTA reduction: such layers are
-  // faster as independent tiles (measured: 6144 x 4096 takes 8.1 us here, 6.4 us there).
-  if (M <= 4 && pl.n_slices == 1 && pl.q == 1 && pl.pieces > 0) return false;
+  // Less than two whole items per CTA is all ramp (and cross-CTA reduction where pieces are involved): such
+  // layers are faster as independent tiles at M <= 4 (measured: 6144 x 4096 takes 8.1 us here, 6.4 us
+  // there; 4096 x 4096 5.1 against 4.7 us).
+  if (M <= 4 && pl.n_slices == 1 && pl.q < 2) return false;
   if ((size_t)pl.n_tiles >= kStatusIndex) return false;
   return persist_smem(M, pl.sps, 2, pl.rows, pl.red_bufs) <= kPersistSmemCap;
 }

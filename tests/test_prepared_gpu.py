@@ -34,11 +34,11 @@ def _layer(n, k, seed=0):
 
 
 def _split(prep):
-    """(operand-order activations as int16, table as float32 [steps, 16, 2]) of a prepared buffer."""
+    """(operand-order fp16 activations as int16, table (E, SX, g) as float32 [steps, rows, 3]) of a prepared buffer."""
     m, k = prep.rows, prep.k
     off = (m * k * 2 + 255) // 256 * 256
     xp = prep.buffer[: m * k * 2].view(torch.int16).reshape(m, k)
-    tab = prep.buffer[off: off + (k // 128) * 16 * 8].view(torch.float32).reshape(k // 128, 16, 2)[:, :m]
+    tab = prep.buffer[off: off + (k // 128) * 16 * 16].view(torch.float32).reshape(k // 128, 16, 4)[:, :m, :3]
     return xp, tab
 
 
