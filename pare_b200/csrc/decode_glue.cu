@@ -25,6 +25,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_residual_kernel(const T*
   uint4 wv[kVecs];   // the norm weights do not depend on the previous kernel
 #pragma unroll
   for (int j = 0; j < kVecs; ++j) {
+    if (j * kNormThreads >= nvec) break;   // block-uniform: no vector of this round is inside the row
     const int v = threadIdx.x + j * kNormThreads;
     if (v < nvec) wv[j] = *reinterpret_cast<const uint4*>(weight + v * 8);
   }
@@ -32,6 +33,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_residual_kernel(const T*
   uint4 xv[kVecs], dv[kVecs];
 #pragma unroll
   for (int j = 0; j < kVecs; ++j) {
+    if (j * kNormThreads >= nvec) break;   // block-uniform: no vector of this round is inside the row
     const int v = threadIdx.x + j * kNormThreads;
     if (v < nvec) {
       xv[j] = *reinterpret_cast<const uint4*>(x + row + v * 8);
@@ -41,6 +43,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_residual_kernel(const T*
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < kVecs; ++j) {
+    if (j * kNormThreads >= nvec) break;   // block-uniform: no vector of this round is inside the row
     const int v = threadIdx.x + j * kNormThreads;
     if (v < nvec) {
       T* xe = reinterpret_cast<T*>(&xv[j]);
@@ -69,6 +72,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_residual_kernel(const T*
   const float inv = red[0];
 #pragma unroll
   for (int j = 0; j < kVecs; ++j) {
+    if (j * kNormThreads >= nvec) break;   // block-uniform: no vector of this round is inside the row
     const int v = threadIdx.x + j * kNormThreads;
     const bool live = v < nvec;
     float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
