@@ -108,6 +108,24 @@ int pare_w4a16_forward_prepared(const void* prepared, int x_dtype,
                                 const void* bias, void* y, int64_t ldy, int M, int N, int K, int group_size,
                                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same linear with its activations computed inside the streaming kernel from what a decode
+ * step has at that point, so that the stand-alone RMSNorm / SwiGLU launch disappears (no
+ * counterpart in the reference: model code).  M <= 16.
+ *   PARE_PRODUCER_RMSNORM   x = rmsnorm(a + b) * c over the K columns; a = residual stream
+ *                           [M][lda], b = delta [M][lda] or NULL, c = norm weight [K];
+ *                           resid_out [M][lda] or NULL receives a + b (must not alias a)
+ *   PARE_PRODUCER_SILU_MUL  x = silu(a[:, 0:K]) * a[:, K:2K]; a = fused gate|up [M][lda], lda >= 2 K
+ * a, b, c, resid_out have the activation dtype, are 16-byte aligned, lda % 8 == 0.  Needs
+ * K % 512 == 0 and group % 128 == 0 (PARE_ERR_UNSUPPORTED otherwise).  Cases the fused staging does
+ * not cover (M > 4, a row longer than one CTA's K range) run as the stand-alone glue kernel
+ * followed by pare_w4a16_forward_prepared on a part of the workspace: same result. */
+enum { PARE_PRODUCER_RMSNORM = 1, PARE_PRODUCER_SILU_MUL = 2 };
+int pare_w4a16_forward_produced(int producer, const void* a, const void* b, const void* c, void* resid_out,
+                                int64_t lda, float eps, int x_dtype,
+                                const uint8_t* packed, const float* scale, const float* zero, const void* meta_h2,
+                                const void* bias, void* y, int64_t ldy, int M, int N, int K, int group_size,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
 
 /* ------------------------------------------------------------------------
  * KIVI quantized KV cache.  Replaces the eager primitives and the cache

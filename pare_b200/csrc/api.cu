@@ -2,11 +2,20 @@
 #include "prep.cuh"
 
 namespace pare {
+struct ProducerArgs {
+  int kind;
+  const void* a;
+  const void* b;
+  const void* c;
+  void* resid_out;
+  int64_t lda;
+  float eps;
+};
 size_t gemv_workspace_bytes(int M, int N, int K, int G);
 int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale,
                  const float* zero, const void* meta_h2, const int32_t* col_perm, const float* input_scale,
                  const void* bias, void* y, int64_t ldy, int M, int N, int K, int G, void* workspace,
-                 size_t workspace_bytes, cudaStream_t stream, const void* prepared);
+                 size_t workspace_bytes, cudaStream_t stream, const void* prepared, const ProducerArgs* prod);
 int gemv_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_perm, const float* input_scale, int M, int K,
                  void* prepared, cudaStream_t stream);
 void gemv_set_tuning(int rb, int splits, int pf);
@@ -66,7 +75,7 @@ int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* p
     const int rc = pare::gemv_forward(reinterpret_cast<const unsigned char*>(x) + (size_t)m0 * ldx * esz, x_dtype, ldx,
                                       packed, scale, zero, meta_h2, col_perm, input_scale, bias,
                                       reinterpret_cast<unsigned char*>(y) + (size_t)m0 * ldy * esz, ldy, mc, N, K,
-                                      group_size, workspace, workspace_bytes, s, nullptr);
+                                      group_size, workspace, workspace_bytes, s, nullptr, nullptr);
     if (rc != PARE_OK) return rc;
   }
   return PARE_OK;
@@ -93,7 +102,45 @@ int pare_w4a16_forward_prepared(const void* prepared, int x_dtype, const uint8_t
   PARE_REQUIRE(x_dtype == PARE_F16 || x_dtype == PARE_BF16, PARE_ERR_DTYPE);
   PARE_REQUIRE(prepared && packed && y && (meta_h2 || (scale && zero)), PARE_ERR_SHAPE);
   return pare::gemv_forward(nullptr, x_dtype, K, packed, scale, zero, meta_h2, nullptr, nullptr, bias, y, ldy, M, N, K,
-                            group_size, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream), prepared);
+                            group_size, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream), prepared, nullptr);
+}
+
+int pare_w4a16_forward_produced(int producer, const void* a, const void* b, const void* c, void* resid_out, int64_t lda,
+                                float eps, int x_dtype, const uint8_t* packed, const float* scale, const float* zero,
+                                const void* meta_h2, const void* bias, void* y, int64_t ldy, int M, int N, int K,
+                                int group_size, void* workspace, size_t workspace_bytes, void* stream) {
+  PARE_REQUIRE(M > 0 && M <= 16 && N > 0 && K > 0 && group_size > 0, PARE_ERR_SHAPE);
+  PARE_REQUIRE((K % 512) == 0 && (group_size % 128) == 0 && (K % group_size) == 0 && ldy >= N, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE(x_dtype == PARE_F16 || x_dtype == PARE_BF16, PARE_ERR_DTYPE);
+  PARE_REQUIRE(a && packed && y && (meta_h2 || (scale && zero)), PARE_ERR_SHAPE);
+  PARE_REQUIRE(pare::aligned16(a) && lda % 8 == 0, PARE_ERR_ALIGN);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (producer == PARE_PRODUCER_RMSNORM) {
+    PARE_REQUIRE(c != nullptr && lda >= K && resid_out != a, PARE_ERR_SHAPE);
+    PARE_REQUIRE(pare::aligned16(c) && (b == nullptr || pare::aligned16(b)) && (resid_out == nullptr || pare::aligned16(resid_out)),
+                 PARE_ERR_ALIGN);
+  } else if (producer == PARE_PRODUCER_SILU_MUL) {
+    PARE_REQUIRE(lda >= 2 * (int64_t)K, PARE_ERR_SHAPE);
+  } else {
+    return PARE_ERR_UNSUPPORTED;
+  }
+  const pare::ProducerArgs prod{producer, a, b, c, resid_out, lda, eps};
+  int rc = pare::gemv_forward(nullptr, x_dtype, K, packed, scale, zero, meta_h2, nullptr, nullptr, bias, y, ldy, M, N, K,
+                              group_size, workspace, workspace_bytes, s, nullptr, &prod);
+  if (rc != PARE_ERR_UNSUPPORTED) return rc;
+  // no fused path for this shape: stand-alone glue kernel into the workspace's prepared-activation area
+  // (same layout as a caller-owned prepared buffer), then the plain prepared forward
+  PARE_REQUIRE(workspace && workspace_bytes >= pare_w4a16_workspace_bytes(M, N, K, group_size), PARE_ERR_WORKSPACE);
+  void* prepared = reinterpret_cast<unsigned char*>(workspace) + pare::gemv::kCounterBytes;
+  if (producer == PARE_PRODUCER_RMSNORM) {
+    PARE_REQUIRE(lda == K, PARE_ERR_UNSUPPORTED);   // the stand-alone kernel reads dense rows
+    rc = pare_rmsnorm_residual(a, b, c, resid_out, nullptr, prepared, M, K, eps, x_dtype, stream);
+  } else {
+    rc = pare_silu_mul(a, nullptr, prepared, M, K, lda, x_dtype, stream);
+  }
+  if (rc != PARE_OK) return rc;
+  return pare::gemv_forward(nullptr, x_dtype, K, packed, scale, zero, meta_h2, nullptr, nullptr, bias, y, ldy, M, N, K,
+                            group_size, workspace, workspace_bytes, s, prepared, nullptr);
 }
 
 void pare_w4a16_set_tuning(int row_blocks, int k_splits, int prefetch) {

@@ -41,6 +41,14 @@ struct GemvParams {
   float* partial;       // [splits][M][N]
   int* counters;        // [row tiles]; counters[kStatusIndex] is the status word
   int x_vec_ok;
+  // activations computed inside the kernel (stage.cuh) instead of read from xp / tabg
+  int producer;         // 0 = none, PARE_PRODUCER_RMSNORM, PARE_PRODUCER_SILU_MUL
+  const void* pa;       // rmsnorm: residual stream x [M][lda]; silu_mul: fused gate|up [M][lda], lda >= 2 K
+  const void* pb;       // rmsnorm: delta added to x first (may be NULL)
+  const void* pc;       // rmsnorm: norm weight [K]
+  void* resid_out;      // rmsnorm: x + delta is stored here by the first CTA (may be NULL; must not alias x)
+  int64_t lda;
+  float eps;
 };
 
 // ---- mbarrier / bulk-copy primitives -----------------------------------------------------

@@ -33,8 +33,21 @@
 
 #include "gemv_common.cuh"
 #include "prep.cuh"
+#include "stage.cuh"
 
 namespace pare {
+
+// what stage.cuh computes the activations from
+struct ProducerArgs {
+  int kind;
+  const void* a;
+  const void* b;
+  const void* c;
+  void* resid_out;
+  int64_t lda;
+  float eps;
+};
+
 namespace {
 
 using namespace gemv;
@@ -81,7 +94,8 @@ __global__ void __launch_bounds__(128) w4a16_prep_kernel(const GemvParams p) {
 // RB = 16-row blocks per CTA (every warp takes all of them over its share of K: the activation
 // fragments are read once per step for all RB blocks, and the per-warp prologue / epilogue is paid
 // once for RB times the work).
-template <typename T, int MB, int WARPS, bool META16, int RB>
+// PROD: the activations are computed by this kernel (stage.cuh, M <= 4) instead of copied from a prepared buffer.
+template <typename T, int MB, int WARPS, bool META16, int RB, bool PROD>
 __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int MP = 8 * MB;
@@ -159,12 +173,20 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
     }
   }
 
+  // staging threads per 128-column step: THREADS / 16 half warps, so K <= 4096 takes 4096 / (8 THREADS) rounds
+  constexpr int kRounds = WARPS == 8 ? 2 : 4;
+  uint4 norm_w[kRounds];
+  if constexpr (PROD) stage_prefetch_norm<T, kRounds>(p, nst, threadIdx.x, THREADS, norm_w);
   pdl_launch_dependents();
   pdl_wait();  // from here on the previous kernel's output (x) is visible
 
   // ---- activations arrive in operand order with their per-step sums (prepared once per call by
-  // w4a16_prep_kernel): straight 16-byte copies into shared memory, nothing is recomputed per CTA ----
-  {
+  // w4a16_prep_kernel or by the kernel that computed them): straight 16-byte copies into shared
+  // memory; or this CTA computes them itself (stage.cuh) ----
+  if constexpr (PROD) {
+    stage_produce<T, kRounds>(p, st0, nst, xs, xstride, tab, mcols, threadIdx.x, THREADS, red, blockIdx.x == 0 && blockIdx.y == 0,
+                              norm_w, [] { __syncthreads(); });
+  } else {
     const int vec_per_row = nst * 16;  // 256 bytes per step
     const unsigned char* xp = reinterpret_cast<const unsigned char*>(p.xp);
     for (int m = 0; m < xrows; ++m) {
@@ -421,9 +443,9 @@ Plan make_plan_rb(int M, int N, int K, int G, int rb_request) {
   return pl;
 }
 
-template <typename T, int MB, int WARPS, bool META16, int RB>
+template <typename T, int MB, int WARPS, bool META16, int RB, bool PROD = false>
 int launch_gemv(const GemvParams& p, const Plan& pl, cudaStream_t stream) {
-  auto kern = w4a16_gemv_kernel<T, MB, WARPS, META16, RB>;
+  auto kern = w4a16_gemv_kernel<T, MB, WARPS, META16, RB, PROD>;
   static bool attr_done[64] = {};  // per instantiation and device
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return PARE_ERR_CUDA;
@@ -449,6 +471,14 @@ int launch_gemv(const GemvParams& p, const Plan& pl, cudaStream_t stream) {
 template <typename T, int MB>
 int dispatch_warps(const GemvParams& p, const Plan& pl, cudaStream_t stream) {
   const bool m16 = p.meta_h2 != nullptr;
+  if constexpr (MB == 1) {
+    if (p.producer) {   // M <= 4
+      if (pl.rb == 2) return m16 ? launch_gemv<T, 1, 8, true, 2, true>(p, pl, stream) : launch_gemv<T, 1, 8, false, 2, true>(p, pl, stream);
+      if (pl.warps == 8) return m16 ? launch_gemv<T, 1, 8, true, 1, true>(p, pl, stream) : launch_gemv<T, 1, 8, false, 1, true>(p, pl, stream);
+      return m16 ? launch_gemv<T, 1, 4, true, 1, true>(p, pl, stream) : launch_gemv<T, 1, 4, false, 1, true>(p, pl, stream);
+    }
+  }
+  if (p.producer) return PARE_ERR_UNSUPPORTED;
   if (MB == 1 && pl.rb == 2)   // 32-row CTAs always run 8 warps (4 steps x 2 row blocks per warp)
     return m16 ? launch_gemv<T, 1, 8, true, 2>(p, pl, stream) : launch_gemv<T, 1, 8, false, 2>(p, pl, stream);
   if (pl.warps == 8)
@@ -496,7 +526,7 @@ size_t gemv_workspace_bytes(int M, int N, int K, int G) {
 int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale,
                  const float* zero, const void* meta_h2, const int32_t* col_perm, const float* input_scale,
                  const void* bias, void* y, int64_t ldy, int M, int N, int K, int G, void* workspace,
-                 size_t workspace_bytes, cudaStream_t stream, const void* prepared) {
+                 size_t workspace_bytes, cudaStream_t stream, const void* prepared, const ProducerArgs* prod) {
   GemvParams p{};
   p.x = x;
   p.ldx = ldx;
@@ -518,6 +548,11 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
 
   Plan pl = make_plan(M, N, K, G);
   if (prepared) PARE_REQUIRE(pl.fast && col_perm == nullptr && input_scale == nullptr && aligned16(prepared), PARE_ERR_UNSUPPORTED);
+  if (prod) {
+    PARE_REQUIRE(pl.fast && col_perm == nullptr && input_scale == nullptr && prepared == nullptr && M <= 4, PARE_ERR_UNSUPPORTED);
+    p.producer = prod->kind;
+    p.pa = prod->a; p.pb = prod->b; p.pc = prod->c; p.resid_out = prod->resid_out; p.lda = prod->lda; p.eps = prod->eps;
+  }
   if (!pl.fast) {
     return x_dtype == PARE_F16 ? launch_generic<__half>(p, packed, G, stream)
                                : launch_generic<__nv_bfloat16>(p, packed, G, stream);
@@ -543,8 +578,17 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
     p.xp = const_cast<void*>(prepared);
     p.tabg = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(p.xp) + prepared_tab_offset(M, K));
   }
+  if (prod) {
+    // RMSNorm needs the whole row in one CTA, and few enough steps per half warp of the staging threads
+    if (persist) {
+      PARE_REQUIRE(prod->kind != PARE_PRODUCER_RMSNORM || K <= 4096, PARE_ERR_UNSUPPORTED);
+    } else {
+      PARE_REQUIRE(prod->kind != PARE_PRODUCER_RMSNORM || (pl.splits == 1 && K <= 4096),
+                   PARE_ERR_UNSUPPORTED);
+    }
+  }
   // 1) activations into operand order (one warp per row and 128-column step)
-  if (!prepared) {
+  if (!prepared && !prod) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((M * (K / 128) + 7) / 8, 1, 1);
     cfg.blockDim = dim3(128, 1, 1);

@@ -25,6 +25,7 @@
 #include <type_traits>
 
 #include "gemv_common.cuh"
+#include "stage.cuh"
 
 namespace pare {
 namespace {
@@ -110,7 +111,7 @@ __device__ __forceinline__ Item item_of(const StreamPlan& pl, int bl, int i) {
 
 // SPW = 128-column steps per consumer warp and slice, RB = 16-row blocks per tile, MB = blocks of 8
 // activation rows (M <= 8 MB).
-template <typename T, bool META16, int SPW, int RB, int MB>
+template <typename T, bool META16, int SPW, int RB, int MB, bool PROD>
 __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const GemvParams p, const StreamPlan pl) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int R = 16 * RB;   // rows per tile
@@ -357,8 +358,13 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
   bool active = n_items > 0 && warp_active(cur);
   if (active) load_meta(cur);
 
+  uint4 norm_w[1];   // 32 half warps: one step each
+  if constexpr (PROD) stage_prefetch_norm<T, 1>(p, sps_this, threadIdx.x, kCW * 32, norm_w);
   pdl_wait();  // the activations are the previous kernel's output
-  {
+  if constexpr (PROD) {   // this CTA computes its activations itself (stage.cuh)
+    stage_produce<T, 1>(p, s0, sps_this, xs, xstride, tab, mcols, threadIdx.x, kCW * 32, reinterpret_cast<float*>(red),
+                        blockIdx.x == 0, norm_w, [] { named_sync(1, kCW * 32); });
+  } else {
     const int vec_per_row = sps_this * 16;
     const unsigned char* xp = reinterpret_cast<const unsigned char*>(p.xp);
     for (int m = 0; m < p.M; ++m) {
@@ -575,8 +581,9 @@ int gemv_persist_launch(const gemv::GemvParams& p, int x_dtype, cudaStream_t str
   auto pick = [&](auto t_tag, auto m16_tag) -> int {
     using TT = typename decltype(t_tag)::type;
     constexpr bool M16 = decltype(m16_tag)::value;
-    return pl.rows == 32 ? launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 2, 1>)
-                         : launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 1, 2>);
+    if (p.producer) return pl.rows == 32 ? launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 2, 1, true>) : PARE_ERR_UNSUPPORTED;
+    return pl.rows == 32 ? launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 2, 1, false>)
+                         : launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 1, 2, false>);
   };
   const bool m16 = p.meta_h2 != nullptr;
   if (x_dtype == PARE_F16) return m16 ? pick(TypeTag<__half>{}, std::true_type{}) : pick(TypeTag<__half>{}, std::false_type{});

@@ -11,11 +11,20 @@
 #include "common.cuh"
 
 namespace pare {
+struct ProducerArgs {
+  int kind;
+  const void* a;
+  const void* b;
+  const void* c;
+  void* resid_out;
+  int64_t lda;
+  float eps;
+};
 size_t gemv_workspace_bytes(int M, int N, int K, int G);
 int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale,
                  const float* zero, const void* meta_h2, const int32_t* col_perm, const float* input_scale,
                  const void* bias, void* y, int64_t ldy, int M, int N, int K, int G, void* workspace,
-                 size_t workspace_bytes, cudaStream_t stream, const void* prepared);
+                 size_t workspace_bytes, cudaStream_t stream, const void* prepared, const ProducerArgs* prod);
 }  // namespace pare
 
 namespace {
@@ -67,7 +76,7 @@ int pare_w4a16_forward_static(const void* x, int x_dtype, int64_t ldx, const uin
   // the array keeps whatever the previous call left: the counters are the part that must start at zero
   if (cudaMemsetAsync(scratch, 0, kZeroedPrefixBytes, s) != cudaSuccess) return PARE_ERR_CUDA;
   return pare::gemv_forward(x, x_dtype, ldx, packed, scale, zero, meta_h2, col_perm, input_scale, bias, y, ldy, M, N, K,
-                            group_size, scratch, kStaticScratchBytes, s, nullptr);
+                            group_size, scratch, kStaticScratchBytes, s, nullptr, nullptr);
 }
 
 }  // extern "C"

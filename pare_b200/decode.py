@@ -113,14 +113,13 @@ class DecodeStack(nn.Module):
         return out
 
     def _prepared(self, m: int):
-        """Per-batch-size hand-over buffers between the kernels of a block (hidden, attention, FFN widths)."""
-        bufs = self._prep_cache.get(m)
-        if bufs is None:
+        """Per-batch-size hand-over buffer between the attention kernel and the o projection."""
+        buf = self._prep_cache.get(m)
+        if buf is None:
             blk = self.blocks[0]
-            mk = lambda k: PreparedActivations(m, k, self.dtype, self.device)  # noqa: E731
-            bufs = (mk(self.hidden), mk(blk.hq * blk.d), mk(self.hidden), mk(blk.ffn))
-            self._prep_cache[m] = bufs
-        return bufs
+            buf = PreparedActivations(m, blk.hq * blk.d, self.dtype, self.device)
+            self._prep_cache[m] = buf
+        return buf
 
     def _all_reduce(self, t: Tensor) -> Tensor:
         if self.tp_world > 1:
@@ -147,9 +146,10 @@ class DecodeStack(nn.Module):
     def forward(self, x: Tensor) -> Tensor:
         """``x [M, hidden]``: hidden state of the newest token of each of M sequences → same shape.
 
-        For M <= 16 every activation goes from the kernel that computes it to the next linear as
-        prepared activations (8 launches per block: 2 RMSNorm, 4 linears, attention, SwiGLU; the new
-        K / V token is appended by the attention kernel).  Larger M takes plain tensors.
+        For M <= 16 a block is five launches: q|k|v linear (normalises the residual stream itself),
+        attention (appends the new K / V token, hands its output over as prepared activations), o linear,
+        gate|up linear (adds the attention branch to the residual stream and normalises it itself), down
+        linear (applies the SwiGLU gate itself).  Larger M takes plain tensors and stand-alone glue kernels.
         """
         m = x.shape[0]
         resid = x.clone()
@@ -157,12 +157,14 @@ class DecodeStack(nn.Module):
         blk0 = self.blocks[0]
         fused = all(l.supports_prepared(m) for l in (blk0.qkv, blk0.o, blk0.gate_up, blk0.down))
         if fused:
-            p_h1, p_attn, p_h2, p_act = self._prepared(m)
+            p_attn = self._prepared(m)
+            spare = torch.empty_like(resid)   # the residual stream ping-pongs: the kernels that normalise it read one, write the other
         for i, blk in enumerate(self.blocks):
             d, hq, hkv = blk.d, blk.hq, blk.hkv
             if fused:
-                self._rmsnorm(resid, delta, blk.norm1, store_residual=delta is not None, prepared=p_h1)
-                qkv = blk.qkv.forward_prepared(p_h1)
+                qkv = blk.qkv.forward_rmsnorm(resid, delta, blk.norm1, resid_out=spare if delta is not None else None)
+                if delta is not None:
+                    resid, spare = spare, resid
             else:
                 qkv = blk.qkv(self._rmsnorm(resid, delta, blk.norm1, store_residual=delta is not None))
             q = qkv[:, : hq * d].unflatten(1, (hq, d))
@@ -171,9 +173,9 @@ class DecodeStack(nn.Module):
             if fused:
                 self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d), prepared_out=p_attn)
                 o = self._all_reduce(blk.o.forward_prepared(p_attn))
-                self._rmsnorm(resid, o, blk.norm2, store_residual=True, prepared=p_h2)
-                self._silu_mul(blk.gate_up.forward_prepared(p_h2), blk.ffn, prepared=p_act)
-                delta = self._all_reduce(blk.down.forward_prepared(p_act))
+                gate_up = blk.gate_up.forward_rmsnorm(resid, o, blk.norm2, resid_out=spare)
+                resid, spare = spare, resid
+                delta = self._all_reduce(blk.down.forward_silu_mul(gate_up))
             else:
                 attn = self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d))
                 o = self._all_reduce(blk.o(attn.reshape(m, hq * d)))

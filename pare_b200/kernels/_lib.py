@@ -16,6 +16,7 @@ import torch
 LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libpare_b200.so"
 
 F16, BF16, F32 = 0, 1, 2
+PRODUCER_RMSNORM, PRODUCER_SILU_MUL = 1, 2
 _DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
 
 _lock = threading.Lock()
@@ -34,6 +35,9 @@ SIGNATURES: dict[str, tuple] = {
     "pare_w4a16_prepared_bytes": (_sz, [_i, _i]),
     "pare_w4a16_prepare": (_i, [_vp, _i, _i64, _vp, _vp, _i, _i, _vp, _vp]),
     "pare_w4a16_forward_prepared": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                                         _i, _i, _i, _i, _vp, _sz, _vp]),
+    "pare_w4a16_forward_produced": (_i, [_i, _vp, _vp, _vp, _vp, _i64, C.c_float, _i,
+                                         _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                          _i, _i, _i, _i, _vp, _sz, _vp]),
     "pare_kivi_append": (_i, [_vp, _vp, _i, _i64, _i64, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
                               _i, _i, _i, _i, _i, _i, _vp]),

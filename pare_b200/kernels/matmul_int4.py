@@ -157,6 +157,40 @@ def w4a16_forward_prepared(prep: PreparedActivations, packed_weight: Tensor, sca
     return y
 
 
+def w4a16_forward_produced(producer: int, a: Tensor, packed_weight: Tensor, scale: Tensor | None, zero: Tensor | None,
+                           group_size: int, *, delta: Tensor | None = None, norm_weight: Tensor | None = None,
+                           resid_out: Tensor | None = None, eps: float = 1e-5, bias: Tensor | None = None,
+                           meta_h2: Tensor | None = None, out: Tensor | None = None) -> Tensor:
+    """The linear with its activations computed inside the streaming kernel (M <= 16).
+
+    ``producer = _lib.PRODUCER_RMSNORM``: ``x = rmsnorm(a + delta) * norm_weight`` (``a [M, K]``; ``a + delta`` is
+    stored to ``resid_out``, which must not be ``a``).  ``producer = _lib.PRODUCER_SILU_MUL``:
+    ``x = silu(a[:, :K]) * a[:, K:2K]`` for a fused gate|up tensor ``a [M, >= 2K]``.
+    """
+    n, k_half = packed_weight.shape
+    k = 2 * k_half
+    m = a.shape[0]
+    assert a.is_cuda and a.dim() == 2 and a.stride(1) == 1 and packed_weight.is_contiguous()
+    if producer == _lib.PRODUCER_RMSNORM:
+        assert a.shape[1] == k and norm_weight is not None and norm_weight.dtype == a.dtype
+        assert delta is None or (delta.shape == a.shape and delta.stride() == a.stride() and delta.dtype == a.dtype)
+        assert resid_out is None or (resid_out.shape == a.shape and resid_out.stride() == a.stride()
+                                     and resid_out.data_ptr() != a.data_ptr())
+    else:
+        assert a.shape[1] >= 2 * k
+    if bias is not None and bias.dtype != a.dtype:
+        bias = bias.to(a.dtype)
+    y = out if out is not None else torch.empty(m, n, device=a.device, dtype=a.dtype)
+    L = _lib.lib()
+    ws = _lib.workspace(a.device, L.pare_w4a16_workspace_bytes(m, n, k, group_size))
+    status = L.pare_w4a16_forward_produced(
+        producer, a.data_ptr(), _lib.ptr(delta), _lib.ptr(norm_weight), _lib.ptr(resid_out), a.stride(0), float(eps),
+        _lib.dtype_code(a.dtype), packed_weight.data_ptr(), _lib.ptr(scale), _lib.ptr(zero), _lib.ptr(meta_h2), _lib.ptr(bias),
+        y.data_ptr(), y.stride(0), m, n, k, group_size, ws.data_ptr(), ws.numel(), _lib.current_stream(a.device))
+    _lib.check(status, "pare_w4a16_forward_produced")
+    return y
+
+
 # kernel-layout tensor (as passed by reference-style callers) -> storage layout, cached per tensor
 # object: keyed by id() (tensors do not hash/compare as dict keys) and dropped when it dies
 _storage_cache: dict[int, tuple[int, int, Tensor]] = {}

@@ -193,6 +193,33 @@ class QuantizedLinear(nn.Module):
             None if use_h2 else self._scale_kernel, None if use_h2 else self._zero_kernel,
             self._kernel_group_size(), bias=self.bias, meta_h2=self._meta_h2_kernel if use_h2 else None)
 
+    def _forward_produced(self, producer: int, a: Tensor, **kw) -> Tensor:
+        from pare_b200.kernels.matmul_int4 import w4a16_forward_produced
+
+        if not self.supports_prepared(a.shape[0]):
+            raise ValueError("this layer cannot compute its activations in-kernel (act-order, input scale, shape or row count)")
+        if not hasattr(self, "_packed_weight_kernel"):
+            self._prepare_kernel_buffers()
+        use_h2 = self.kernel_meta_fp16
+        return w4a16_forward_produced(
+            producer, a, self._packed_weight_kernel,
+            None if use_h2 else self._scale_kernel, None if use_h2 else self._zero_kernel,
+            self._kernel_group_size(), bias=self.bias, meta_h2=self._meta_h2_kernel if use_h2 else None, **kw)
+
+    def forward_rmsnorm(self, x: Tensor, delta: Tensor | None, norm_weight: Tensor, resid_out: Tensor | None = None,
+                        eps: float = 1e-5) -> Tensor:
+        """``self(rmsnorm(x + delta) * norm_weight)`` for ``x [rows <= 16, in_features]`` in one launch: the
+        streaming kernel normalises the row itself.  ``x + delta`` is stored to ``resid_out`` (not ``x``)."""
+        from pare_b200.kernels import _lib
+
+        return self._forward_produced(_lib.PRODUCER_RMSNORM, x, delta=delta, norm_weight=norm_weight, resid_out=resid_out, eps=eps)
+
+    def forward_silu_mul(self, gate_up: Tensor) -> Tensor:
+        """``self(silu(gate) * up)`` for a fused ``gate_up [rows <= 16, 2 * in_features]`` in one launch."""
+        from pare_b200.kernels import _lib
+
+        return self._forward_produced(_lib.PRODUCER_SILU_MUL, gate_up)
+
     # -- alternate constructors ----------------------------------------------
     @classmethod
     def from_tensors(

@@ -166,3 +166,66 @@ def test_decode_stack_fused_equals_plain(cuda_lib, monkeypatch):
     mx, mean = ow.rel_err(a, b)
     assert mx <= 1e-2 and mean <= 1e-3, (mx, mean)
     assert np.isfinite(a).all()
+
+
+# ---- activations computed inside the streaming kernel ------------------------------------------
+
+def _oracle_linear(x16, packed, scale, zero):
+    return ow.linear(x16.float().cpu().numpy(), packed.cpu().numpy(), scale.cpu().numpy(), zero.cpu().numpy())
+
+
+def _bars(y, ref, dtype):
+    mx, mean = ow.rel_err(y.float().cpu().numpy(), ref)
+    assert mx <= 1e-2 and mean <= (2.5e-3 if dtype == torch.bfloat16 else 1e-3), (mx, mean)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", [(1, 1024, 1024), (4, 6144, 4096), (2, 9472, 1024), (1, 28672, 4096), (8, 1024, 1024)])
+def test_linear_normalises_its_input_itself(m, n, k, dtype, cuda_lib):
+    """rmsnorm(x + delta) * w -> linear in one launch (tile kernel, persistent kernel, and M = 8 through the
+    stand-alone kernel) against the oracle on the fp32 reference of the norm rounded to the activation dtype;
+    the new residual stream is exact."""
+    from pare_b200.kernels.matmul_int4 import w4a16_forward_produced
+    packed, scale, zero = _layer(n, k, seed=n + k + m)
+    x = torch.randn(m, k, device="cuda").to(dtype)
+    delta = torch.randn(m, k, device="cuda").to(dtype)
+    w = (1 + 0.1 * torch.randn(k, device="cuda")).to(dtype)
+    resid = torch.empty_like(x)
+    y = w4a16_forward_produced(_lib.PRODUCER_RMSNORM, x, packed, scale, zero, 128, delta=delta, norm_weight=w,
+                               resid_out=resid, eps=1e-5)
+    h = (x.float() + delta.float()).to(dtype)
+    assert torch.equal(resid, h)
+    hn = (h.float() * torch.rsqrt((h.float() ** 2).mean(-1, keepdim=True) + 1e-5) * w.float()).to(dtype)
+    _bars(y, _oracle_linear(hn, packed, scale, zero), dtype)
+    # without a delta and without storing the stream
+    y0 = w4a16_forward_produced(_lib.PRODUCER_RMSNORM, h, packed, scale, zero, 128, norm_weight=w, eps=1e-5)
+    _bars(y0, _oracle_linear(hn, packed, scale, zero), dtype)
+    y1 = w4a16_forward_produced(_lib.PRODUCER_RMSNORM, x, packed, scale, zero, 128, delta=delta, norm_weight=w,
+                                resid_out=resid, eps=1e-5)
+    assert torch.equal(y, y1)   # deterministic
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k", [(1, 1024, 2048), (3, 4096, 14336), (1, 10240, 1024), (6, 512, 1024)])
+def test_linear_applies_the_swiglu_gate_itself(m, n, k, dtype, cuda_lib):
+    from pare_b200.kernels.matmul_int4 import w4a16_forward_produced
+    packed, scale, zero = _layer(n, k, seed=n + k + m)
+    gu = torch.randn(m, 2 * k + 8, device="cuda").to(dtype)[:, : 2 * k]     # a row stride larger than 2 K
+    y = w4a16_forward_produced(_lib.PRODUCER_SILU_MUL, gu, packed, scale, zero, 128)
+    act = (torch.nn.functional.silu(gu[:, :k].float()) * gu[:, k:].float()).to(dtype)
+    _bars(y, _oracle_linear(act, packed, scale, zero), dtype)
+    assert torch.equal(y, w4a16_forward_produced(_lib.PRODUCER_SILU_MUL, gu, packed, scale, zero, 128))
+
+
+def test_produced_rejects_aliasing_and_odd_shapes(cuda_lib):
+    from pare_b200.kernels.matmul_int4 import w4a16_forward_produced
+    packed, scale, zero = _layer(256, 640)
+    x = torch.randn(1, 640, device="cuda").half()
+    w = torch.ones(640, device="cuda").half()
+    with pytest.raises(_lib.KernelLibraryError):     # K % 512 != 0
+        w4a16_forward_produced(_lib.PRODUCER_RMSNORM, x, packed, scale, zero, 128, norm_weight=w)
+    packed, scale, zero = _layer(256, 1024)
+    x = torch.randn(1, 1024, device="cuda").half()
+    with pytest.raises(AssertionError):              # the stream must not be normalised in place
+        w4a16_forward_produced(_lib.PRODUCER_RMSNORM, x, packed, scale, zero, 128, norm_weight=torch.ones(1024, device="cuda").half(),
+                               resid_out=x)
