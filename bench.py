@@ -15,7 +15,8 @@ One JSON line on stdout (rank 0): ``value`` = decode tok/s with everything resid
 public Python API with the hidden state copied from pinned host memory and the result copied
 back every step; ``roofline`` = the dominant kernel (fused gate|up dequant-GEMV) timed on its
 own over 32 distinct layers' weights; ``layers`` = us/layer and fraction of the measured HBM
-peak for every projection at M = 1/4/16; ``cpu_baseline`` = the reference's CPU op sequence
+peak for every projection at M = 1/4/16; ``attention`` = the fused KIVI decode attention alone at
+batch 1 and batch 16; ``cpu_baseline`` = the reference's CPU op sequence
 (oracle port) timed on the host cores on a bounded sample.  ``--impl reference`` prints only
 that CPU arm.
 """
@@ -40,9 +41,9 @@ import torch  # noqa: E402
 METRIC = "decode_tok_s_llama3.1-8b_w4a16_kivi4"
 UNIT = "tok/s"
 FALLBACK_HBM_GBS = 6650.0
-# kernels of this library launched per decode block: 2 rmsnorm, 4 GEMV, attention, silu_mul (activations travel
-# between them as prepared activations; the attention kernel appends the new K / V token itself)
-LAUNCHES_PER_BLOCK = 8
+# kernels of this library launched per decode block: 4 linears (q|k|v and gate|up normalise their input
+# themselves, down applies the SwiGLU gate itself) and attention (which appends the new K / V token itself)
+LAUNCHES_PER_BLOCK = 5
 # dram__bytes_read + dram__bytes_write of one gate|up GEMV launch (28672 x 4096, M = 1) from the ncu capture
 # summarised in profiles/w4a16_gemv_persist_gate_up_m1.md
 GATE_UP_DRAM_TRAFFIC = 66_100_000 + 540_000
@@ -60,6 +61,7 @@ def parse_args():
     ap.add_argument("--shape", default="llama-3.1-8b")
     ap.add_argument("--skip-layer-table", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="for profiler captures: GPU work only")
+    ap.add_argument("--table-batches", default="1,4,16", help="activation rows of the per-layer table")
     return ap.parse_args()
 
 
@@ -289,6 +291,41 @@ def layer_table(stack, peak: float, batches=(1, 4, 16)) -> dict:
     return table
 
 
+def attention_table(dtype, device, peak: float, cases=((1, 4096, 32), (16, 4096, 8))) -> dict:
+    """Fused KIVI decode attention alone (8 KV heads, 32 query heads, D = 128, 4-bit g32, residual window 128):
+    one CUDA graph over ``layers`` distinct caches (larger than L2 together), us per call and fraction of the HBM
+    peak by the bytes the call must read (168 B per compressed token and KV head, 512 B per window token)."""
+    from pare_b200.kv_cache import KVCacheConfig, QuantizedKVCache
+
+    table = {}
+    for batch, ctx, layers in cases:
+        cache = QuantizedKVCache(layers, KVCacheConfig(bits=4, group_size=32, residual_length=128), max_seq_len=ctx + 256)
+        g = torch.Generator(device=device).manual_seed(0)
+        n0 = 128 + ((ctx - 128) // 32) * 32
+        for layer in range(layers):
+            k = torch.randn(batch, 8, n0, 128, device=device, generator=g).to(dtype)
+            v = torch.randn(batch, 8, n0, 128, device=device, generator=g).to(dtype)
+            cache._append(layer, k, v)
+        q = torch.randn(batch, 32, 1, 128, device=device).to(dtype)
+        k1 = torch.randn(batch, 8, 1, 128, device=device).to(dtype)
+        v1 = torch.randn(batch, 8, 1, 128, device=device).to(dtype)
+
+        def run():
+            for layer in range(layers):
+                cache.attend(layer, q, k1, v1)
+                cache._stores[layer].r_len -= 1   # the same step again: the token lands in the same window slot
+
+        gr, _ = capture(run)
+        reps = 20
+        sec = time_events(gr.replay, reps, 3, 1)
+        us = sec / (reps * layers) * 1e6
+        st = cache._stores[0]
+        nbytes = batch * 8 * (st.n_comp * 168 + (st.r_len + 1) * 512) + batch * 32 * 128 * 4
+        table[f"b{batch}_ctx{ctx}"] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peak, 4)}
+        del gr, cache
+    return table
+
+
 def run_ours(args) -> None:
     from pare_b200.decode import SHAPES, DecodeStack
     from pare_b200.kernels import _lib
@@ -347,8 +384,9 @@ def run_ours(args) -> None:
     line["step_frac_hbm"] = round(step_bytes / (sec / steps) / 1e9 / peak, 4)
 
     if world == 1:
-        table = {} if args.skip_layer_table else layer_table(stack, peak)
+        table = {} if args.skip_layer_table else layer_table(stack, peak, tuple(int(b) for b in args.table_batches.split(",")))
         line["layers"] = table
+        line["attention"] = {} if args.skip_layer_table else attention_table(dtype, stack.device, peak)
         key = f"gate_up_{blk.gate_up.out_features}x{blk.gate_up.in_features}_m{args.batch}"
         if key in table:
             achieved = table[key]["gbs"]
