@@ -201,7 +201,9 @@ def dist_setup(n_gpus: int):
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ["NCCL_DEBUG"] = "WARN"   # keep NCCL's version banner off stdout: one JSON line only
+        # keep NCCL's version banner off stdout (one JSON line only): warnings only, and into a file
+        os.environ["NCCL_DEBUG"] = "WARN"
+        os.environ.setdefault("NCCL_DEBUG_FILE", os.path.join(tempfile.gettempdir(), "nccl_%h_%p.log"))
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
     return world, rank, local
 
@@ -349,6 +351,7 @@ def run_ours(args) -> None:
     y_host = torch.empty(args.batch, hidden, dtype=dtype).pin_memory()
     x_dev = x_host.cuda(non_blocking=True)
 
+    barrier(world)   # every rank has built its shard before the first step touches a peer
     graph, y_dev = capture(lambda: stack(x_dev))
 
     sampler = ClockSampler(local) if rank == 0 else None
@@ -371,7 +374,7 @@ def run_ours(args) -> None:
         "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
         "e2e": {"value": args.batch * steps / sec_e2e, "unit": UNIT,
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
-        "gpu_launches": LAUNCHES_PER_BLOCK * args.layers * steps,
+        "gpu_launches": (LAUNCHES_PER_BLOCK + (2 if world > 1 and stack.peer_reduce is not None else 0)) * args.layers * steps,
         "clocks": clocks,
     }
     # bytes one step must move: all linears (algorithmic) + the cache

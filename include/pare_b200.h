@@ -235,6 +235,29 @@ int pare_w4a16_forward_static(const void* x, int x_dtype, int64_t ldx,
                               int M, int N, int K, int group_size,
                               void* stream);
 
+/* ------------------------------------------------------------------------
+ * One-shot all-reduce of a small activation tensor over NVLink peer memory, for tensor-parallel
+ * decode (the two partial sums per block after the row-parallel o and down projections).  No
+ * counterpart in the reference, which is single-GPU.  Every rank stores its partial into every
+ * peer's exchange buffer (plain peer stores), raises a flag, waits (bounded) for its own flags and
+ * adds the partials in rank order: fp32, deterministic, the same bits on every rank; one launch.
+ *   pare_peer_buffer_create  allocates and zeroes this rank's exchange buffer and returns its
+ *                            64-byte CUDA IPC handle (to be sent to the peers by any host channel)
+ *   pare_peer_buffer_open    maps a peer's buffer from its handle; _close unmaps; _destroy frees
+ *   pare_peer_allreduce      y = sum over ranks of x, [rows][cols] F16/BF16, cols % 8 == 0,
+ *                            rows*cols*2 <= (buffer_bytes - 4096) / (2 * world); buffers = HOST array
+ *                            of `world` device pointers (own buffer at index `rank`); 2 <= world <= 8;
+ *                            every rank makes the same sequence of calls; capturable in a CUDA graph
+ *   pare_peer_status         0 or PARE_ERR_TIMEOUT (a wait for a peer ran out); synchronises `stream`
+ * The create / open / close / destroy calls are the only ones in this library that allocate. */
+int pare_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[64]);
+int pare_peer_buffer_open(const unsigned char handle[64], void** ptr);
+int pare_peer_buffer_close(void* ptr);
+int pare_peer_buffer_destroy(void* ptr);
+int pare_peer_status(const void* own_buffer, void* stream);
+int pare_peer_allreduce(const void* x, int64_t ldx, void* y, int64_t ldy, int rows, int cols, int dtype,
+                        int rank, int world, void* const* buffers, size_t buffer_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

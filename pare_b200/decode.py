@@ -78,7 +78,7 @@ class DecodeStack(nn.Module):
 
     def __init__(self, shape: str | tuple, *, device="cuda", dtype=torch.bfloat16, n_layers: int | None = None,
                  kv_config: KVCacheConfig | None = None, max_seq_len: int = 8192, tp_world: int = 1,
-                 process_group=None, seed: int = 0) -> None:
+                 process_group=None, seed: int = 0, peer_all_reduce: bool = True) -> None:
         super().__init__()
         hidden, ffn, hq, hkv, d, layers = SHAPES[shape] if isinstance(shape, str) else shape
         self.hidden, self.d = hidden, d
@@ -91,6 +91,11 @@ class DecodeStack(nn.Module):
         self.cache = QuantizedKVCache(self.n_layers, kv_config or KVCacheConfig(), max_seq_len=max_seq_len)
         self._code = _lib.dtype_code(dtype)
         self._prep_cache: dict[int, tuple] = {}
+        # one-launch all-reduce over NVLink peer memory for the small decode tensors; NCCL for anything larger
+        self.peer_reduce = None
+        if tp_world > 1 and peer_all_reduce:
+            from pare_b200.parallel import PeerAllReduce
+            self.peer_reduce = PeerAllReduce(process_group)
 
     # ---- glue kernels ------------------------------------------------------------------
     def _rmsnorm(self, x: Tensor, delta: Tensor | None, weight: Tensor, store_residual: bool, prepared=None):
@@ -123,6 +128,8 @@ class DecodeStack(nn.Module):
 
     def _all_reduce(self, t: Tensor) -> Tensor:
         if self.tp_world > 1:
+            if self.peer_reduce is not None and t.numel() <= self.peer_reduce.max_elements() and t.shape[1] % 8 == 0:
+                return self.peer_reduce(t)
             torch.distributed.all_reduce(t, group=self.group)
         return t
 

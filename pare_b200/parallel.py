@@ -87,3 +87,73 @@ def gather_columns(y_shard: Tensor, group=None) -> Tensor:
     parts = [torch.empty_like(y_shard) for _ in range(dist.get_world_size(group))]
     dist.all_gather(parts, y_shard.contiguous(), group=group)
     return torch.cat(parts, dim=-1)
+
+
+class PeerAllReduce:
+    """Sum of a small ``[rows, cols]`` fp16/bf16 tensor over the ranks of ``group`` through NVLink peer memory.
+
+    One kernel launch per call (``pare_peer_allreduce``): every rank stores its partial into every peer's
+    exchange buffer, waits for the peers' flags and adds the partials in rank order (fp32, deterministic,
+    identical on all ranks).  The exchange buffers are allocated once here and shared by CUDA IPC handles
+    exchanged over ``torch.distributed``; every rank must construct this object and then make the same
+    sequence of calls.  Capturable in a CUDA graph.  2 <= world <= 8, one process per GPU on one node.
+    """
+
+    def __init__(self, group=None, max_bytes: int = 256 << 10) -> None:
+        import ctypes as C
+
+        import torch.distributed as dist
+
+        from pare_b200.kernels import _lib
+
+        self._lib = _lib
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if not 2 <= self.world <= 8:
+            raise ValueError("PeerAllReduce serves 2..8 ranks")
+        self.buffer_bytes = 4096 + 2 * self.world * ((max_bytes + 255) // 256 * 256)
+        L = _lib.lib()
+        own = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        _lib.check(L.pare_peer_buffer_create(self.buffer_bytes, C.byref(own), handle), "pare_peer_buffer_create")
+        self._own = own.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, (self.rank, bytes(handle.raw)), group=group)
+        ptrs = (C.c_void_p * self.world)()
+        self._opened = []
+        for r, h in handles:
+            if r == self.rank:
+                ptrs[r] = self._own
+            else:
+                peer = C.c_void_p()
+                _lib.check(L.pare_peer_buffer_open(h, C.byref(peer)), "pare_peer_buffer_open")
+                ptrs[r] = peer.value
+                self._opened.append(peer.value)
+        self._ptrs = ptrs
+        dist.barrier(group=group)   # nobody stores into a buffer that is not mapped everywhere yet
+
+    def max_elements(self) -> int:
+        return ((self.buffer_bytes - 4096) // (2 * self.world) // 256 * 256) // 2
+
+    def __call__(self, x, out=None):
+        assert x.is_cuda and x.dim() == 2 and x.stride(1) == 1
+        y = out if out is not None else torch.empty_like(x)
+        status = self._lib.lib().pare_peer_allreduce(
+            x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), x.shape[0], x.shape[1], self._lib.dtype_code(x.dtype),
+            self.rank, self.world, self._ptrs, self.buffer_bytes, self._lib.current_stream(x.device))
+        self._lib.check(status, "pare_peer_allreduce")
+        return y
+
+    def status(self, device) -> int:
+        """0, or the timeout code if a wait for a peer ran out since the buffer was created (synchronises)."""
+        return self._lib.lib().pare_peer_status(self._own, self._lib.current_stream(device))
+
+    def close(self) -> None:
+        L = self._lib.lib()
+        for p in self._opened:
+            L.pare_peer_buffer_close(p)
+        self._opened = []
+        if self._own:
+            L.pare_peer_buffer_destroy(self._own)
+            self._own = None
