@@ -137,7 +137,10 @@ int pare_w4a16_forward_produced(int producer, const void* a, const void* b, cons
  * (cap % 128 == 0); the reference grows six tensors with torch.cat instead:
  *   k_codes [B][H][cap][D*bits/8]           uint8, packed along channels (channel c of a
  *                                           token at bit c*bits of its row, little endian)
- *   k_scale, k_zero [B][H][cap/group][D]    fp32, per (token group, channel); zero = group min
+ *   k_scale, k_zero [B][H][cap/group][D]    fp32, per (token group, channel); zero = group min.
+ *                                           When D % 128 == 0, channel c of a row sits at position
+ *                                           (c & ~127) + ((c>>3)&3)*32 + ((c>>5)&3)*8 + (c&7): the order
+ *                                           in which the decode-attention kernel reads it
  *   v_codes [B][H][cap/128][D][128*bits/8]  uint8, packed along tokens inside 128-token blocks
  *                                           (token t of the block at bit t*bits of row d)
  *   v_scale, v_zero [B][H][cap]             fp32, per token (min/max over all D channels)

@@ -150,6 +150,16 @@ struct Nibbles<__nv_bfloat16> {
   }
 };
 
+// ---- storage position of a channel in the KIVI key scale / zero rows -----------------------
+// Inside every block of 128 channels the rows are stored as [word i = (c>>3)&3][lane quad = (c>>5)&3][c&7]:
+// the decode-attention kernel reads, for one code word i, the eight channels of each of the four lanes of a
+// quad, and this order puts those four 32-byte pieces next to each other (no shared-memory bank conflicts
+// after the row has been bulk-copied as it is).  Head dims that are not a multiple of 128 keep channel order.
+__host__ __device__ __forceinline__ int kmeta_pos(int c, int D) {
+  if (D & 127) return c;
+  return (c & ~127) | (((c >> 3) & 3) << 5) | (((c >> 5) & 3) << 3) | (c & 7);
+}
+
 // ---- scalar conversions -----------------------------------------------------
 template <typename T>
 __device__ __forceinline__ float to_float(T v);

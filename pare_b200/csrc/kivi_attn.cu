@@ -57,6 +57,8 @@ constexpr size_t kCounterInts = gemv::kCounterInts;
 constexpr size_t kCounterBytes = gemv::kCounterBytes;
 constexpr size_t kAttnSmemCap = 200 * 1024;
 constexpr float kNegBig = -1e30f;
+constexpr int kQS = 132;   // floats per staged query row: channel c at (c>>3 & 3)*32 + (c>>5)*8 + (c&7), rows 16 bytes off a bank period
+__device__ __forceinline__ int q_pos(int c) { return (((c >> 3) & 3) << 5) | ((c >> 5) << 3) | (c & 7); }
 
 struct AttnParams {
   const void* q;
@@ -133,8 +135,8 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
   float* st_m = reinterpret_cast<float*>(smem + 16);                // [8]
   float* st_l = st_m + kHeads;
   float* st_c = st_l + kHeads;
-  float* qf = reinterpret_cast<float*>(smem + 128);                 // [8][128]
-  float* S = qf + kHeads * kD;                                      // [8][s_stride]
+  float* qf = reinterpret_cast<float*>(smem + 128);                 // [8][kQS], channels in q_pos order
+  float* S = qf + kHeads * kQS;                                     // [8][s_stride]
   unsigned char* P = reinterpret_cast<unsigned char*>(S + kHeads * p.s_stride);  // [8][p_stride] fp16 hi parts
   unsigned char* P2 = P + kHeads * p.p_stride;                                   // [8][p_stride] fp16 lo parts
   unsigned char* stage = P2 + kHeads * p.p_stride;   // 128-byte aligned by construction of the strides
@@ -147,7 +149,6 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
     mbar_init(bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
   pdl_launch_dependents();
 
   // operand stage of a compressed split
@@ -175,6 +176,7 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       bulk_load(smem_u32(vz_s), p.v_zero + bh * p.cap + chunk_start, valid * 4, bar);
     }
   }
+  __syncthreads();   // the barrier is initialised for everybody
   pdl_wait();   // q, the newest token and the residual window may come from the previous kernels
 
   unsigned char* rk_s = stage;
@@ -223,8 +225,8 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
         lo4 = make_float4(to_float<T>(e[0]), to_float<T>(e[1]), to_float<T>(e[2]), to_float<T>(e[3]));
         hi4 = make_float4(to_float<T>(e[4]), to_float<T>(e[5]), to_float<T>(e[6]), to_float<T>(e[7]));
       }
-      *reinterpret_cast<float4*>(qf + hh * kD + c8) = lo4;
-      *reinterpret_cast<float4*>(qf + hh * kD + c8 + 4) = hi4;
+      *reinterpret_cast<float4*>(qf + hh * kQS + q_pos(c8)) = lo4;
+      *reinterpret_cast<float4*>(qf + hh * kQS + q_pos(c8) + 4) = hi4;
     }
   }
   __syncthreads();
@@ -237,22 +239,30 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
     const int ngroups = valid / G;
 
     // ================= phase A: scores =================
-    for (int gl = warp; gl < ngroups; gl += kAttnWarps) {
+    // one (group, 16-token tile) item per warp when that occupies no more than the eight warps (short chunks:
+    // the per-group operand preparation is repeated, the serial tile loop is cut); else one group per warp
+    const int tpg = G / 16;
+    const bool split_tiles = ngroups * tpg <= kAttnWarps;
+    const int n_items = split_tiles ? ngroups * tpg : ngroups;
+    for (int item = warp; item < n_items; item += kAttnWarps) {
+      const int gl = split_tiles ? item / tpg : item;
+      const int tile_lo = split_tiles ? item - gl * tpg : 0, tile_hi = split_tiles ? tile_lo + 1 : tpg;
       const unsigned char* krow = kc_s + (gl * G) * 64 + tig * 16;
-      const float* ks = ks_s + gl * kD + tig * 32;
-      const float* kz = kz_s + gl * kD + tig * 32;
+      const float* ks = ks_s + gl * kD + tig * 8;   // rows in kmeta_pos order: word i of this lane at i * 32 + tig * 8
+      const float* kz = kz_s + gl * kD + tig * 8;
+      const float* qrow = qf + gid * kQS + tig * 8;
       // q * scale as a two-term fp16 expansion (hi + lo, ~22 bits): a single fp16 rounding of
       // this operand would move the logits by more than the reference's own fp16 cast of K^
       uint32_t xh[4][4], xl[4][4];
       float bias = 0.f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float4 s0 = *reinterpret_cast<const float4*>(ks + i * 8);
-        const float4 s1 = *reinterpret_cast<const float4*>(ks + i * 8 + 4);
-        const float4 z0 = *reinterpret_cast<const float4*>(kz + i * 8);
-        const float4 z1 = *reinterpret_cast<const float4*>(kz + i * 8 + 4);
-        const float4 q0 = *reinterpret_cast<const float4*>(qf + gid * kD + tig * 32 + i * 8);
-        const float4 q1 = *reinterpret_cast<const float4*>(qf + gid * kD + tig * 32 + i * 8 + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(ks + i * 32);
+        const float4 s1 = *reinterpret_cast<const float4*>(ks + i * 32 + 4);
+        const float4 z0 = *reinterpret_cast<const float4*>(kz + i * 32);
+        const float4 z1 = *reinterpret_cast<const float4*>(kz + i * 32 + 4);
+        const float4 q0 = *reinterpret_cast<const float4*>(qrow + i * 32);
+        const float4 q1 = *reinterpret_cast<const float4*>(qrow + i * 32 + 4);
         bias = fmaf(q0.x, z0.x, bias); bias = fmaf(q0.y, z0.y, bias); bias = fmaf(q0.z, z0.z, bias); bias = fmaf(q0.w, z0.w, bias);
         bias = fmaf(q1.x, z1.x, bias); bias = fmaf(q1.y, z1.y, bias); bias = fmaf(q1.z, z1.z, bias); bias = fmaf(q1.w, z1.w, bias);
         // operand order of one code word: (c0,c4) (c1,c5) (c2,c6) (c3,c7)
@@ -266,7 +276,7 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       const float c0 = __shfl_sync(0xffffffffu, bias, (tig * 2) * 4);
       const float c1 = __shfl_sync(0xffffffffu, bias, (tig * 2 + 1) * 4);
 
-      for (int tile = 0; tile < G / 16; ++tile) {
+      for (int tile = tile_lo; tile < tile_hi; ++tile) {
         const uint4 wa4 = *reinterpret_cast<const uint4*>(krow + (tile * 16 + gid) * 64);
         const uint4 wb4 = *reinterpret_cast<const uint4*>(krow + (tile * 16 + gid + 8) * 64);
         const uint32_t wa[4] = {wa4.x, wa4.y, wa4.z, wa4.w};
@@ -379,8 +389,8 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
         const int c0 = (j * 4 + tig) * 8;
         const uint4 ka = *reinterpret_cast<const uint4*>(rk_s + tA * kResPitch + c0 * 2);
         const uint4 kb = *reinterpret_cast<const uint4*>(rk_s + tB * kResPitch + c0 * 2);
-        const float4 q0 = *reinterpret_cast<const float4*>(qf + gid * kD + c0);
-        const float4 q1 = *reinterpret_cast<const float4*>(qf + gid * kD + c0 + 4);
+        const float4 q0 = *reinterpret_cast<const float4*>(qf + gid * kQS + q_pos(c0));
+        const float4 q1 = *reinterpret_cast<const float4*>(qf + gid * kQS + q_pos(c0) + 4);
         mma16816<__half>(d0, pair_to_h2<T>(ka.x), pair_to_h2<T>(kb.x), pair_to_h2<T>(ka.y), pair_to_h2<T>(kb.y),
                          h2_bits(q0.x, q0.y), h2_bits(q0.z, q0.w));
         mma16816<__half>(d0, pair_to_h2<T>(ka.z), pair_to_h2<T>(kb.z), pair_to_h2<T>(ka.w), pair_to_h2<T>(kb.w),
@@ -455,7 +465,30 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
   __threadfence();
   const float* pm = p.part_ml + bh * p.n_split * (size_t)(kHeads * 2);
   const float* po = p.part_o + bh * p.n_split * (size_t)(kHeads * kD);
-  // statistics of all splits -> shared memory (one load per thread), then weights per (split, head)
+  // Everything the merge needs from global memory is requested before anything waits: first the partial outputs
+  // of this thread (registers), then the statistics of all splits (shared memory).
+  // thread = (split group, head, 8 channels): the groups take contiguous ranges of splits; their partial sums
+  // meet in shared memory and are added in group order
+  const int rep_pad = p.rep <= 1 ? 1 : (p.rep <= 2 ? 2 : (p.rep <= 4 ? 4 : 8));
+  const int pairs = 16 * rep_pad, n_sg = kAttnThreads / pairs;
+  const int pair = threadIdx.x % pairs, sg = threadIdx.x / pairs;
+  const int mh = pair >> 4, mc = pair & 15;
+  const bool head_ok = mh < p.rep;
+  const int per = (p.n_split + n_sg - 1) / n_sg;
+  const int s_lo = sg * per, s_hi = min(p.n_split, s_lo + per);
+  constexpr int kPer = 5;   // splits per thread whose partial outputs are held in registers
+  float4 pa0[kPer], pa1[kPer];
+  const float* psrc = po + mh * kD + mc * 8;
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    const int sp = s_lo + k;
+    pa0[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    pa1[k] = pa0[k];
+    if (head_ok && sp < s_hi) {
+      pa0[k] = __ldcg(reinterpret_cast<const float4*>(psrc + (size_t)sp * (kHeads * kD)));
+      pa1[k] = __ldcg(reinterpret_cast<const float4*>(psrc + (size_t)sp * (kHeads * kD) + 4));
+    }
+  }
   float* w_s = reinterpret_cast<float*>(stage);   // [n_split][8]: max, then weight (the operand stage is free by now)
   float* l_s = w_s + p.n_split * kHeads;          // [n_split][8]: sum
   for (int i = threadIdx.x; i < p.n_split * kHeads; i += kAttnThreads) {
@@ -464,33 +497,54 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
     l_s[i] = hh < p.rep ? __ldcg(pm + i * 2 + 1) : 0.f;
   }
   __syncthreads();
-  if (threadIdx.x < kHeads) {
-    const int hh = threadIdx.x;
+  if (warp < p.rep) {   // one warp per head: weights of the splits and their sum
+    const int hh = warp;
     float M = kNegBig;
-    for (int s = 0; s < p.n_split; ++s) M = fmaxf(M, w_s[s * kHeads + hh]);
+    for (int sp = lane; sp < p.n_split; sp += 32) M = fmaxf(M, w_s[sp * kHeads + hh]);
+    M = warp_max(M);
     float L = 0.f;
-    for (int s = 0; s < p.n_split; ++s) {
-      const float w = __expf(w_s[s * kHeads + hh] - M);
-      w_s[s * kHeads + hh] = w;
-      L = fmaf(w, l_s[s * kHeads + hh], L);
+    for (int sp = lane; sp < p.n_split; sp += 32) {
+      const float w = __expf(w_s[sp * kHeads + hh] - M);
+      w_s[sp * kHeads + hh] = w;
+      L = fmaf(w, l_s[sp * kHeads + hh], L);
     }
-    st_l[hh] = L;
+    L = warp_sum(L);
+    if (lane == 0) st_l[hh] = L;
   }
   __syncthreads();
   {
-    // thread = (head, 8 channels); all threads run the loop so the half-warp sums below are whole
-    const int hh = threadIdx.x >> 4, c = threadIdx.x & 15;
-    const bool active = hh < p.rep;
+    const int hh = mh, c = mc;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (active) {
-      const float* src = po + hh * kD + c * 8;
+    if (head_ok) {
+#pragma unroll
+      for (int k = 0; k < kPer; ++k) {
+        const int sp = s_lo + k;
+        const float w = sp < s_hi ? w_s[sp * kHeads + hh] : 0.f;
+        acc[0] = fmaf(w, pa0[k].x, acc[0]); acc[1] = fmaf(w, pa0[k].y, acc[1]); acc[2] = fmaf(w, pa0[k].z, acc[2]); acc[3] = fmaf(w, pa0[k].w, acc[3]);
+        acc[4] = fmaf(w, pa1[k].x, acc[4]); acc[5] = fmaf(w, pa1[k].y, acc[5]); acc[6] = fmaf(w, pa1[k].z, acc[6]); acc[7] = fmaf(w, pa1[k].w, acc[7]);
+      }
 #pragma unroll 4
-      for (int s = 0; s < p.n_split; ++s) {
-        const float w = w_s[s * kHeads + hh];
-        const float4 a0 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)s * (kHeads * kD)));
-        const float4 a1 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)s * (kHeads * kD) + 4));
+      for (int sp = s_lo + kPer; sp < s_hi; ++sp) {   // long contexts: the rest in batches of four
+        const float w = w_s[sp * kHeads + hh];
+        const float4 a0 = __ldcg(reinterpret_cast<const float4*>(psrc + (size_t)sp * (kHeads * kD)));
+        const float4 a1 = __ldcg(reinterpret_cast<const float4*>(psrc + (size_t)sp * (kHeads * kD) + 4));
         acc[0] = fmaf(w, a0.x, acc[0]); acc[1] = fmaf(w, a0.y, acc[1]); acc[2] = fmaf(w, a0.z, acc[2]); acc[3] = fmaf(w, a0.w, acc[3]);
         acc[4] = fmaf(w, a1.x, acc[4]); acc[5] = fmaf(w, a1.y, acc[5]); acc[6] = fmaf(w, a1.z, acc[6]); acc[7] = fmaf(w, a1.w, acc[7]);
+      }
+    }
+    float* red = reinterpret_cast<float*>(stage + 16384);   // [n_sg][pairs][8], 8 KB
+    if (sg > 0) {
+      *reinterpret_cast<float4*>(red + (sg * pairs + pair) * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(red + (sg * pairs + pair) * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+    __syncthreads();
+    const bool active = head_ok && sg == 0;
+    if (active) {
+      for (int g2 = 1; g2 < n_sg; ++g2) {
+        const float4 a0 = *reinterpret_cast<const float4*>(red + (g2 * pairs + pair) * 8);
+        const float4 a1 = *reinterpret_cast<const float4*>(red + (g2 * pairs + pair) * 8 + 4);
+        acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w;
+        acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
       }
       const float L = st_l[hh];
 #pragma unroll
@@ -526,12 +580,10 @@ int pick_chunk(int B, int H, int n_comp, int group) {
   if (g_attn_chunk) {
     chunk = g_attn_chunk;
   } else {
-    // about two CTAs per SM; chunks of at most 256 tokens keep three CTAs resident per SM, which is what
-    // overlaps one CTA's copies with another's arithmetic once the grid is larger than the machine
-    const long long want = ((long long)n_comp * B * H + 295) / 296;
-    chunk = (int)((want + 127) / 128 * 128);
-    if (chunk < 128) chunk = 128;
-    if (chunk > 256) chunk = 256;
+    // 256 tokens per CTA: every warp has a 32-token group to score, three CTAs stay resident per SM (what overlaps
+    // one CTA's copies with another's arithmetic once the grid is larger than the machine), and the merge of
+    // a 4096-token context reads each split's partial output in one round trip
+    chunk = n_comp <= 128 ? 128 : 256;
     while (chunk < kMaxChunk && (n_comp + chunk - 1) / chunk > 96) chunk += 128;   // bound the merge
   }
   if (chunk % group) chunk = (chunk + group - 1) / group * group;
@@ -554,7 +606,7 @@ AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group) {
   a.p_stride = (span / 128) * 256 + 64;
   if (a.p_stride < 512) a.p_stride = 512;   // the residual branch reuses the buffer for an [8][128] fp32 reduction
   const int st = stage_bytes(a.chunk, group), rs = 2 * kResChunk * kResPitch;
-  a.smem = 128 + (size_t)kHeads * kD * sizeof(float) + (size_t)kHeads * a.s_stride * sizeof(float) +
+  a.smem = 128 + (size_t)kHeads * kQS * sizeof(float) + (size_t)kHeads * a.s_stride * sizeof(float) +
            2 * (size_t)kHeads * a.p_stride + (size_t)(st > rs ? st : rs);
   return a;
 }
@@ -611,7 +663,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
 
   const AttnPlan plan = make_attn_plan(B, H, n_comp, n_res, group);
   PARE_REQUIRE(plan.chunk % 128 == 0 && plan.chunk % group == 0 && plan.chunk <= kMaxChunk, PARE_ERR_UNSUPPORTED);
-  PARE_REQUIRE(plan.smem <= kAttnSmemCap && (size_t)plan.n_split * 2 * kHeads * sizeof(float) <= 2 * kResChunk * kResPitch, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE(plan.smem <= kAttnSmemCap && (size_t)plan.n_split * 2 * kHeads * sizeof(float) <= 16384, PARE_ERR_UNSUPPORTED);
 
   AttnParams p{};
   p.q = q; p.q_sb = q_stride_b; p.q_sh = q_stride_h;

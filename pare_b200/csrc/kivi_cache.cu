@@ -3,7 +3,8 @@
 // Storage of one layer (caller-owned, preallocated for `cap` tokens, cap % 128 == 0):
 //   k_codes [B][H][cap][D*bits/8]            codes packed along CHANNELS: channel c of a token
 //                                            sits at bit (c*bits) of the token's row (little endian)
-//   k_scale, k_zero [B][H][cap/group][D]     fp32 per (group of `group` tokens, channel)
+//   k_scale, k_zero [B][H][cap/group][D]     fp32 per (group of `group` tokens, channel); channel c at
+//                                            position kmeta_pos(c, D) of the row (common.cuh)
 //   v_codes [B][H][cap/128][D][128*bits/8]   codes packed along TOKENS inside blocks of 128 tokens:
 //                                            token t of the block sits at bit (t*bits) of row d
 //   v_scale, v_zero [B][H][cap]              fp32 per token
@@ -67,7 +68,7 @@ __global__ void kivi_append_kernel(const void* k_src, const void* v_src, int64_t
       hi = fmaxf(hi, x);
     }
     const float scale = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), qmax), 1e-8f);
-    const size_t mi = (bh * (c.cap / G) + tok0 / G) * D + d;
+    const size_t mi = (bh * (c.cap / G) + tok0 / G) * D + kmeta_pos(d, D);
     c.k_scale[mi] = scale;
     c.k_zero[mi] = lo;
     for (int t = 0; t < G; ++t) {
@@ -140,7 +141,7 @@ __global__ void kivi_dequant_kernel(CachePtrs c, int n_comp, void* out_k, void* 
   for (int t = blk * 128; t < t_end; ++t) {
     const uint8_t kb = c.k_codes[(bh * c.cap + t) * (size_t)k_row_bytes + (d * bits >> 3)];
     const float kq = (float)((kb >> ((d * bits) & 7)) & mask);
-    const size_t mi = (bh * (c.cap / G) + t / G) * D + d;
+    const size_t mi = (bh * (c.cap / G) + t / G) * D + kmeta_pos(d, D);
     ok[(int64_t)t * ot + d] = from_float<T>(__fadd_rn(__fmul_rn(kq, c.k_scale[mi]), c.k_zero[mi]));
     const int tl = t & 127;
     const uint8_t vb = vrow[tl * bits >> 3];

@@ -136,13 +136,22 @@ class _CompressedKV:
         blocks = _unpack_along_last(s.v_codes[:, :, :nb], s.cfg.bits, _V_BLOCK)        # [B,H,nb,D,128]
         return blocks.permute(0, 1, 2, 4, 3).reshape(s.B, s.H, nb * _V_BLOCK, s.D)[:, :, : s.n_comp].contiguous()
 
+    def _key_meta(self, stored: Tensor) -> Tensor:
+        """Stored key scale / zero rows -> channel order.  Inside every 128 channels the kernels keep the row as
+        [word (c>>3)&3][lane quad (c>>5)&3][c&7] (what the decode-attention kernel reads conflict-free)."""
+        s = self._s
+        rows = stored[:, :, : s.n_comp // s.cfg.group_size]
+        if s.D % 128:
+            return rows
+        return rows.unflatten(-1, (s.D // 128, 4, 4, 8)).transpose(-3, -2).flatten(-4)
+
     @property
     def k_scale(self) -> Tensor:
-        return self._s.k_scale[:, :, : self._s.n_comp // self._s.cfg.group_size]
+        return self._key_meta(self._s.k_scale)
 
     @property
     def k_zero(self) -> Tensor:
-        return self._s.k_zero[:, :, : self._s.n_comp // self._s.cfg.group_size]
+        return self._key_meta(self._s.k_zero)
 
     @property
     def v_scale(self) -> Tensor:
