@@ -16,7 +16,8 @@ public Python API with the hidden state copied from pinned host memory and the r
 back every step; ``roofline`` = the dominant kernel (fused gate|up dequant-GEMV) timed on its
 own over 32 distinct layers' weights; ``layers`` = us/layer and fraction of the measured HBM
 peak for every projection at M = 1/4/16; ``attention`` = the fused KIVI decode attention alone at
-batch 1 and batch 16; ``cpu_baseline`` = the reference's CPU op sequence
+batch 1 and batch 16; ``prefill_layers`` = the tensor-core path at M = 64 / 256 as a fraction of the
+measured dense bf16 peak; ``cpu_baseline`` = the reference's CPU op sequence
 (oracle port) timed on the host cores on a bounded sample.  ``--impl reference`` prints only
 that CPU arm.
 """
@@ -293,6 +294,32 @@ def layer_table(stack, peak: float, batches=(1, 4, 16)) -> dict:
     return table
 
 
+def prefill_table(stack, batches=(64, 256)) -> dict:
+    """Tensor-core path (tcgen05 tiles over dequantized operands, M > 48): us per layer, TFLOP/s and the fraction of
+    the measured dense bf16 peak (burst figure: each projection is timed alone)."""
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tf_peak = float(peaks.get("bf16_tflops", 1590.0))
+    table = {}
+    kinds = {"qkv": lambda b: b.qkv, "o": lambda b: b.o, "gate_up": lambda b: b.gate_up, "down": lambda b: b.down}
+    for name, pick in kinds.items():
+        layers = [pick(b) for b in stack.blocks][:8]
+        n, k = layers[0].out_features, layers[0].in_features
+        for m in batches:
+            x = torch.randn(m, k, device=stack.device, dtype=stack.dtype)
+
+            def run():
+                for layer in layers:
+                    layer(x)
+            g, _ = capture(run)
+            reps = 10
+            sec = time_events(g.replay, reps, 3, 1)
+            us = sec / (reps * len(layers)) * 1e6
+            tf = 2.0 * m * n * k / us / 1e6
+            table[f"{name}_{n}x{k}_m{m}"] = {"us_per_layer": round(us, 2), "tflops": round(tf, 1), "frac_tensor": round(tf / tf_peak, 4)}
+            del g
+    return table
+
+
 def attention_table(dtype, device, peak: float, cases=((1, 4096, 32), (16, 4096, 8))) -> dict:
     """Fused KIVI decode attention alone (8 KV heads, 32 query heads, D = 128, 4-bit g32, residual window 128):
     one CUDA graph over ``layers`` distinct caches (larger than L2 together), us per call and fraction of the HBM
@@ -390,6 +417,7 @@ def run_ours(args) -> None:
         table = {} if args.skip_layer_table else layer_table(stack, peak, tuple(int(b) for b in args.table_batches.split(",")))
         line["layers"] = table
         line["attention"] = {} if args.skip_layer_table else attention_table(dtype, stack.device, peak)
+        line["prefill_layers"] = {} if args.skip_layer_table else prefill_table(stack)
         key = f"gate_up_{blk.gate_up.out_features}x{blk.gate_up.in_features}_m{args.batch}"
         if key in table:
             achieved = table[key]["gbs"]
