@@ -320,15 +320,16 @@ def prefill_table(stack, batches=(64, 256)) -> dict:
     return table
 
 
-def attention_table(dtype, device, peak: float, cases=((1, 4096, 32), (16, 4096, 8))) -> dict:
-    """Fused KIVI decode attention alone (8 KV heads, 32 query heads, D = 128, 4-bit g32, residual window 128):
+def attention_table(dtype, device, peak: float, cases=((1, 4096, 32, 4), (16, 4096, 8, 4), (16, 4096, 8, 2))) -> dict:
+    """Fused KIVI decode attention alone (8 KV heads, 32 query heads, D = 128, g32, residual window 128):
     one CUDA graph over ``layers`` distinct caches (larger than L2 together), us per call and fraction of the HBM
-    peak by the bytes the call must read (168 B per compressed token and KV head, 512 B per window token)."""
+    peak by the bytes the call must read (168 B per compressed token and KV head at 4 bits, 104 B at 2 bits,
+    512 B per window token)."""
     from pare_b200.kv_cache import KVCacheConfig, QuantizedKVCache
 
     table = {}
-    for batch, ctx, layers in cases:
-        cache = QuantizedKVCache(layers, KVCacheConfig(bits=4, group_size=32, residual_length=128), max_seq_len=ctx + 256)
+    for batch, ctx, layers, bits in cases:
+        cache = QuantizedKVCache(layers, KVCacheConfig(bits=bits, group_size=32, residual_length=128), max_seq_len=ctx + 256)
         g = torch.Generator(device=device).manual_seed(0)
         n0 = 128 + ((ctx - 128) // 32) * 32
         for layer in range(layers):
@@ -349,8 +350,8 @@ def attention_table(dtype, device, peak: float, cases=((1, 4096, 32), (16, 4096,
         sec = time_events(gr.replay, reps, 3, 1)
         us = sec / (reps * layers) * 1e6
         st = cache._stores[0]
-        nbytes = batch * 8 * (st.n_comp * 168 + (st.r_len + 1) * 512) + batch * 32 * 128 * 4
-        table[f"b{batch}_ctx{ctx}"] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peak, 4)}
+        nbytes = batch * 8 * (st.n_comp * (168 if bits == 4 else 104) + (st.r_len + 1) * 512) + batch * 32 * 128 * 4
+        table[f"b{batch}_ctx{ctx}_{bits}bit"] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peak, 4)}
         del gr, cache
     return table
 

@@ -183,7 +183,7 @@ int pare_kivi_dequant(const uint8_t* k_codes, const float* k_scale, const float*
  *   out           may be NULL when prepared_out is given
  *   prepared_out  NULL, or a pare_w4a16_prepared_bytes(B, Hq*D) buffer that receives the result as
  *                 prepared activations of the next W4A16 linear (B <= 16)
- * D == 128, bits == 4.  workspace: pare_kivi_attn_workspace_bytes(), zero-filled once
+ * D == 128, bits == 4 or 2.  workspace: pare_kivi_attn_workspace_bytes(), zero-filled once
  * (same contract as the W4A16 workspace; one buffer may serve both). */
 size_t pare_kivi_attn_workspace_bytes(int B, int H, int n_comp, int n_res);
 

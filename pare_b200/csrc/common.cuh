@@ -137,6 +137,19 @@ __device__ __forceinline__ void unpack_codes_exact(uint32_t w, uint32_t (&p)[4])
   p[3] = *reinterpret_cast<uint32_t*>(&h3);
 }
 
+// Same for 2-bit codes: a word holds c0..c15 (c_i at bits 2i); the eight results are the pairs (c_j, c_{j+8}),
+// each code - CENTER exactly.
+template <int CENTER>
+__device__ __forceinline__ void unpack_codes2_exact(uint32_t w, uint32_t (&p)[8]) {
+  const __half2 off = __float2half2_rn(1024.f + CENTER);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint32_t r = and_or(w >> (2 * j), 0x00030003u, 0x64006400u);
+    __half2 h = __hsub2(*reinterpret_cast<__half2*>(&r), off);
+    p[j] = *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
 template <>
 struct Nibbles<__nv_bfloat16> {
   static constexpr float kOffsetLo = 128.f;

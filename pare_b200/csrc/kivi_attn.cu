@@ -116,13 +116,26 @@ __device__ __forceinline__ uint32_t pair_to_h2<__nv_bfloat16>(uint32_t raw) {
 __device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // bytes of the operand stage of a compressed split
-__host__ __device__ inline int stage_bytes(int chunk, int group) {
-  return chunk * 64 + 2 * (chunk / group) * kD * 4 + (chunk / 128) * kD * 64 + 2 * chunk * 4;
+__host__ __device__ inline int stage_bytes(int chunk, int group, int bits) {
+  return chunk * (kD * bits / 8) + 2 * (chunk / group) * kD * 4 + (chunk / 128) * kD * (128 * bits / 8) + 2 * chunk * 4;
 }
 
-template <typename T>
+// codes - CENTER of one word as exact fp16 pairs: four pairs (c_k, c_k+4) at 4 bits, eight pairs (c_j, c_j+8) at 2 bits
+template <int BITS, int CENTER>
+__device__ __forceinline__ void unpack_exact(uint32_t w, uint32_t (&p)[BITS == 4 ? 4 : 8]) {
+  if constexpr (BITS == 4) unpack_codes_exact<CENTER>(w, p);
+  else unpack_codes2_exact<CENTER>(w, p);
+}
+
+template <typename T, int BITS>
 __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int NW = BITS == 4 ? 4 : 2;          // code words of the 32 channels / tokens a lane owns
+  constexpr int PW = BITS == 4 ? 4 : 8;          // fp16 pairs per word
+  constexpr int LB = 4 * BITS;                   // bytes of those 32 codes
+  constexpr int KROW = kD * BITS / 8;            // bytes of a token's key codes
+  constexpr int VROW = 128 * BITS / 8;           // bytes of a channel's value codes in a 128-token block
+  constexpr int VCENTER = BITS == 4 ? 8 : 2;     // value codes are centred (halves the magnitude of the products)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -154,10 +167,10 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
   // operand stage of a compressed split
   const int ngr_full = p.chunk / p.group;
   unsigned char* kc_s = stage;
-  float* ks_s = reinterpret_cast<float*>(kc_s + p.chunk * 64);
+  float* ks_s = reinterpret_cast<float*>(kc_s + p.chunk * KROW);
   float* kz_s = ks_s + ngr_full * kD;
   unsigned char* vc_s = reinterpret_cast<unsigned char*>(kz_s + ngr_full * kD);
-  float* vs_s = reinterpret_cast<float*>(vc_s + (p.chunk / 128) * kD * 64);
+  float* vs_s = reinterpret_cast<float*>(vc_s + (p.chunk / 128) * kD * VROW);
   float* vz_s = vs_s + p.chunk;
 
   if (!is_res) {
@@ -167,11 +180,11 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       // the compressed cache does not change during a decode step: fetch before the dependency wait
       const int ngroups = valid / p.group, nblk = (valid + 127) >> 7;
       const size_t grow = bh * (p.cap / p.group) + chunk_start / p.group;
-      mbar_expect_tx(bar, valid * 64 + 2 * ngroups * kD * 4 + nblk * kD * 64 + 2 * valid * 4);
-      bulk_load(smem_u32(kc_s), p.k_codes + (bh * p.cap + chunk_start) * 64, valid * 64, bar);
+      mbar_expect_tx(bar, valid * KROW + 2 * ngroups * kD * 4 + nblk * kD * VROW + 2 * valid * 4);
+      bulk_load(smem_u32(kc_s), p.k_codes + (bh * p.cap + chunk_start) * (size_t)KROW, valid * KROW, bar);
       bulk_load(smem_u32(ks_s), p.k_scale + grow * kD, ngroups * kD * 4, bar);
       bulk_load(smem_u32(kz_s), p.k_zero + grow * kD, ngroups * kD * 4, bar);
-      bulk_load(smem_u32(vc_s), p.v_codes + (bh * (p.cap / 128) + (chunk_start >> 7)) * (size_t)(kD * 64), nblk * kD * 64, bar);
+      bulk_load(smem_u32(vc_s), p.v_codes + (bh * (p.cap / 128) + (chunk_start >> 7)) * (size_t)(kD * VROW), nblk * kD * VROW, bar);
       bulk_load(smem_u32(vs_s), p.v_scale + bh * p.cap + chunk_start, valid * 4, bar);
       bulk_load(smem_u32(vz_s), p.v_zero + bh * p.cap + chunk_start, valid * 4, bar);
     }
@@ -247,29 +260,41 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
     for (int item = warp; item < n_items; item += kAttnWarps) {
       const int gl = split_tiles ? item / tpg : item;
       const int tile_lo = split_tiles ? item - gl * tpg : 0, tile_hi = split_tiles ? tile_lo + 1 : tpg;
-      const unsigned char* krow = kc_s + (gl * G) * 64 + tig * 16;
-      const float* ks = ks_s + gl * kD + tig * 8;   // rows in kmeta_pos order: word i of this lane at i * 32 + tig * 8
+      const unsigned char* krow = kc_s + (gl * G) * KROW + tig * LB;
+      const float* ks = ks_s + gl * kD + tig * 8;   // rows in kmeta_pos order: channels 8u .. 8u+7 of this lane at u * 32 + tig * 8
       const float* kz = kz_s + gl * kD + tig * 8;
       const float* qrow = qf + gid * kQS + tig * 8;
       // q * scale as a two-term fp16 expansion (hi + lo, ~22 bits): a single fp16 rounding of
-      // this operand would move the logits by more than the reference's own fp16 cast of K^
-      uint32_t xh[4][4], xl[4][4];
+      // this operand would move the logits by more than the reference's own fp16 cast of K^.
+      // xh / xl[w * PW + j]: the operand pair that meets pair j of code word w.
+      uint32_t xh[16], xl[16];
       float bias = 0.f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float4 s0 = *reinterpret_cast<const float4*>(ks + i * 32);
-        const float4 s1 = *reinterpret_cast<const float4*>(ks + i * 32 + 4);
-        const float4 z0 = *reinterpret_cast<const float4*>(kz + i * 32);
-        const float4 z1 = *reinterpret_cast<const float4*>(kz + i * 32 + 4);
-        const float4 q0 = *reinterpret_cast<const float4*>(qrow + i * 32);
-        const float4 q1 = *reinterpret_cast<const float4*>(qrow + i * 32 + 4);
-        bias = fmaf(q0.x, z0.x, bias); bias = fmaf(q0.y, z0.y, bias); bias = fmaf(q0.z, z0.z, bias); bias = fmaf(q0.w, z0.w, bias);
-        bias = fmaf(q1.x, z1.x, bias); bias = fmaf(q1.y, z1.y, bias); bias = fmaf(q1.z, z1.z, bias); bias = fmaf(q1.w, z1.w, bias);
-        // operand order of one code word: (c0,c4) (c1,c5) (c2,c6) (c3,c7)
-        split_h2(q0.x * s0.x, q1.x * s1.x, xh[i][0], xl[i][0]);
-        split_h2(q0.y * s0.y, q1.y * s1.y, xh[i][1], xl[i][1]);
-        split_h2(q0.z * s0.z, q1.z * s1.z, xh[i][2], xl[i][2]);
-        split_h2(q0.w * s0.w, q1.w * s1.w, xh[i][3], xl[i][3]);
+      for (int h2 = 0; h2 < 2; ++h2) {   // sixteen channels (two runs of eight) at a time
+        float pr[2][8];
+#pragma unroll
+        for (int u2 = 0; u2 < 2; ++u2) {
+          const int u = h2 * 2 + u2;
+          const float4 s0 = *reinterpret_cast<const float4*>(ks + u * 32);
+          const float4 s1 = *reinterpret_cast<const float4*>(ks + u * 32 + 4);
+          const float4 z0 = *reinterpret_cast<const float4*>(kz + u * 32);
+          const float4 z1 = *reinterpret_cast<const float4*>(kz + u * 32 + 4);
+          const float4 q0 = *reinterpret_cast<const float4*>(qrow + u * 32);
+          const float4 q1 = *reinterpret_cast<const float4*>(qrow + u * 32 + 4);
+          bias = fmaf(q0.x, z0.x, bias); bias = fmaf(q0.y, z0.y, bias); bias = fmaf(q0.z, z0.z, bias); bias = fmaf(q0.w, z0.w, bias);
+          bias = fmaf(q1.x, z1.x, bias); bias = fmaf(q1.y, z1.y, bias); bias = fmaf(q1.z, z1.z, bias); bias = fmaf(q1.w, z1.w, bias);
+          pr[u2][0] = q0.x * s0.x; pr[u2][1] = q0.y * s0.y; pr[u2][2] = q0.z * s0.z; pr[u2][3] = q0.w * s0.w;
+          pr[u2][4] = q1.x * s1.x; pr[u2][5] = q1.y * s1.y; pr[u2][6] = q1.z * s1.z; pr[u2][7] = q1.w * s1.w;
+        }
+        if constexpr (BITS == 4) {   // a word is one run of eight channels: pairs (c_k, c_k+4)
+#pragma unroll
+          for (int u2 = 0; u2 < 2; ++u2)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) split_h2(pr[u2][k], pr[u2][k + 4], xh[(h2 * 2 + u2) * 4 + k], xl[(h2 * 2 + u2) * 4 + k]);
+        } else {                      // a word is both runs: pairs (c_j, c_j+8)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) split_h2(pr[0][j], pr[1][j], xh[h2 * 8 + j], xl[h2 * 8 + j]);
+        }
       }
       bias += __shfl_xor_sync(0xffffffffu, bias, 1);
       bias += __shfl_xor_sync(0xffffffffu, bias, 2);
@@ -277,20 +302,32 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       const float c1 = __shfl_sync(0xffffffffu, bias, (tig * 2 + 1) * 4);
 
       for (int tile = tile_lo; tile < tile_hi; ++tile) {
-        const uint4 wa4 = *reinterpret_cast<const uint4*>(krow + (tile * 16 + gid) * 64);
-        const uint4 wb4 = *reinterpret_cast<const uint4*>(krow + (tile * 16 + gid + 8) * 64);
-        const uint32_t wa[4] = {wa4.x, wa4.y, wa4.z, wa4.w};
-        const uint32_t wb[4] = {wb4.x, wb4.y, wb4.z, wb4.w};
+        uint32_t wa[NW], wb[NW];
+        if constexpr (BITS == 4) {
+          const uint4 wa4 = *reinterpret_cast<const uint4*>(krow + (tile * 16 + gid) * KROW);
+          const uint4 wb4 = *reinterpret_cast<const uint4*>(krow + (tile * 16 + gid + 8) * KROW);
+          wa[0] = wa4.x; wa[1] = wa4.y; wa[2] = wa4.z; wa[3] = wa4.w;
+          wb[0] = wb4.x; wb[1] = wb4.y; wb[2] = wb4.z; wb[3] = wb4.w;
+        } else {
+          const uint2 wa2 = *reinterpret_cast<const uint2*>(krow + (tile * 16 + gid) * KROW);
+          const uint2 wb2 = *reinterpret_cast<const uint2*>(krow + (tile * 16 + gid + 8) * KROW);
+          wa[0] = wa2.x; wa[1] = wa2.y;
+          wb[0] = wb2.x; wb[1] = wb2.y;
+        }
         float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t pa[4], pb[4];
-          unpack_codes_exact<0>(wa[i], pa);
-          unpack_codes_exact<0>(wb[i], pb);
-          mma16816<__half>(d0, pa[0], pb[0], pa[1], pb[1], xh[i][0], xh[i][1]);
-          mma16816<__half>(d1, pa[2], pb[2], pa[3], pb[3], xh[i][2], xh[i][3]);
-          mma16816<__half>(d0, pa[0], pb[0], pa[1], pb[1], xl[i][0], xl[i][1]);
-          mma16816<__half>(d1, pa[2], pb[2], pa[3], pb[3], xl[i][2], xl[i][3]);
+        for (int w = 0; w < NW; ++w) {
+          uint32_t pa[PW], pb[PW];
+          unpack_exact<BITS, 0>(wa[w], pa);
+          unpack_exact<BITS, 0>(wb[w], pb);
+#pragma unroll
+          for (int q4 = 0; q4 < PW / 4; ++q4) {
+            const int x0 = w * PW + q4 * 4;
+            mma16816<__half>(d0, pa[q4 * 4], pb[q4 * 4], pa[q4 * 4 + 1], pb[q4 * 4 + 1], xh[x0], xh[x0 + 1]);
+            mma16816<__half>(d1, pa[q4 * 4 + 2], pb[q4 * 4 + 2], pa[q4 * 4 + 3], pb[q4 * 4 + 3], xh[x0 + 2], xh[x0 + 3]);
+            mma16816<__half>(d0, pa[q4 * 4], pb[q4 * 4], pa[q4 * 4 + 1], pb[q4 * 4 + 1], xl[x0], xl[x0 + 1]);
+            mma16816<__half>(d1, pa[q4 * 4 + 2], pb[q4 * 4 + 2], pa[q4 * 4 + 3], pb[q4 * 4 + 3], xl[x0 + 2], xl[x0 + 3]);
+          }
         }
         const int tl = gl * G + tile * 16 + gid;
         float* s0 = S + (tig * 2) * p.s_stride + tl;
@@ -318,14 +355,22 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
           const float e = __expf(srow[t] - m);
           l += e;
           const float sc = vs_s[t];
-          z = fmaf(e, fmaf(8.f, sc, vz_s[t]), z);   // value codes are centred at 8 in phase C
+          z = fmaf(e, fmaf((float)VCENTER, sc, vz_s[t]), z);   // value codes are centred in phase C
           pv = e * sc;
         }
-        // operand layout of a 128-token block: [word 0..3][quad 0..3] chunks of 8 halves, slots 0,4,1,5,2,6,3,7
-        const int tl = t & 127, pos = tl & 7;
-        const int slot = ((pos & 3) << 1) | (pos >> 2);
+        // operand layout of a 128-token block: [4 operand quads][lane quad 0..3] chunks of 8 halves = four pairs, in the
+        // order the pairs of the value code words come out of the unpack (4 bits: (t_k, t_k+4) per 8 tokens; 2 bits:
+        // (t_j, t_j+8) per 16 tokens)
+        const int tl = t & 127;
+        int off;
+        if constexpr (BITS == 4) {
+          const int pos = tl & 7;
+          off = (t >> 7) * 256 + ((tl >> 3) & 3) * 64 + (tl >> 5) * 16 + ((((pos & 3) << 1) | (pos >> 2)) * 2);
+        } else {
+          const int e = tl & 15, j = e & 7;
+          off = (t >> 7) * 256 + ((((tl >> 4) & 1) * 2 + (j >> 2)) * 64) + (tl >> 5) * 16 + (((j & 3) * 2 + (e >> 3)) * 2);
+        }
         // two-term fp16 expansion of p * scale (hi + residual): keeps P.V at fp32-level accuracy
-        const int off = (t >> 7) * 256 + ((tl >> 3) & 3) * 64 + (tl >> 5) * 16 + slot * 2;
         const __half hv = __float2half_rn(pv);
         *reinterpret_cast<__half*>(prow + off) = hv;
         *reinterpret_cast<__half*>(prow + kHeads * p.p_stride + off) = __float2half_rn(pv - __half2float(hv));
@@ -343,27 +388,39 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
     // ================= phase C: O^T[c][h] = sum_t code_v[t][c] * P'[t][h] =================
     {
       const int row = warp * 16 + gid;  // channel
-      const unsigned char* vbase = vc_s + row * 64 + tig * 16;
+      const unsigned char* vbase = vc_s + row * VROW + tig * LB;
       float o0[4] = {0.f, 0.f, 0.f, 0.f}, o1[4] = {0.f, 0.f, 0.f, 0.f};
       for (int blk = 0; blk < nblk; ++blk) {
-        const uint4 va = *reinterpret_cast<const uint4*>(vbase + blk * (kD * 64));
-        const uint4 vb = *reinterpret_cast<const uint4*>(vbase + blk * (kD * 64) + 8 * 64);
-        const uint32_t wa[4] = {va.x, va.y, va.z, va.w};
-        const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
+        uint32_t wa[NW], wb[NW];
+        if constexpr (BITS == 4) {
+          const uint4 va = *reinterpret_cast<const uint4*>(vbase + blk * (kD * VROW));
+          const uint4 vb = *reinterpret_cast<const uint4*>(vbase + blk * (kD * VROW) + 8 * VROW);
+          wa[0] = va.x; wa[1] = va.y; wa[2] = va.z; wa[3] = va.w;
+          wb[0] = vb.x; wb[1] = vb.y; wb[2] = vb.z; wb[3] = vb.w;
+        } else {
+          const uint2 va = *reinterpret_cast<const uint2*>(vbase + blk * (kD * VROW));
+          const uint2 vb = *reinterpret_cast<const uint2*>(vbase + blk * (kD * VROW) + 8 * VROW);
+          wa[0] = va.x; wa[1] = va.y;
+          wb[0] = vb.x; wb[1] = vb.y;
+        }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 pf = make_uint4(0u, 0u, 0u, 0u), pl = make_uint4(0u, 0u, 0u, 0u);
-          if (gid < p.rep) {
-            pf = *reinterpret_cast<const uint4*>(P + gid * p.p_stride + blk * 256 + i * 64 + tig * 16);
-            pl = *reinterpret_cast<const uint4*>(P2 + gid * p.p_stride + blk * 256 + i * 64 + tig * 16);
+        for (int w = 0; w < NW; ++w) {
+          uint32_t pa[PW], pb[PW];
+          unpack_exact<BITS, VCENTER>(wa[w], pa);
+          unpack_exact<BITS, VCENTER>(wb[w], pb);
+#pragma unroll
+          for (int q4 = 0; q4 < PW / 4; ++q4) {
+            const int i = w * (PW / 4) + q4;   // operand quad
+            uint4 pf = make_uint4(0u, 0u, 0u, 0u), pl = make_uint4(0u, 0u, 0u, 0u);
+            if (gid < p.rep) {
+              pf = *reinterpret_cast<const uint4*>(P + gid * p.p_stride + blk * 256 + i * 64 + tig * 16);
+              pl = *reinterpret_cast<const uint4*>(P2 + gid * p.p_stride + blk * 256 + i * 64 + tig * 16);
+            }
+            mma16816<__half>(o0, pa[q4 * 4], pb[q4 * 4], pa[q4 * 4 + 1], pb[q4 * 4 + 1], pf.x, pf.y);
+            mma16816<__half>(o1, pa[q4 * 4 + 2], pb[q4 * 4 + 2], pa[q4 * 4 + 3], pb[q4 * 4 + 3], pf.z, pf.w);
+            mma16816<__half>(o0, pa[q4 * 4], pb[q4 * 4], pa[q4 * 4 + 1], pb[q4 * 4 + 1], pl.x, pl.y);
+            mma16816<__half>(o1, pa[q4 * 4 + 2], pb[q4 * 4 + 2], pa[q4 * 4 + 3], pb[q4 * 4 + 3], pl.z, pl.w);
           }
-          uint32_t pa[4], pb[4];
-          unpack_codes_exact<8>(wa[i], pa);
-          unpack_codes_exact<8>(wb[i], pb);
-          mma16816<__half>(o0, pa[0], pb[0], pa[1], pb[1], pf.x, pf.y);
-          mma16816<__half>(o1, pa[2], pb[2], pa[3], pb[3], pf.z, pf.w);
-          mma16816<__half>(o0, pa[0], pb[0], pa[1], pb[1], pl.x, pl.y);
-          mma16816<__half>(o1, pa[2], pb[2], pa[3], pb[3], pl.z, pl.w);
         }
       }
 #pragma unroll
@@ -598,7 +655,7 @@ struct AttnPlan {
   size_t smem;
 };
 
-AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group) {
+AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group, int bits) {
   AttnPlan a;
   a.chunk = pick_chunk(B, H, n_comp, group);
   a.n_csplit = (n_comp + a.chunk - 1) / a.chunk;
@@ -608,7 +665,7 @@ AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group) {
   a.s_stride = span + 4;
   a.p_stride = (span / 128) * 256 + 64;
   if (a.p_stride < 512) a.p_stride = 512;   // the residual branch reuses the buffer for an [8][128] fp32 reduction
-  const int st = stage_bytes(a.chunk, group), rs = 2 * kResChunk * kResPitch;
+  const int st = stage_bytes(a.chunk, group, bits), rs = 2 * kResChunk * kResPitch;
   a.smem = 128 + (size_t)kHeads * kQS * sizeof(float) + (size_t)kHeads * a.s_stride * sizeof(float) +
            2 * (size_t)kHeads * a.p_stride + (size_t)(st > rs ? st : rs);
   return a;
@@ -637,7 +694,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
                           int bits, int group, int cap, void* workspace, size_t workspace_bytes, void* stream) {
   using namespace pare;
   PARE_REQUIRE(B > 0 && Hq > 0 && H > 0 && Hq % H == 0, PARE_ERR_SHAPE);
-  PARE_REQUIRE(D == kD && bits == 4, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE(D == kD && (bits == 4 || bits == 2), PARE_ERR_UNSUPPORTED);
   PARE_REQUIRE(Hq / H <= kHeads, PARE_ERR_UNSUPPORTED);
   PARE_REQUIRE(group == 16 || group == 32 || group == 64 || group == 128, PARE_ERR_UNSUPPORTED);
   PARE_REQUIRE(dtype == PARE_F16 || dtype == PARE_BF16, PARE_ERR_DTYPE);
@@ -664,7 +721,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
                      aligned16(v_zero),
                  PARE_ERR_ALIGN);
 
-  const AttnPlan plan = make_attn_plan(B, H, n_comp, n_res, group);
+  const AttnPlan plan = make_attn_plan(B, H, n_comp, n_res, group, bits);
   PARE_REQUIRE(plan.chunk % 128 == 0 && plan.chunk % group == 0 && plan.chunk <= kMaxChunk, PARE_ERR_UNSUPPORTED);
   PARE_REQUIRE(plan.smem <= kAttnSmemCap && (size_t)plan.n_split * 2 * kHeads * sizeof(float) <= 16384, PARE_ERR_UNSUPPORTED);
 
@@ -704,7 +761,8 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess ? PARE_OK : PARE_ERR_CUDA;
   };
-  return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half>) : launch(kivi_decode_attn_kernel<__nv_bfloat16>);
+  if (bits == 4) return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 4>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 4>);
+  return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 2>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 2>);
 }
 
 }  // extern "C"

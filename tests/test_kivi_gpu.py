@@ -183,7 +183,7 @@ def test_cpu_tensors_rejected(cuda_lib):
 
 # ---- fused decode attention ------------------------------------------------------------------
 
-def _attn_case(bsz, hkv, hq, ctx, dtype, residual=128, group=32, seed=0):
+def _attn_case(bsz, hkv, hq, ctx, dtype, residual=128, group=32, seed=0, bits=4):
     g = torch.Generator().manual_seed(seed)
     k = torch.randn(bsz, hkv, ctx, D, generator=g)
     v = torch.randn(bsz, hkv, ctx, D, generator=g)
@@ -191,11 +191,11 @@ def _attn_case(bsz, hkv, hq, ctx, dtype, residual=128, group=32, seed=0):
     k[..., idx] *= 10.0                                  # outlier channels
     q = torch.randn(bsz, hq, 1, D, generator=g)
     k, v, q = k.to(dtype).cuda(), v.to(dtype).cuda(), q.to(dtype).cuda()
-    cfg = KVCacheConfig(bits=4, group_size=group, residual_length=residual)
+    cfg = KVCacheConfig(bits=bits, group_size=group, residual_length=residual)
     cache = QuantizedKVCache(1, cfg, max_seq_len=ctx + 256)
     cache.update(0, k[:, :, :-1], v[:, :, :-1])
     out = cache.attend(0, q, k[:, :, -1:], v[:, :, -1:])
-    ref_cache = ok.Cache(4, group, residual)
+    ref_cache = ok.Cache(bits, group, residual)
     rk, rv = ref_cache.update(k.float().cpu().numpy(), v.float().cpu().numpy())
     cast = (lambda a: torch.from_numpy(a).to(dtype).float().numpy())
     qf = q.float().cpu().numpy()
@@ -211,6 +211,15 @@ def test_decode_attention_matches_oracle(bsz, hkv, hq, ctx, dtype, cuda_lib):
     assert out.shape == (bsz, hq, 1, D) and out.dtype == dtype
     o = out.float().cpu().numpy()
     _check_attn(o, ref, ref32, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bsz,hkv,hq,ctx,group", [(1, 4, 28, 1000, 32), (2, 2, 16, 4096, 32), (1, 1, 8, 200, 16), (1, 2, 4, 700, 64)])
+def test_decode_attention_two_bit_cache(bsz, hkv, hq, ctx, group, dtype, cuda_lib):
+    """The same kernel over a 2-bit cache (16 codes per word, pairs (c_j, c_j+8)); same bars: the kernel's arithmetic
+    is exact on the stored codes, so the coarser quantization is in the oracle's K^ / V^ as well."""
+    out, ref, _, ref32 = _attn_case(bsz, hkv, hq, ctx, dtype, group=group, residual=64 if group == 64 else 128, bits=2, seed=ctx)
+    _check_attn(out.float().cpu().numpy(), ref, ref32, dtype)
 
 
 def _check_attn(o, ref, ref32, dtype):
