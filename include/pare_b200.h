@@ -98,7 +98,7 @@ void pare_w4a16_set_tuning(int reserved, int columns_per_cta, int warps_per_cta)
  * pare_w4a16_prepared_bytes(M, K) bytes (0 if unsupported: M > 16 or K % 128 != 0), and tied to
  * the activation dtype.  pare_w4a16_prepare fills one from a plain x (applying the act-order
  * gather and the run-time input scale if given); pare_w4a16_forward_prepared is
- * pare_w4a16_forward minus x / col_perm / input_scale and needs K % 512 == 0, group % 128 == 0
+ * pare_w4a16_forward minus x / col_perm / input_scale and needs K % 256 == 0, group % 128 == 0
  * (PARE_ERR_UNSUPPORTED otherwise: use the plain call). */
 size_t pare_w4a16_prepared_bytes(int M, int K);
 int pare_w4a16_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_perm, const float* input_scale,
@@ -116,7 +116,7 @@ int pare_w4a16_forward_prepared(const void* prepared, int x_dtype,
  *                           resid_out [M][lda] or NULL receives a + b (must not alias a)
  *   PARE_PRODUCER_SILU_MUL  x = silu(a[:, 0:K]) * a[:, K:2K]; a = fused gate|up [M][lda], lda >= 2 K
  * a, b, c, resid_out have the activation dtype, are 16-byte aligned, lda % 8 == 0.  Needs
- * K % 512 == 0 and group % 128 == 0 (PARE_ERR_UNSUPPORTED otherwise).  Cases the fused staging does
+ * K % 256 == 0 and group % 128 == 0 (PARE_ERR_UNSUPPORTED otherwise).  Cases the fused staging does
  * not cover (M > 4, a row longer than one CTA's K range) run as the stand-alone glue kernel
  * followed by pare_w4a16_forward_prepared on a part of the workspace: same result. */
 enum { PARE_PRODUCER_RMSNORM = 1, PARE_PRODUCER_SILU_MUL = 2 };
@@ -242,13 +242,14 @@ int pare_w4a16_forward_static(const void* x, int x_dtype, int64_t ldx,
  * One-shot all-reduce of a small activation tensor over NVLink peer memory, for tensor-parallel
  * decode (the two partial sums per block after the row-parallel o and down projections).  No
  * counterpart in the reference, which is single-GPU.  Every rank stores its partial into every
- * peer's exchange buffer (plain peer stores), raises a flag, waits (bounded) for its own flags and
- * adds the partials in rank order: fp32, deterministic, the same bits on every rank; one launch.
+ * peer's exchange buffer (plain peer stores; each 8 bytes travel with their own validity marks, so
+ * there is no fence and no separate flag) and adds the partials from its own buffer in rank order as
+ * they arrive (bounded waits): fp32, deterministic, the same bits on every rank; one launch.
  *   pare_peer_buffer_create  allocates and zeroes this rank's exchange buffer and returns its
  *                            64-byte CUDA IPC handle (to be sent to the peers by any host channel)
  *   pare_peer_buffer_open    maps a peer's buffer from its handle; _close unmaps; _destroy frees
- *   pare_peer_allreduce      y = sum over ranks of x, [rows][cols] F16/BF16, cols % 8 == 0,
- *                            rows*cols*2 <= (buffer_bytes - 4096) / (2 * world); buffers = HOST array
+ *   pare_peer_allreduce      y = sum over ranks of x, [rows][cols] F16/BF16, cols % 4 == 0,
+ *                            rows*cols*4 <= (buffer_bytes - 4096) / (2 * world); buffers = HOST array
  *                            of `world` device pointers (own buffer at index `rank`); 2 <= world <= 8;
  *                            every rank makes the same sequence of calls; capturable in a CUDA graph
  *   pare_peer_status         0 or PARE_ERR_TIMEOUT (a wait for a peer ran out); synchronises `stream`

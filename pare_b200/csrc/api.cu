@@ -110,7 +110,7 @@ int pare_w4a16_forward_produced(int producer, const void* a, const void* b, cons
                                 const void* meta_h2, const void* bias, void* y, int64_t ldy, int M, int N, int K,
                                 int group_size, void* workspace, size_t workspace_bytes, void* stream) {
   PARE_REQUIRE(M > 0 && M <= 16 && N > 0 && K > 0 && group_size > 0, PARE_ERR_SHAPE);
-  PARE_REQUIRE((K % 512) == 0 && (group_size % 128) == 0 && (K % group_size) == 0 && ldy >= N, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE((K % 256) == 0 && (group_size % 128) == 0 && (K % group_size) == 0 && ldy >= N, PARE_ERR_UNSUPPORTED);
   PARE_REQUIRE(x_dtype == PARE_F16 || x_dtype == PARE_BF16, PARE_ERR_DTYPE);
   PARE_REQUIRE(a && packed && y && (meta_h2 || (scale && zero)), PARE_ERR_SHAPE);
   PARE_REQUIRE(pare::aligned16(a) && lda % 8 == 0, PARE_ERR_ALIGN);

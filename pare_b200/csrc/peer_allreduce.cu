@@ -1,18 +1,21 @@
 // One-shot all-reduce of a small activation tensor over NVLink peer memory, sm_100a.
 //
 // Tensor-parallel decode sums two [rows x hidden] partial results per block (after the o and the
-// down projection).  At decode sizes (a few KB) a library all-reduce is all latency; here every
-// rank simply stores its partial into a slot of every peer's exchange buffer (plain peer stores,
-// no multicast), raises a flag there, waits for the flags of its own buffer and adds the slots in
-// rank order (fp32, deterministic, identical on all ranks).  One kernel launch per all-reduce.
+// down projection).  At decode sizes (a few KB) an all-reduce is all latency, so the protocol has no
+// fence and no separate flag: every rank stores its partial into a slot of every peer's exchange
+// buffer as 16-byte units {4 bytes data, epoch, 4 bytes data, epoch} (plain peer stores, no
+// multicast) -- each 8-byte half carries its own validity mark and arrives atomically -- and then
+// reads the slots of its own buffer, spinning (bounded) on each unit until both marks show the
+// current epoch, adding the ranks' values in rank order (fp32, deterministic, the same bits on all
+// ranks).  One kernel launch per all-reduce, one NVLink store latency end to end.
 //
 // Exchange buffer of a rank (allocated by pare_peer_buffer_create, mapped into the peers with
-// CUDA IPC):  [0, 4096): header -- epoch[kMaxCtas] ints, then flags[2][kMaxRanks][kMaxCtas] ints;
-// [4096, ...): data[2][world][slot].  Slots and flags are double-buffered by the parity of a
-// per-CTA epoch that the kernel itself advances, so a captured CUDA graph can be replayed: a rank
-// can only be one call ahead of a peer (it needs the peer's flag of the current call to finish).
-// The wait is bounded; a timeout sets PARE_ERR_TIMEOUT in the header's status word and the call
-// returns whatever it has (the host reads the word with pare_peer_status).
+// CUDA IPC):  [0, 4096): header -- epoch[kMaxCtas] ints, status word; [4096, ...): data[2][world][slot].
+// Slots are double-buffered by the parity of a per-CTA epoch that the kernel itself advances, so a
+// captured CUDA graph can be replayed: a rank can only be one call ahead of a peer (it needs the
+// peer's data of the current call to finish), so a slot is never overwritten while it is being read.
+// A wait that runs out sets PARE_ERR_TIMEOUT in the header's status word and the call returns
+// whatever it has (the host reads the word with pare_peer_status).
 
 #include "common.cuh"
 
@@ -23,7 +26,6 @@ constexpr int kMaxRanks = 8;
 constexpr int kMaxCtas = 16;
 constexpr size_t kHeaderBytes = 4096;
 constexpr int kStatusWord = kMaxCtas;                        // ints into the header
-constexpr int kFlagBase = 64;                                // ints into the header
 constexpr uint32_t kPeerSpinLimit = 1u << 24;
 constexpr int kThreads = 256;
 
@@ -35,72 +37,65 @@ struct PeerParams {
   int rows, cols;
   int rank, world;
   size_t slot_bytes;
-  int vec_per_cta;   // 16-byte vectors of the flattened [rows x cols] tensor per CTA
+  int units_per_cta;   // 8-byte payload units (4 elements) of the flattened [rows x cols] tensor per CTA
 };
 
-__device__ __forceinline__ void st_release_sys(int* p, int v) { asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
 
-// cols % 8 == 0: a 16-byte vector never straddles a row
+// cols % 4 == 0: an 8-byte unit never straddles a row
 template <typename T>
 __global__ void __launch_bounds__(kThreads) peer_allreduce_kernel(const PeerParams p) {
   pdl_launch_dependents();
   pdl_wait();   // x is the previous kernel's output
   const int c = blockIdx.x;
   int* hdr = reinterpret_cast<int*>(p.buf[p.rank]);
-  const int e = hdr[c] + 1;
+  const uint32_t e = (uint32_t)hdr[c] + 1u;
   const int par = e & 1;
-  const int vec_per_row = p.cols >> 3;
-  const int v_lo = c * p.vec_per_cta, v_hi = min(v_lo + p.vec_per_cta, p.rows * vec_per_row);
+  const int units_per_row = p.cols >> 2;
+  const int u_lo = c * p.units_per_cta, u_hi = min(u_lo + p.units_per_cta, p.rows * units_per_row);
   const size_t slot_off = kHeaderBytes + ((size_t)par * p.world + p.rank) * p.slot_bytes;
 
-  // 1) my partial into slot `rank` of every rank's buffer (own buffer included)
+  // 1) my partial into slot `rank` of every rank's buffer (own buffer included), each 8 bytes with the epoch
   const T* x = reinterpret_cast<const T*>(p.x);
-  for (int v = v_lo + threadIdx.x; v < v_hi; v += kThreads) {
-    const int r = v / vec_per_row, cc = (v - r * vec_per_row) * 8;
-    const uint4 val = *reinterpret_cast<const uint4*>(x + (size_t)r * p.ldx + cc);
-    for (int q = 0; q < p.world; ++q) *reinterpret_cast<uint4*>(p.buf[q] + slot_off + (size_t)v * 16) = val;
+  for (int u = u_lo + threadIdx.x; u < u_hi; u += kThreads) {
+    const int r = u / units_per_row, cc = (u - r * units_per_row) * 4;
+    const uint2 val = *reinterpret_cast<const uint2*>(x + (size_t)r * p.ldx + cc);
+    const uint4 unit = make_uint4(val.x, e, val.y, e);
+    for (int q = 0; q < p.world; ++q) *reinterpret_cast<uint4*>(p.buf[q] + slot_off + (size_t)u * 16) = unit;
   }
-  __threadfence_system();
-  __syncthreads();
-  // 2) tell every rank that this CTA's share of my partial has landed, then wait for theirs
-  if (threadIdx.x < p.world) {
-    const int q = threadIdx.x;
-    st_release_sys(reinterpret_cast<int*>(p.buf[q]) + kFlagBase + (par * kMaxRanks + p.rank) * kMaxCtas + c, e);
-    const int* mine = hdr + kFlagBase + (par * kMaxRanks + q) * kMaxCtas + c;
-    uint32_t i = 0;
-    while (ld_acquire_sys(mine) != e) {
-      if (++i >= kPeerSpinLimit) {
-        atomicExch(hdr + kStatusWord, PARE_ERR_TIMEOUT);
-        break;
-      }
-    }
-  }
-  __syncthreads();
-  // 3) sum in rank order
+  // 2) the ranks' partials from my own buffer, in rank order, as they arrive
   T* y = reinterpret_cast<T*>(p.y);
   const unsigned char* data = p.buf[p.rank] + kHeaderBytes + (size_t)par * p.world * p.slot_bytes;
-  for (int v = v_lo + threadIdx.x; v < v_hi; v += kThreads) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  bool timed_out = false;
+  for (int u = u_lo + threadIdx.x; u < u_hi; u += kThreads) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int q = 0; q < p.world; ++q) {
-      const uint4 val = __ldcg(reinterpret_cast<const uint4*>(data + (size_t)q * p.slot_bytes + (size_t)v * 16));
+      const unsigned char* src = data + (size_t)q * p.slot_bytes + (size_t)u * 16;
+      uint4 v = ld_volatile_v4(src);
+      uint32_t i = 0;
+      while ((v.y != e || v.w != e) && !timed_out) {
+        if (++i >= kPeerSpinLimit) timed_out = true;
+        v = ld_volatile_v4(src);
+      }
+      const uint2 val = make_uint2(v.x, v.z);
       const T* ve = reinterpret_cast<const T*>(&val);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] += to_float<T>(ve[k]);
+      for (int k = 0; k < 4; ++k) acc[k] += to_float<T>(ve[k]);
     }
-    uint4 out;
+    uint2 out;
     T* oe = reinterpret_cast<T*>(&out);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) oe[k] = from_float<T>(acc[k]);
-    const int r = v / vec_per_row, cc = (v - r * vec_per_row) * 8;
-    *reinterpret_cast<uint4*>(y + (size_t)r * p.ldy + cc) = out;
+    for (int k = 0; k < 4; ++k) oe[k] = from_float<T>(acc[k]);
+    const int r = u / units_per_row, cc = (u - r * units_per_row) * 4;
+    *reinterpret_cast<uint2*>(y + (size_t)r * p.ldy + cc) = out;
   }
-  __syncthreads();
-  if (threadIdx.x == 0) hdr[c] = e;
+  if (timed_out) atomicExch(hdr + kStatusWord, PARE_ERR_TIMEOUT);
+  __syncthreads();   // every thread has read this CTA's epoch
+  if (threadIdx.x == 0) hdr[c] = (int)e;
 }
 
 }  // namespace
@@ -145,30 +140,33 @@ int pare_peer_status(const void* own_buffer, void* stream) {
   return v;
 }
 
-// y[r][:] = sum over ranks of x[r][:] for a [rows x cols] tensor (cols % 8 == 0, 16-byte aligned rows) that is
-// small enough for the exchange buffers: rows * cols * 2 <= (buffer_bytes - 4096) / (2 * world).  buffers: HOST
-// array of `world` device pointers, buffers[rank] this rank's own buffer, the others its peers' buffers as mapped
-// into this process.  Every rank must make the same sequence of calls.
+// y[r][:] = sum over ranks of x[r][:] for a [rows x cols] tensor (cols % 4 == 0, 8-byte aligned rows) that is
+// small enough for the exchange buffers: rows * cols * 4 <= (buffer_bytes - 4096) / (2 * world) (every 8 bytes of
+// data travel with 8 bytes of validity marks).  buffers: HOST array of `world` device pointers, buffers[rank] this
+// rank's own buffer, the others its peers' buffers as mapped into this process.  Every rank must make the same
+// sequence of calls.
 int pare_peer_allreduce(const void* x, int64_t ldx, void* y, int64_t ldy, int rows, int cols, int dtype, int rank, int world,
                         void* const* buffers, size_t buffer_bytes, void* stream) {
   using namespace pare;
   PARE_REQUIRE(x && y && buffers && rows > 0 && cols > 0 && ldx >= cols && ldy >= cols, PARE_ERR_SHAPE);
   PARE_REQUIRE(world >= 2 && world <= kMaxRanks && rank >= 0 && rank < world, PARE_ERR_SHAPE);
   PARE_REQUIRE(dtype == PARE_F16 || dtype == PARE_BF16, PARE_ERR_DTYPE);
-  PARE_REQUIRE(cols % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0 && aligned16(x) && aligned16(y), PARE_ERR_ALIGN);
+  PARE_REQUIRE(cols % 4 == 0 && ldx % 4 == 0 && ldy % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 7u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(y) & 7u) == 0,
+               PARE_ERR_ALIGN);
   PeerParams p{};
   for (int q = 0; q < world; ++q) {
     PARE_REQUIRE(buffers[q] != nullptr, PARE_ERR_SHAPE);
     p.buf[q] = reinterpret_cast<unsigned char*>(buffers[q]);
   }
+  PARE_REQUIRE(buffer_bytes > kHeaderBytes, PARE_ERR_WORKSPACE);
   p.slot_bytes = ((buffer_bytes - kHeaderBytes) / (2 * (size_t)world)) & ~(size_t)255;
-  const size_t bytes = (size_t)rows * cols * 2;
-  PARE_REQUIRE(buffer_bytes > kHeaderBytes && bytes <= p.slot_bytes, PARE_ERR_WORKSPACE);
+  const size_t units = (size_t)rows * cols / 4;
+  PARE_REQUIRE(units * 16 <= p.slot_bytes, PARE_ERR_WORKSPACE);
   p.x = x; p.y = y; p.ldx = ldx; p.ldy = ldy; p.rows = rows; p.cols = cols; p.rank = rank; p.world = world;
-  const int nvec = (int)(bytes / 16);
-  int ctas = (nvec + 2 * kThreads - 1) / (2 * kThreads);   // two vectors per thread
+  int ctas = (int)((units + 2 * kThreads - 1) / (2 * kThreads));   // two units per thread
   ctas = ctas < 1 ? 1 : (ctas > kMaxCtas ? kMaxCtas : ctas);
-  p.vec_per_cta = (nvec + ctas - 1) / ctas;
+  p.units_per_cta = (int)((units + ctas - 1) / ctas);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return dtype == PARE_F16 ? launch_pdl(peer_allreduce_kernel<__half>, dim3(ctas), dim3(kThreads), 0, s, p)
                            : launch_pdl(peer_allreduce_kernel<__nv_bfloat16>, dim3(ctas), dim3(kThreads), 0, s, p);

@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
   const int gid = lane >> 2, tig = lane & 3;
   const int steps_total = p.K >> 7;
   const int st0 = blockIdx.y * p.steps_per_split;
-  const int nst = min(p.steps_per_split, steps_total - st0);  // 128-column steps of this CTA (multiple of 4)
+  const int nst = min(p.steps_per_split, steps_total - st0);  // 128-column steps of this CTA (even)
   const int k0 = st0 << 7;
   const int row0 = blockIdx.x * kTileRows;
   const int spg = p.steps_per_group;
@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
   if (threadIdx.x == 0) p.counters[blockIdx.x] = 0;  // leave the workspace ready for the next call
 }
 
-// ---- any-shape fallback: one thread per output, used when K is not a multiple of 512 or the
+// ---- any-shape fallback: one thread per output, used when K is not a multiple of 256 or the
 // group size not a multiple of 128 (tiny layers); correctness path, not a performance path ----
 template <typename T>
 __global__ void w4a16_generic_kernel(const GemvParams p, const uint8_t* packed, int group_size) {
@@ -404,10 +404,10 @@ Plan make_plan(int M, int N, int K, int G) {
 
 Plan make_plan_rb(int M, int N, int K, int G, int rb_request) {
   Plan pl{};
-  pl.fast = (K % 512 == 0) && (G % 128 == 0);  // K ranges are cut in multiples of 512 columns
+  pl.fast = (K % 256 == 0) && (G % 128 == 0);  // K ranges are cut in multiples of 256 columns (an even number of steps)
   if (!pl.fast) return pl;
   const int MB = M <= 8 ? 1 : 2;
-  const int chunks = K / 512;
+  const int chunks = K / 256;
   // two 16-row blocks per CTA when that still leaves at least two CTAs per SM (big layers): half the
   // per-warp overhead per weight.  Small layers keep 16-row CTAs for parallelism.
   int rb = rb_request ? rb_request : (((N + 31) / 32 >= 2 * kSmCount && MB == 1) ? 2 : 1);
@@ -418,7 +418,7 @@ Plan make_plan_rb(int M, int N, int K, int G, int rb_request) {
   // very small layers only: cut K further until there is at least one CTA per SM (going through the
   // global split-K reduction costs more latency than it buys otherwise)
   while (!g_tune_kc && kc > 512 && (long long)row_tiles * ((K + kc - 1) / kc) < kSmCount) kc >>= 1;
-  int cps = kc / 512;                     // 512-column chunks per CTA
+  int cps = kc / 256;                     // 256-column chunks per CTA
   if (cps < 1) cps = 1;
   if (cps > chunks) cps = chunks;
   int splits = (chunks + cps - 1) / cps;
@@ -428,7 +428,7 @@ Plan make_plan_rb(int M, int N, int K, int G, int rb_request) {
     cps = (chunks + 63) / 64;
   }
   splits = (chunks + cps - 1) / cps;
-  const int nst = cps * 4;
+  const int nst = cps * 2;
   const int max_steps = kMaxStepsPerWarp / rb;
   // enough CTAs to fill the machine three times over: fewer, longer warps (less per-warp overhead);
   // otherwise more warps per CTA to shorten each CTA's critical path
@@ -516,7 +516,7 @@ size_t prep_bytes(int M, int K) {  // prepared activations + step table, each ro
 size_t gemv_workspace_bytes(int M, int N, int K, int G) {
   const int m = M < 16 ? M : 16;
   size_t splits = 1;
-  if (K % 512 == 0 && G % 128 == 0) splits = (size_t)(K / 512);  // upper bound on any plan
+  if (K % 256 == 0 && G % 128 == 0) splits = (size_t)(K / 256);  // upper bound on any plan
   if (splits > 64) splits = 64;
   // split-K partial sums of either schedule (the persistent one adds at most one 32-row block per SM)
   return kCounterBytes + prep_bytes(m, K) + (splits * (size_t)m * N + (size_t)kSmCount * 32 * m) * sizeof(float);

@@ -509,7 +509,7 @@ StreamPlan make_stream_plan(int M, int N, int K) {
   pl.rows = M <= 8 ? 32 : 16;
   pl.n_tiles = N / pl.rows;
   pl.n_slices = (steps + slice_steps - 1) / slice_steps;
-  pl.sps = ((steps + pl.n_slices - 1) / pl.n_slices + 1) & ~1;   // even: K % 512 == 0 keeps every slice whole
+  pl.sps = ((steps + pl.n_slices - 1) / pl.n_slices + 1) & ~1;   // even: K % 256 == 0 keeps every slice whole
   pl.n_slices = (steps + pl.sps - 1) / pl.sps;
   pl.gs = kGrid / pl.n_slices;
   if (pl.gs < 1) pl.gs = 1;
@@ -550,7 +550,7 @@ void gemv_persist_set_depth(int d) { g_persist_depth = d; }
 // Layers the persistent schedule serves: 128-column groups, whole 32-row tiles, activations that fit in
 // shared memory next to the weight ring, and enough items to occupy the machine.
 bool gemv_persist_supported(int M, int N, int K, int G) {
-  if (G != 128 || M > 16 || (K % 512) != 0 || (N % kMaxRows) != 0 || N <= 0) return false;
+  if (G != 128 || M > 16 || (K % 256) != 0 || (N % kMaxRows) != 0 || N <= 0) return false;
   const StreamPlan pl = make_stream_plan(M, N, K);
   if (pl.n_slices > kGrid) return false;
   if ((long long)(N / kMaxRows) * pl.n_slices < g_persist_min_items) return false;

@@ -128,7 +128,7 @@ class DecodeStack(nn.Module):
 
     def _all_reduce(self, t: Tensor) -> Tensor:
         if self.tp_world > 1:
-            if self.peer_reduce is not None and t.numel() <= self.peer_reduce.max_elements() and t.shape[1] % 8 == 0:
+            if self.peer_reduce is not None and t.numel() <= self.peer_reduce.max_elements() and t.shape[1] % 4 == 0:
                 return self.peer_reduce(t)
             torch.distributed.all_reduce(t, group=self.group)
         return t

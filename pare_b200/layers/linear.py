@@ -176,7 +176,7 @@ class QuantizedLinear(nn.Module):
         """True if :meth:`forward_prepared` can serve ``rows`` activation rows of this layer."""
         return (self.use_kernel and self.config.dtype == QuantDtype.INT4 and not self.quantize_inputs
                 and self.g_idx is None and self.input_scale is None and rows <= 16
-                and self.in_features % 512 == 0 and self._kernel_group_size() % 128 == 0)
+                and self.in_features % 256 == 0 and self._kernel_group_size() % 128 == 0)
 
     def forward_prepared(self, prep) -> Tensor:
         """Forward for activations handed over as :class:`PreparedActivations` (decode, rows <= 16):

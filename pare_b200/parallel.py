@@ -93,8 +93,9 @@ class PeerAllReduce:
     """Sum of a small ``[rows, cols]`` fp16/bf16 tensor over the ranks of ``group`` through NVLink peer memory.
 
     One kernel launch per call (``pare_peer_allreduce``): every rank stores its partial into every peer's
-    exchange buffer, waits for the peers' flags and adds the partials in rank order (fp32, deterministic,
-    identical on all ranks).  The exchange buffers are allocated once here and shared by CUDA IPC handles
+    exchange buffer (each 8 bytes with their own validity marks, so there is no fence and no separate flag) and
+    adds the partials from its own buffer in rank order as they arrive (fp32, deterministic, identical on all
+    ranks).  The exchange buffers are allocated once here and shared by CUDA IPC handles
     exchanged over ``torch.distributed``; every rank must construct this object and then make the same
     sequence of calls.  Capturable in a CUDA graph.  2 <= world <= 8, one process per GPU on one node.
     """
@@ -112,7 +113,8 @@ class PeerAllReduce:
         self.rank = dist.get_rank(group)
         if not 2 <= self.world <= 8:
             raise ValueError("PeerAllReduce serves 2..8 ranks")
-        self.buffer_bytes = 4096 + 2 * self.world * ((max_bytes + 255) // 256 * 256)
+        # every 8 bytes of data travel with 8 bytes of validity marks
+        self.buffer_bytes = 4096 + 2 * self.world * ((2 * max_bytes + 255) // 256 * 256)
         L = _lib.lib()
         own = C.c_void_p()
         handle = C.create_string_buffer(64)
@@ -134,7 +136,7 @@ class PeerAllReduce:
         dist.barrier(group=group)   # nobody stores into a buffer that is not mapped everywhere yet
 
     def max_elements(self) -> int:
-        return ((self.buffer_bytes - 4096) // (2 * self.world) // 256 * 256) // 2
+        return ((self.buffer_bytes - 4096) // (2 * self.world) // 256 * 256) // 4
 
     def __call__(self, x, out=None):
         assert x.is_cuda and x.dim() == 2 and x.stride(1) == 1

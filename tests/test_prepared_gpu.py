@@ -43,7 +43,7 @@ def _split(prep):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (4, 28672, 4096), (16, 512, 1024), (3, 4096, 14336), (1, 9472, 3584)])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (4, 28672, 4096), (16, 512, 1024), (3, 4096, 14336), (1, 9472, 3584), (2, 4096, 1792)])
 def test_prepared_forward_is_the_plain_forward(m, n, k, dtype, cuda_lib):
     packed, scale, zero = _layer(n, k, seed=n + k)
     x = torch.randn(m, k, device="cuda").to(dtype)
@@ -57,7 +57,7 @@ def test_prepared_rejects_what_it_cannot_do(cuda_lib):
         PreparedActivations(17, 1024, torch.float16, "cuda")
     with pytest.raises(ValueError):
         PreparedActivations(1, 1000, torch.float16, "cuda")
-    packed, scale, zero = _layer(256, 640)          # K % 512 != 0: only the any-shape kernel serves it
+    packed, scale, zero = _layer(256, 640)          # K % 256 != 0: only the any-shape kernel serves it
     x = torch.randn(1, 640, device="cuda").half()
     with pytest.raises(_lib.KernelLibraryError):
         w4a16_forward_prepared(prepare(x), packed, scale, zero, 128)
@@ -206,7 +206,7 @@ def test_linear_normalises_its_input_itself(m, n, k, dtype, cuda_lib):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("m,n,k", [(1, 1024, 2048), (3, 4096, 14336), (1, 10240, 1024), (6, 512, 1024)])
+@pytest.mark.parametrize("m,n,k", [(1, 1024, 2048), (3, 4096, 14336), (1, 10240, 1024), (6, 512, 1024), (2, 4096, 1792)])
 def test_linear_applies_the_swiglu_gate_itself(m, n, k, dtype, cuda_lib):
     from pare_b200.kernels.matmul_int4 import w4a16_forward_produced
     packed, scale, zero = _layer(n, k, seed=n + k + m)

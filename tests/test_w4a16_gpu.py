@@ -88,7 +88,8 @@ def test_matches_oracle_small(m, dtype, cuda_lib):
     check(y, oracle_y(ql, x), dtype)
 
 
-@pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336), (1000, 512), (48, 128)])
+@pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336), (1000, 512), (48, 128),
+                                   (4096, 1792), (768, 4096), (9472, 768)])   # the last three: K % 512 != 0 / TP-8 shards
 @pytest.mark.parametrize("m", [1, 4, 16])
 def test_matches_oracle_layer_shapes(shape, m, cuda_lib):
     """8B-shaped projections (out, in) plus ragged N; exercises split-K and the row-tile edge."""
