@@ -157,6 +157,44 @@ def test_quantize_rtn_and_save_load_roundtrip(tmp_path):
         pare_b200.quantize(nn.Linear(4, 4), QuantConfig(scheme="gptq"))
 
 
+def test_load_quantized_tensor_parallel_slices(tmp_path):
+    """Loading with a tensor-parallel plan reads each rank's slice from the file; the slices are those of
+    ``shard_linear`` and together reproduce the unsharded model (column shards concatenate, row shards add)."""
+    from pare_b200.parallel import shard_linear
+
+    class MLP(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up_proj = nn.Linear(256, 512, bias=True)
+            self.down_proj = nn.Linear(512, 256, bias=True)
+
+        def forward(self, x):
+            return self.down_proj(torch.relu(self.up_proj(x)))
+
+    torch.manual_seed(3)
+    model = MLP()
+    pare_b200.quantize(model, QuantConfig(bits=4, scheme="rtn", group_size=128))
+    x = torch.randn(3, 256)
+    y = model(x)
+    pare_b200.save_quantized(model, tmp_path / "ckpt")
+    plan = {"up_proj": "column", "down_proj": "row"}
+    partial = []
+    for rank in range(2):
+        shard = MLP()
+        pare_b200.load_quantized(shard, tmp_path / "ckpt", tp_plan=plan, tp_rank=rank, tp_world=2)
+        assert shard.up_proj.out_features == 256 and shard.down_proj.in_features == 256
+        for name, mode in plan.items():
+            want = shard_linear(getattr(model, name), mode, rank, 2)
+            got = getattr(shard, name)
+            assert torch.equal(got.packed_weight, want.packed_weight) and torch.equal(got.scale, want.scale)
+            assert torch.equal(got.zero, want.zero)
+            assert (got.bias is None) == (want.bias is None) and (got.bias is None or torch.equal(got.bias, want.bias))
+        partial.append(shard(x))     # up: this rank's columns -> relu -> down: this rank's partial sum
+    assert torch.allclose(partial[0] + partial[1], y, atol=1e-5, rtol=1e-5)
+    with pytest.raises(ValueError):
+        pare_b200.load_quantized(MLP(), tmp_path / "ckpt", tp_plan={"up_proj": "diagonal"}, tp_rank=0, tp_world=2)
+
+
 # ---- cache schedule ----------------------------------------------------------------------------------
 
 def test_plan_update_matches_oracle_state_machine():
