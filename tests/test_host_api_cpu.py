@@ -195,6 +195,34 @@ def test_load_quantized_tensor_parallel_slices(tmp_path):
         pare_b200.load_quantized(MLP(), tmp_path / "ckpt", tp_plan={"up_proj": "diagonal"}, tp_rank=0, tp_world=2)
 
 
+def test_awq_gemm_layout_roundtrip():
+    """The AutoAWQ GEMM layout: nibble i of an int32 holds output column 8w + (0,2,4,6,1,3,5,7)[i]; export then
+    import gives the same codes, zero points and (fp16-rounded) scales, hence the same dequantized weights."""
+    from pare_b200.model.awq_format import ORDER, _pack_columns, _unpack_columns, from_awq_gemm, to_awq_gemm
+
+    codes = torch.arange(16, dtype=torch.uint8).repeat(2)[:16].reshape(1, 16)       # columns 0..15 hold codes 0..15
+    word = _pack_columns(codes)
+    assert word.dtype == torch.int32 and word.shape == (1, 2)
+    w0 = int(word[0, 0]) & 0xFFFFFFFF
+    assert [(w0 >> (4 * i)) & 0xF for i in range(8)] == list(ORDER)                  # nibble i <- column ORDER[i]
+    assert torch.equal(_unpack_columns(word), codes)
+    hi = _pack_columns(torch.full((1, 8), 15, dtype=torch.uint8))                    # all nibbles set: wraps to -1
+    assert int(hi[0, 0]) == -1 and torch.equal(_unpack_columns(hi), torch.full((1, 8), 15, dtype=torch.uint8))
+
+    torch.manual_seed(5)
+    lin = nn.Linear(256, 64, bias=True)
+    ql = QuantizedLinear.from_linear(lin, QuantConfig(bits=4, scheme="rtn", group_size=128))
+    t = to_awq_gemm(ql)
+    assert t["qweight"].shape == (256, 8) and t["qzeros"].shape == (2, 8) and t["scales"].shape == (2, 64)
+    back = from_awq_gemm(t["qweight"], t["qzeros"], t["scales"], t["bias"], group_size=128)
+    assert torch.equal(back.packed_weight, ql.packed_weight) and torch.equal(back.zero, ql.zero)
+    assert torch.equal(back.scale, ql.scale.half().float())
+    assert torch.allclose(back.dequantize(), ql.dequantize(), rtol=2 ** -10, atol=0)   # scales went through fp16
+    assert back.bias.dtype == torch.float16 and torch.equal(back.bias.float(), lin.bias.detach().half().float())
+    with pytest.raises(ValueError):
+        to_awq_gemm(QuantizedLinear.from_linear(nn.Linear(256, 64), QuantConfig(bits=4, scheme="rtn", granularity="per_channel")))
+
+
 # ---- cache schedule ----------------------------------------------------------------------------------
 
 def test_plan_update_matches_oracle_state_machine():
