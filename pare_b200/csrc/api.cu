@@ -19,7 +19,7 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
 int gemv_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_perm, const float* input_scale, int M, int K,
                  void* prepared, cudaStream_t stream);
 void gemv_set_tuning(int rb, int splits, int pf);
-bool gemv_persist_supported(int M, int N, int K, int G);
+bool gemv_persist_supported(int M, int N, int K, int G, bool producer = false);
 bool gemm_supported(int M, int K, int G, const float* scale, const float* zero);
 size_t gemm_workspace_bytes(int M, int N, int K);
 int gemm_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale, const float* zero,

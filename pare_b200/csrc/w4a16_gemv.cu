@@ -501,7 +501,7 @@ int launch_generic(const GemvParams& p, const uint8_t* packed, int G, cudaStream
 
 }  // namespace
 
-bool gemv_persist_supported(int M, int N, int K, int G);
+bool gemv_persist_supported(int M, int N, int K, int G, bool producer = false);
 size_t gemv_persist_partial_floats(int M, int N, int K);
 void gemv_persist_set_min_items(int n);
 void gemv_persist_set_depth(int d);
@@ -563,7 +563,7 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   PARE_REQUIRE((pl.steps_per_split + pl.warps - 1) / pl.warps <= kMaxStepsPerWarp / pl.rb, PARE_ERR_UNSUPPORTED);
   p.splits = pl.splits;
   p.steps_per_split = pl.steps_per_split;
-  const bool persist = g_tune_persist >= 0 && gemv_persist_supported(M, N, K, G);
+  const bool persist = g_tune_persist >= 0 && gemv_persist_supported(M, N, K, G, prod != nullptr);
   const size_t need = kCounterBytes + prep_bytes(M, K) +
                       (persist ? gemv_persist_partial_floats(M, N, K) * sizeof(float)
                                : (pl.splits > 1 ? (size_t)pl.splits * M * N * sizeof(float) : 0));

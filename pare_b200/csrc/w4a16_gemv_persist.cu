@@ -549,15 +549,16 @@ void gemv_persist_set_depth(int d) { g_persist_depth = d; }
 
 // Layers the persistent schedule serves: 128-column groups, whole 32-row tiles, activations that fit in
 // shared memory next to the weight ring, and enough items to occupy the machine.
-bool gemv_persist_supported(int M, int N, int K, int G) {
+bool gemv_persist_supported(int M, int N, int K, int G, bool producer) {
   if (G != 128 || M > 16 || (K % 256) != 0 || (N % kMaxRows) != 0 || N <= 0) return false;
   const StreamPlan pl = make_stream_plan(M, N, K);
   if (pl.n_slices > kGrid) return false;
   if ((long long)(N / kMaxRows) * pl.n_slices < g_persist_min_items) return false;
   // Less than two whole items per CTA is all ramp (and cross-CTA reduction where pieces are involved): such
   // layers are faster as independent tiles at M <= 4 (measured: 6144 x 4096 takes 8.1 us here, 6.4 us
-  // there; 4096 x 4096 5.1 against 4.7 us).
-  if (M <= 4 && pl.n_slices == 1 && pl.q < 2) return false;
+  // there; 4096 x 4096 5.1 against 4.7 us) -- unless the kernel computes its own activations: 148 resident
+  // CTAs normalise the row once each instead of 384 tiles doing it (the whole decode step gains 8 %).
+  if (M <= 4 && pl.n_slices == 1 && pl.q < 2 && !(producer && pl.q == 1)) return false;
   if ((size_t)pl.n_tiles >= kStatusIndex) return false;
   return persist_smem(M, pl.sps, 2, pl.rows, pl.red_bufs) <= kPersistSmemCap;
 }
