@@ -85,9 +85,10 @@ int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx,
                        void* workspace, size_t workspace_bytes,
                        void* stream);
 
-/* Tuning override for experiments (host state, process-wide, not thread-safe):
- * (reserved), columns per CTA (multiple of 512), warps per CTA (4 or 8); 0 = choose automatically. */
-void pare_w4a16_set_tuning(int reserved, int columns_per_cta, int warps_per_cta);
+/* Tuning override for experiments (host state, process-wide, not thread-safe): schedule (-1 = tile kernel only,
+ * 1 / 2 = 16-row blocks per tile CTA, 0 = automatic), columns per tile CTA (multiple of 256) and warps per tile
+ * CTA (4 or 8); 0 = choose automatically. */
+void pare_w4a16_set_tuning(int schedule, int columns_per_cta, int warps_per_cta);
 
 /* ------------------------------------------------------------------------
  * Prepared activations: the M <= 16 path of pare_w4a16_forward in two halves, so that the

@@ -6,8 +6,11 @@
 // which is the reference formula (q - zero) * scale (pare/core/functional.py:78-91) with
 // the zero-point and the scale hoisted out of the inner loop.
 //
-// The kernel is HBM-bound; every weight byte is read exactly once.  Design:
-//   * A CTA owns 16 output rows x one K range of up to 4096 columns.  Lanes 0..15 of warp 0
+// The path is HBM-bound by design; every weight byte is read exactly once.  This file holds the tile kernel
+// (small layers, and the fallback of every fast-path shape), the activation-preparation kernel, the
+// any-shape fallback and the host-side routing; large layers run the persistent schedule of
+// w4a16_gemv_persist.cu.  Tile kernel:
+//   * A CTA owns 16 (or 32) output rows x one K range of up to 4096 columns.  Lanes 0..15 of warp 0
 //     issue one bulk async copy (cp.async.bulk, the non-tensor TMA path) per row: a row's
 //     whole K range is one contiguous request of up to 2 KB, which is what HBM and the copy
 //     engine like; all 16 complete on one mbarrier.  Every CTA has its whole tile in flight
@@ -15,14 +18,14 @@
 //   * The shared-memory row pitch is (bytes + 64), so the 16-byte reads of a quarter-warp
 //     (two adjacent rows x four chunks) fall in distinct banks without any swizzle.
 //   * The WARPS warps of the CTA split the K range; each takes all 16 rows.  Per 128-column
-//     step a lane reads 2 x 16 bytes of codes, turns them into exact integer-valued fp16/bf16
-//     by OR-ing into the mantissa of a power of two, and multiplies them with the activations
+//     step a lane reads 2 x 16 bytes of codes, turns them into exact integer-valued fp16
+//     by OR-ing into the mantissa of 1024.0, and multiplies them with the (fp16, per-step scaled) activations
 //     on the warp-level MMA unit (fp32 accumulation; the 8 MMA columns carry up to 8
 //     activation rows at the cost of one).  Scale and zero of the warp's groups are
 //     prefetched into registers before anything else.
-//   * Activations are put in operand order ONCE per call by a small preparation kernel, together
-//     with the per-step sums the hoisted zero-point needs (warp-shuffle reductions); the CTAs
-//     only copy their slice into shared memory.
+//   * Activations arrive prepared (prep.cuh: operand order + per-step table), written once per call by
+//     w4a16_prep_kernel or by the kernel that computed them; the CTAs only copy their slice into shared
+//     memory -- or compute it themselves from the residual stream / the fused gate|up tensor (stage.cuh).
 //   * The warps' partial sums meet in shared memory.  Only when K exceeds one CTA's range do
 //     partial sums go through the global workspace: the CTA that arrives last at a
 //     per-row-tile counter adds them in split order (deterministic) and resets the counter.
@@ -503,8 +506,6 @@ int launch_generic(const GemvParams& p, const uint8_t* packed, int G, cudaStream
 
 bool gemv_persist_supported(int M, int N, int K, int G, bool producer = false);
 size_t gemv_persist_partial_floats(int M, int N, int K);
-void gemv_persist_set_min_items(int n);
-void gemv_persist_set_depth(int d);
 int gemv_persist_launch(const gemv::GemvParams& p, int x_dtype, cudaStream_t stream);
 
 size_t prep_bytes(int M, int K) {  // prepared activations + step table, each rounded to 256 bytes
@@ -635,14 +636,11 @@ int gemv_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_per
   return e == cudaSuccess ? PARE_OK : PARE_ERR_CUDA;
 }
 
-// Tuning override for experiments: columns per CTA (multiple of 512) and warps per CTA (4 or 8).
-void gemv_set_tuning(int rb, int kc, int warps) {
-  g_tune_persist = rb < 0 ? -1 : 0;
-  gemv_persist_set_min_items(rb >= 100 ? rb : 96);   // experiments: rb >= 100 sets the persistent schedule's threshold,
-  gemv_persist_set_depth(rb >= 100 ? warps : 0);      // and `warps` its ring depth
-  if (rb >= 100) { rb = 0; warps = 0; kc = 0; }
-  if (rb < 0) rb = 0;
-  g_tune_rb = rb;
+// Tuning override for experiments: schedule (-1 = tile kernel only, 1 / 2 = 16-row blocks per tile CTA, 0 = automatic),
+// columns per tile CTA (multiple of 256) and warps per tile CTA (4 or 8); 0 = automatic.
+void gemv_set_tuning(int schedule, int kc, int warps) {
+  g_tune_persist = schedule < 0 ? -1 : 0;
+  g_tune_rb = schedule == 1 || schedule == 2 ? schedule : 0;
   g_tune_kc = kc;
   g_tune_warps = warps;
 }

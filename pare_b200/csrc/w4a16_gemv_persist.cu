@@ -54,7 +54,6 @@ struct StreamPlan {
   int units;      // contributions per slice: n_full + pieces
   int depth;      // ring slots
   int compact;    // M <= 2: the exchange area keeps only the two activation columns in use
-  int flags;      // experiments: 1 = sleeping waits for producer / epilogue
 };
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -72,8 +71,7 @@ __device__ __forceinline__ bool wait_or_die(uint32_t bar, uint32_t parity, int* 
 
 // Wait of a warp that is not on the critical path (producer, epilogue): sleeps between polls so that
 // its polling does not compete with the consumers for issue slots and the shared-memory pipe.
-__device__ __forceinline__ bool wait_relaxed(uint32_t bar, uint32_t parity, int* status, bool& dead, bool relax) {
-  if (!relax) return wait_or_die(bar, parity, status, dead);
+__device__ __forceinline__ bool wait_relaxed(uint32_t bar, uint32_t parity, int* status, bool& dead) {
   if (dead) return false;
 #pragma unroll 1
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
@@ -164,7 +162,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
       const Item it = item_of(pl, bl, i);
       const int lo = min(it.w_lo * SPW, sps_this), hi = min(it.w_hi * SPW, sps_this);
       const int bytes = (hi - lo) * 64;
-      wait_relaxed(empty0 + slot * 8, ph ^ 1, status, dead, pl.flags & 1);
+      wait_relaxed(empty0 + slot * 8, ph ^ 1, status, dead);
       if (lane == 0) mbar_expect_tx(full0 + slot * 8, R * bytes);
       __syncwarp();
       if (bytes > 0 && lane < R) {
@@ -191,7 +189,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
     int rph = 0;
     for (int i = par; i < n_items; i += nred, rph ^= 1) {
       const Item it = item_of(pl, bl, i);
-      wait_relaxed(rfull0 + par * 8, rph, status, dead, pl.flags & 1);
+      wait_relaxed(rfull0 + par * 8, rph, status, dead);
       const uint32_t red_base = red_u32 + par * red_buf;
       const int w_hi = min(it.w_hi, n_active);
       // full layout: lane (gid, tig) holds rows gid, gid+8 x activation rows 2 tig, 2 tig + 1 of row block rb
@@ -495,8 +493,6 @@ size_t persist_smem(int M, int sps, int depth, int rows, int red_bufs) {
          (2 * kMaxDepth + 4) * 8 + 128;
 }
 
-int g_persist_depth = 0;   // 0 = as deep as fits
-int g_persist_flags = 1;
 
 // Tile height and exchange buffers by the number of activation rows: 32-row tiles while one block of
 // eight activation rows is enough (two exchange buffers if they fit, else one), 16-row tiles for
@@ -525,11 +521,9 @@ StreamPlan make_stream_plan(int M, int N, int K) {
   }
   pl.units = pl.n_full + pl.pieces;
   pl.compact = M <= 2 ? 1 : 0;
-  pl.flags = g_persist_flags;
   pl.red_bufs = persist_smem(M, pl.sps, 2, pl.rows, 2) <= kPersistSmemCap ? 2 : 1;
   pl.depth = 2;
-  const int want = g_persist_depth ? g_persist_depth : kMaxDepth;
-  while (pl.depth < want && pl.depth < pl.q + (pl.pieces ? 1 : 0) &&
+  while (pl.depth < kMaxDepth && pl.depth < pl.q + (pl.pieces ? 1 : 0) &&
          persist_smem(M, pl.sps, pl.depth + 1, pl.rows, pl.red_bufs) <= kPersistSmemCap)
     ++pl.depth;
   return pl;
@@ -542,10 +536,7 @@ struct TypeTag {
 
 }  // namespace
 
-int g_persist_min_items = 96;
-
-void gemv_persist_set_min_items(int n) { g_persist_min_items = n >= 100 ? 96 : n; g_persist_flags = n >= 100 ? (n - 100) & 1 : 1; }
-void gemv_persist_set_depth(int d) { g_persist_depth = d; }
+constexpr int kPersistMinItems = 96;   // fewer items than this cannot occupy the machine: tile kernel
 
 // Layers the persistent schedule serves: 128-column groups, whole 32-row tiles, activations that fit in
 // shared memory next to the weight ring, and enough items to occupy the machine.
@@ -553,7 +544,7 @@ bool gemv_persist_supported(int M, int N, int K, int G, bool producer) {
   if (G != 128 || M > 16 || (K % 256) != 0 || (N % kMaxRows) != 0 || N <= 0) return false;
   const StreamPlan pl = make_stream_plan(M, N, K);
   if (pl.n_slices > kGrid) return false;
-  if ((long long)(N / kMaxRows) * pl.n_slices < g_persist_min_items) return false;
+  if ((long long)(N / kMaxRows) * pl.n_slices < kPersistMinItems) return false;
   // Less than two whole items per CTA is all ramp (and cross-CTA reduction where pieces are involved): such
   // layers are faster as independent tiles at M <= 4 (measured: 6144 x 4096 takes 8.1 us here, 6.4 us
   // there; 4096 x 4096 5.1 against 4.7 us) -- unless the kernel computes its own activations: 148 resident
