@@ -170,7 +170,7 @@ class ClockSampler:
         self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(index)],
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(index)],
                 stdout=self.tmp, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -364,7 +364,7 @@ def run_ours(args) -> None:
         raise SystemExit("bench.py needs a CUDA device (there is no CPU implementation of the product path)")
     _lib.lib()  # fail loudly if the CUDA library is missing
     world, rank, local = dist_setup(args.gpus)
-    steps = args.steps or 30
+    steps = args.steps or 200   # ~0.4 s timed: enough for several clock samples
     warmup = args.warmup if args.warmup is not None else 5
     peak, peak_kind = measured_peak()
     dtype = torch.bfloat16
