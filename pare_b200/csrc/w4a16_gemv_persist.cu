@@ -36,6 +36,7 @@ constexpr int kMaxDepth = 4;           // ring slots (2..4, as many as fit)
 constexpr int kMaxRows = 32;           // rows of a tile: 32, or 16 when two blocks of activation rows are in play
 constexpr int kCW = 16;                // consumer warps
 constexpr int kEpi = 2;                // epilogue warps
+constexpr int kMaxRed = 4;             // exchange buffers at most
 constexpr int kThreads = (kCW + 1 + kEpi) * 32;   // consumers + producer + epilogue warps
 constexpr int kGrid = 148;
 
@@ -45,7 +46,7 @@ struct StreamPlan {
   int sps;        // 128-column steps per slice (a multiple of spw, <= 16 * spw)
   int spw;        // steps per consumer warp and slice
   int rows;       // rows per tile (16 or 32)
-  int red_bufs;   // exchange buffers (2, or 1 when shared memory is short)
+  int red_bufs;   // exchange buffers (1, 2 or 4; an even count is shared by two epilogue warps)
   int gs;         // CTAs per slice
   int q;          // whole items per CTA
   int n_full;     // q * gs: items of a slice handed out whole
@@ -135,7 +136,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
   uint32_t* zero_blk = reinterpret_cast<uint32_t*>(red + nred * red_buf);            // 256 zero bytes
   uint64_t* bars = reinterpret_cast<uint64_t*>(zero_blk + 64);                    // full[4] empty[4] red_full[2] red_empty[2]
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kMaxDepth);
-  const uint32_t rfull0 = smem_u32(bars + 2 * kMaxDepth), rempty0 = smem_u32(bars + 2 * kMaxDepth + 2);
+  const uint32_t rfull0 = smem_u32(bars + 2 * kMaxDepth), rempty0 = smem_u32(bars + 2 * kMaxDepth + kMaxRed);
   const uint32_t ring_u32 = smem_u32(ring), xs_u32 = smem_u32(xs), tab_u32 = smem_u32(tab), red_u32 = smem_u32(red);
   int* status = p.counters + kStatusIndex;
   bool dead = false;
@@ -145,7 +146,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
       mbar_init(full0 + i * 8, 1);
       mbar_init(empty0 + i * 8, kCW);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kMaxRed; ++i) {
       mbar_init(rfull0 + i * 8, kCW);
       mbar_init(rempty0 + i * 8, 1);
     }
@@ -183,12 +184,14 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
     T* yg = reinterpret_cast<T*>(p.y);
     const T* bias = reinterpret_cast<const T*>(p.bias);
     const int n_active = sps_this / SPW;   // consumer warps with a share of this slice
-    // one epilogue warp per exchange buffer, so that each sees every phase of its buffer's barriers
-    if (warp - kCW - 1 >= nred) return;
-    const int par = warp - kCW - 1;
-    int rph = 0;
-    for (int i = par; i < n_items; i += nred, rph ^= 1) {
+    // the epilogue warps take the items in turn; their count divides the buffer count, so a buffer is always
+    // served by the same warp, which therefore sees every phase of its barriers
+    const int n_epi = nred >= 2 ? 2 : 1;
+    const int ew = warp - kCW - 1;
+    if (ew >= n_epi) return;
+    for (int i = ew; i < n_items; i += n_epi) {
       const Item it = item_of(pl, bl, i);
+      const int par = i % nred, rph = (i / nred) & 1;
       wait_relaxed(rfull0 + par * 8, rph, status, dead);
       const uint32_t red_base = red_u32 + par * red_buf;
       const int w_hi = min(it.w_hi, n_active);
@@ -490,7 +493,7 @@ size_t persist_smem(int M, int sps, int depth, int rows, int red_bufs) {
   const int mb = M <= 8 ? 1 : 2;
   const size_t red = (size_t)red_bufs * kCW * (rows / 16) * mb * (M <= 2 ? 8 : 32) * 16;
   return (size_t)depth * rows * (sps * 64 + 64) + (size_t)M * (sps * 256 + 64) + (size_t)sps * ((M + 1) & ~1) * sizeof(float4) + red + 256 +
-         (2 * kMaxDepth + 4) * 8 + 128;
+         (2 * kMaxDepth + 2 * kMaxRed) * 8 + 128;
 }
 
 
@@ -521,6 +524,7 @@ StreamPlan make_stream_plan(int M, int N, int K) {
   }
   pl.units = pl.n_full + pl.pieces;
   pl.compact = M <= 2 ? 1 : 0;
+  // two exchange buffers if they fit (four were measured: no gain, the consumer warps do not wait on them)
   pl.red_bufs = persist_smem(M, pl.sps, 2, pl.rows, 2) <= kPersistSmemCap ? 2 : 1;
   pl.depth = 2;
   while (pl.depth < kMaxDepth && pl.depth < pl.q + (pl.pieces ? 1 : 0) &&
