@@ -109,7 +109,10 @@ int pare_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[64]) 
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
   void* p = nullptr;
   if (cudaMalloc(&p, bytes) != cudaSuccess) return PARE_ERR_CUDA;
-  if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) return PARE_ERR_CUDA;
+  if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+    cudaFree(p);
+    return PARE_ERR_CUDA;
+  }
   cudaIpcMemHandle_t h;
   if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
     cudaFree(p);
