@@ -181,6 +181,12 @@ int pare_kivi_dequant(const uint8_t* k_codes, const float* k_scale, const float*
  *                 of 8, 16-byte aligned): it is attended to as window position n_res-1 AND stored
  *                 there by this call (the append of pare/kv_cache.py:229-231 for one token), so
  *                 the caller copies nothing; positions 0..n_res-2 must already be in the window
+ *   rope          NULL, or D floats (16-byte aligned) cos[0..D/2) then sin[0..D/2) of the newest token's
+ *                 position: q and new_k get the rotary embedding (pairs i, i + D/2:
+ *                 x'[i] = x[i] cos[i] - x[i+D/2] sin[i], x'[i+D/2] = x[i+D/2] cos[i] + x[i] sin[i], rounded to
+ *                 the dtype) before they are used, and new_k is stored rotated -- the step a model
+ *                 takes between its q|k|v projection and the cache (not part of the reference, whose
+ *                 callers hand update() keys that are already rotated)
  *   out           may be NULL when prepared_out is given
  *   prepared_out  NULL, or a pare_w4a16_prepared_bytes(B, Hq*D) buffer that receives the result as
  *                 prepared activations of the next W4A16 linear (B <= 16)
@@ -195,6 +201,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
                           void* res_k, void* res_v,
                           int64_t res_stride_b, int64_t res_stride_h, int64_t res_stride_t, int n_res,
                           const void* new_k, const void* new_v, int64_t new_stride_b, int64_t new_stride_h,
+                          const float* rope,
                           void* out, int64_t out_stride_b, int64_t out_stride_h, void* prepared_out,
                           float softmax_scale,
                           int B, int Hq, int H, int D, int bits, int group, int cap,

@@ -116,3 +116,25 @@ def decode_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float |
     p = np.exp(s)
     p = p / p.sum(axis=-1, keepdims=True)
     return np.einsum("bhqt,bhtd->bhqd", p, v).astype(_F)
+
+
+def rope_rows(positions, head_dim: int, theta: float = 10000.0) -> np.ndarray:
+    """``[len(positions), head_dim]`` fp32: ``cos(p f_i)`` for ``i < head_dim/2`` then ``sin(p f_i)``,
+    ``f_i = theta^(-2i/head_dim)``; angles in float64, table in float32.  Rotary position embedding as published
+    (Su et al., RoFormer) in the half-split pairing Llama-family models use; not part of the reference, whose
+    callers hand ``update()`` keys that are already rotated (pare/kv_cache.py:205-231)."""
+    half = head_dim // 2
+    freq = np.float64(theta) ** (-np.arange(half, dtype=np.float64) / half)
+    ang = np.asarray(positions, dtype=np.float64)[:, None] * freq[None, :]
+    return np.concatenate([np.cos(ang), np.sin(ang)], axis=1).astype(_F)
+
+
+def apply_rope(x: np.ndarray, rows: np.ndarray) -> np.ndarray:
+    """``x [..., T, D]`` rotated by ``rows [T, D]`` (or ``[D]``): ``x'[i] = x[i] cos_i - x[i+D/2] sin_i``,
+    ``x'[i+D/2] = x[i+D/2] cos_i + x[i] sin_i`` in fp32, products and sums rounded separately.  The kernel rounds
+    this to the activation dtype before it uses or stores the value; so does the caller of this function."""
+    x = np.asarray(x, dtype=_F)
+    half = x.shape[-1] // 2
+    cos, sin = rows[..., :half].astype(_F), rows[..., half:].astype(_F)
+    a, b = x[..., :half], x[..., half:]
+    return np.concatenate([a * cos - b * sin, b * cos + a * sin], axis=-1).astype(_F)

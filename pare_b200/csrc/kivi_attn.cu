@@ -58,6 +58,27 @@ constexpr size_t kCounterBytes = gemv::kCounterBytes;
 constexpr size_t kAttnSmemCap = 200 * 1024;
 constexpr float kNegBig = -1e30f;
 constexpr int kQS = 132;   // floats per staged query row: channel c at (c>>3 & 3)*32 + (c>>5)*8 + (c&7), rows 16 bytes off a bank period
+// Rotary position embedding of eight consecutive channels c8 .. c8+7 of a head (pairing i <-> i + D/2): own = the
+// channels themselves, other = their partners, cs = cos | sin of the position.  Separately rounded products and
+// sum (no fused multiply-add), then rounded to T: what an fp32 restatement computes.
+template <typename T>
+__device__ __forceinline__ uint4 rope8(const uint4& own, const uint4& other, const float* cs, int c8) {
+  const T* a = reinterpret_cast<const T*>(&own);
+  const T* b = reinterpret_cast<const T*>(&other);
+  const int c = c8 & (kD / 2 - 1);
+  const float4 co0 = *reinterpret_cast<const float4*>(cs + c), co1 = *reinterpret_cast<const float4*>(cs + c + 4);
+  const float4 si0 = *reinterpret_cast<const float4*>(cs + kD / 2 + c), si1 = *reinterpret_cast<const float4*>(cs + kD / 2 + c + 4);
+  const float co[8] = {co0.x, co0.y, co0.z, co0.w, co1.x, co1.y, co1.z, co1.w};
+  const float si[8] = {si0.x, si0.y, si0.z, si0.w, si1.x, si1.y, si1.z, si1.w};
+  const float sign = c8 < kD / 2 ? -1.f : 1.f;
+  uint4 out;
+  T* o = reinterpret_cast<T*>(&out);
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    o[j] = from_float<T>(__fadd_rn(__fmul_rn(to_float<T>(a[j]), co[j]), sign * __fmul_rn(to_float<T>(b[j]), si[j])));
+  return out;
+}
+
 __device__ __forceinline__ int q_pos(int c) { return (((c >> 3) & 3) << 5) | ((c >> 5) << 3) | (c & 7); }
 
 struct AttnParams {
@@ -76,6 +97,7 @@ struct AttnParams {
   int n_res;
   const void* new_k;   // newest token [B][H][D] (may be NULL: the window already holds all n_res tokens)
   const void* new_v;
+  const float* rope;    // NULL, or cos[0..D/2) | sin[0..D/2) of the newest token's position: q and new_k are rotated
   int64_t n_sb, n_sh;
   void* out;           // may be NULL when prep_xp is given
   int64_t o_sb, o_sh;
@@ -213,7 +235,8 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       const bool is_v = lane >= 16;
       const int part = lane & 15;   // 16 bytes each
       const T* src = reinterpret_cast<const T*>(is_v ? p.new_v : p.new_k) + (int64_t)b * p.n_sb + (int64_t)h * p.n_sh;
-      const uint4 val = *reinterpret_cast<const uint4*>(src + part * 8);
+      uint4 val = *reinterpret_cast<const uint4*>(src + part * 8);
+      if (p.rope && !is_v) val = rope8<T>(val, *reinterpret_cast<const uint4*>(src + (part ^ 8) * 8), p.rope, part * 8);
       *reinterpret_cast<uint4*>((is_v ? rv_s : rk_s) + (valid - 1) * kResPitch + part * 16) = val;
       *reinterpret_cast<uint4*>((is_v ? rv : rk) + (int64_t)(p.n_res - 1) * p.r_st + part * 8) = val;
     }
@@ -227,13 +250,19 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
       if (hh < p.rep) {
         uint4 raw;
-        if (p.q_vec) {
-          raw = *reinterpret_cast<const uint4*>(qg + (int64_t)hh * p.q_sh + c8);
-        } else {
-          T* r = reinterpret_cast<T*>(&raw);
+        auto load8 = [&](int c0) {
+          uint4 r4;
+          if (p.q_vec) {
+            r4 = *reinterpret_cast<const uint4*>(qg + (int64_t)hh * p.q_sh + c0);
+          } else {
+            T* r = reinterpret_cast<T*>(&r4);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) r[j] = qg[(int64_t)hh * p.q_sh + c8 + j];
-        }
+            for (int j = 0; j < 8; ++j) r[j] = qg[(int64_t)hh * p.q_sh + c0 + j];
+          }
+          return r4;
+        };
+        raw = load8(c8);
+        if (p.rope) raw = rope8<T>(raw, load8(c8 ^ (kD / 2)), p.rope, c8);
         const T* e = reinterpret_cast<const T*>(&raw);
         lo4 = make_float4(to_float<T>(e[0]), to_float<T>(e[1]), to_float<T>(e[2]), to_float<T>(e[3]));
         hi4 = make_float4(to_float<T>(e[4]), to_float<T>(e[5]), to_float<T>(e[6]), to_float<T>(e[7]));
@@ -689,7 +718,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
                           const float* k_scale, const float* k_zero, const uint8_t* v_codes, const float* v_scale,
                           const float* v_zero, int n_comp, void* res_k, void* res_v, int64_t res_stride_b,
                           int64_t res_stride_h, int64_t res_stride_t, int n_res, const void* new_k, const void* new_v,
-                          int64_t new_stride_b, int64_t new_stride_h, void* out, int64_t out_stride_b,
+                          int64_t new_stride_b, int64_t new_stride_h, const float* rope, void* out, int64_t out_stride_b,
                           int64_t out_stride_h, void* prepared_out, float softmax_scale, int B, int Hq, int H, int D,
                           int bits, int group, int cap, void* workspace, size_t workspace_bytes, void* stream) {
   using namespace pare;
@@ -716,6 +745,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
     PARE_REQUIRE(aligned16(new_k) && aligned16(new_v) && new_stride_b % 8 == 0 && new_stride_h % 8 == 0, PARE_ERR_ALIGN);
   }
   if (prepared_out) PARE_REQUIRE(aligned16(prepared_out), PARE_ERR_ALIGN);
+  if (rope) PARE_REQUIRE(aligned16(rope), PARE_ERR_ALIGN);
   if (n_comp > 0)
     PARE_REQUIRE(aligned16(k_codes) && aligned16(v_codes) && aligned16(k_scale) && aligned16(k_zero) && aligned16(v_scale) &&
                      aligned16(v_zero),
@@ -732,6 +762,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
   p.v_codes = v_codes; p.v_scale = v_scale; p.v_zero = v_zero;
   p.res_k = res_k; p.res_v = res_v; p.r_sb = res_stride_b; p.r_sh = res_stride_h; p.r_st = res_stride_t; p.n_res = n_res;
   p.new_k = new_k; p.new_v = new_v; p.n_sb = new_stride_b; p.n_sh = new_stride_h;
+  p.rope = rope;
   p.out = out; p.o_sb = out_stride_b; p.o_sh = out_stride_h;
   if (prepared_out) {
     p.prep_xp = prepared_out;

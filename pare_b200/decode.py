@@ -24,7 +24,7 @@ from torch import Tensor
 from pare_b200.config import QuantConfig
 from pare_b200.kernels import _lib
 from pare_b200.kernels.matmul_int4 import PreparedActivations
-from pare_b200.kv_cache import KVCacheConfig, QuantizedKVCache
+from pare_b200.kv_cache import KVCacheConfig, QuantizedKVCache, rope_table
 from pare_b200.layers.linear import QuantizedLinear
 
 SHAPES = {
@@ -78,7 +78,8 @@ class DecodeStack(nn.Module):
 
     def __init__(self, shape: str | tuple, *, device="cuda", dtype=torch.bfloat16, n_layers: int | None = None,
                  kv_config: KVCacheConfig | None = None, max_seq_len: int = 8192, tp_world: int = 1,
-                 process_group=None, seed: int = 0, peer_all_reduce: bool = True) -> None:
+                 process_group=None, seed: int = 0, peer_all_reduce: bool = True,
+                 rope_theta: float | None = 500000.0) -> None:
         super().__init__()
         hidden, ffn, hq, hkv, d, layers = SHAPES[shape] if isinstance(shape, str) else shape
         self.hidden, self.d = hidden, d
@@ -91,6 +92,8 @@ class DecodeStack(nn.Module):
         self.cache = QuantizedKVCache(self.n_layers, kv_config or KVCacheConfig(), max_seq_len=max_seq_len)
         self._code = _lib.dtype_code(dtype)
         self._prep_cache: dict[int, tuple] = {}
+        # rotary table [positions, D] (None: no positional rotation); q and the new key are rotated inside the attention launch
+        self.rope = rope_table(max_seq_len + 1, d, rope_theta, self.device) if rope_theta else None
         # one-launch all-reduce over NVLink peer memory for the small decode tensors; NCCL for anything larger
         self.peer_reduce = None
         if tp_world > 1 and peer_all_reduce:
@@ -166,6 +169,7 @@ class DecodeStack(nn.Module):
         if fused:
             p_attn = self._prepared(m)
             spare = torch.empty_like(resid)   # the residual stream ping-pongs: the kernels that normalise it read one, write the other
+        rope = self.rope[self.cache.seq_len(0)] if self.rope is not None else None   # the new token's position
         for i, blk in enumerate(self.blocks):
             d, hq, hkv = blk.d, blk.hq, blk.hkv
             if fused:
@@ -178,13 +182,13 @@ class DecodeStack(nn.Module):
             k = qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, 1, d))
             v = qkv[:, (hq + hkv) * d:].unflatten(1, (hkv, 1, d))
             if fused:
-                self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d), prepared_out=p_attn)
+                self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d), prepared_out=p_attn, rope=rope)
                 o = self._all_reduce(blk.o.forward_prepared(p_attn))
                 gate_up = blk.gate_up.forward_rmsnorm(resid, o, blk.norm2, resid_out=spare)
                 resid, spare = spare, resid
                 delta = self._all_reduce(blk.down.forward_silu_mul(gate_up))
             else:
-                attn = self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d))
+                attn = self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d), rope=rope)
                 o = self._all_reduce(blk.o(attn.reshape(m, hq * d)))
                 h2 = self._rmsnorm(resid, o, blk.norm2, store_residual=True)
                 act = self._silu_mul(blk.gate_up(h2), blk.ffn)

@@ -46,7 +46,7 @@ SIGNATURES: dict[str, tuple] = {
     "pare_kivi_attn_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "pare_kivi_decode_attn": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i,
                                    _vp, _vp, _i64, _i64, _i64, _i,
-                                   _vp, _vp, _i64, _i64,
+                                   _vp, _vp, _i64, _i64, _vp,
                                    _vp, _i64, _i64, _vp, C.c_float,
                                    _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "pare_kivi_attn_set_tuning": (None, [_i]),

@@ -45,6 +45,26 @@ class KVCacheConfig:
     residual_length: int = 128
 
 
+def rope_table(max_positions: int, head_dim: int, theta: float = 10000.0, device=None) -> Tensor:
+    """``[max_positions, head_dim]`` fp32: row p = ``cos(p f_i)`` for ``i < head_dim/2`` followed by ``sin(p f_i)``,
+    ``f_i = theta^(-2i/head_dim)`` -- the rotary table in the form :meth:`QuantizedKVCache.attend` and
+    :func:`apply_rope` take (angles computed in float64, stored in float32)."""
+    half = head_dim // 2
+    freq = theta ** (-torch.arange(half, dtype=torch.float64) / half)
+    ang = torch.arange(max_positions, dtype=torch.float64)[:, None] * freq[None, :]
+    return torch.cat([ang.cos(), ang.sin()], dim=1).to(torch.float32).to(device)
+
+
+def apply_rope(x: Tensor, rows: Tensor) -> Tensor:
+    """Rotary embedding of ``x [..., T, D]`` with ``rows [T, D]`` (or ``[D]``) of a :func:`rope_table`: pairs
+    ``(i, i + D/2)``, products and sum in float32, each rounded separately, result rounded to ``x.dtype`` -- what the
+    attention kernel does to ``q`` and the newest key."""
+    half = x.shape[-1] // 2
+    cos, sin = rows[..., :half].float(), rows[..., half:].float()
+    a, b = x[..., :half].float(), x[..., half:].float()
+    return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1).to(x.dtype)
+
+
 def plan_update(r_len: int, n_new: int, residual_length: int, group_size: int) -> tuple[int, int]:
     """Compression schedule of one ``update`` (reference: ``pare/kv_cache.py:231-244``).
 
@@ -198,11 +218,13 @@ class QuantizedKVCache:
             self._stores[layer_idx] = st
         return st
 
-    def _append(self, layer_idx: int, new_k: Tensor, new_v: Tensor, defer_single: bool = False):
+    def _append(self, layer_idx: int, new_k: Tensor, new_v: Tensor, defer_single: bool = False, rope: Tensor | None = None):
         """Append tokens to the residual window and compress what overflows it.
 
         With ``defer_single`` returns ``(store, deferred)``: when one token arrives and nothing has
-        to be compressed, the copy into the window is left to the attention kernel (``deferred``)."""
+        to be compressed, the copy into the window is left to the attention kernel (``deferred``).  ``rope``: rows of
+        a :func:`rope_table` for the new tokens; applied to the keys here unless the append is deferred (then the
+        attention kernel does it)."""
         if new_k.shape != new_v.shape or new_k.dim() != 4:
             raise ValueError("new_k / new_v must both be [B, H, new_tokens, D]")
         st = self._store(layer_idx, new_k)
@@ -217,6 +239,8 @@ class QuantizedKVCache:
                     and new_k.data_ptr() % 16 == 0 and new_v.data_ptr() % 16 == 0
                     and all(t.stride(3) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 for t in (new_k, new_v))
                     and new_k.stride() == new_v.stride())
+        if rope is not None and not deferred:   # the kernel rotates only a key it appends itself
+            new_k = apply_rope(new_k, rope)
         if deferred:
             pass
         elif total <= st.r_cap:
@@ -272,7 +296,7 @@ class QuantizedKVCache:
         return full_k, full_v
 
     def attend(self, layer_idx: int, q: Tensor, new_k: Tensor, new_v: Tensor, scale: float | None = None,
-               prepared_out=None) -> Tensor | None:
+               prepared_out=None, rope: Tensor | None = None) -> Tensor | None:
         """Append one step's keys / values, then attention of ``q`` over the whole cache.
 
         ``q`` is ``[B, Hq, 1, D]`` (or ``[B, Hq, D]``) with ``Hq`` a multiple of the KV heads
@@ -284,11 +308,16 @@ class QuantizedKVCache:
         side at all: the attention kernel reads it where it is and stores it into the residual
         window itself.  With ``prepared_out`` (a ``PreparedActivations`` of ``B`` rows and
         ``Hq * D`` columns) the result is written as prepared activations of the next linear
-        instead, and ``None`` is returned.
+        instead, and ``None`` is returned.  With ``rope`` (row ``[D]`` of a :func:`rope_table` for the new token's
+        position, float32) ``q`` and the new key get the rotary embedding inside the same launch, and the key is
+        stored rotated; ``q`` and ``new_k`` are then what the q|k|v projection gave, one new token only.
         """
         if q.dtype not in (torch.float16, torch.bfloat16):
             raise ValueError("attend() needs q in float16 or bfloat16")
-        st, fused_new = self._append(layer_idx, new_k, new_v, defer_single=True)
+        if rope is not None:
+            if new_k.shape[2] != 1 or rope.shape != (q.shape[-1],) or rope.dtype != torch.float32 or not rope.is_contiguous():
+                raise ValueError("rope must be one float32 row [D] of rope_table and needs exactly one new token")
+        st, fused_new = self._append(layer_idx, new_k, new_v, defer_single=True, rope=rope)
         if q.dtype != st.dtype:
             raise ValueError("attend() needs q in the cache dtype")
         q3 = q.reshape(q.shape[0], q.shape[1], q.shape[-1])
@@ -310,6 +339,7 @@ class QuantizedKVCache:
             *st.cache_args(), st.n_comp,
             st.res_k.data_ptr(), st.res_v.data_ptr(), st.res_k.stride(0), st.res_k.stride(1), st.res_k.stride(2), st.r_len,
             _lib.ptr(nk), _lib.ptr(nv), nk.stride(0) if fused_new else 0, nk.stride(1) if fused_new else 0,
+            _lib.ptr(rope),
             _lib.ptr(out), out.stride(0) if out is not None else 0, out.stride(1) if out is not None else 0,
             prepared_out.data_ptr() if prepared_out is not None else None,
             float(scale if scale is not None else 1.0 / math.sqrt(D)),

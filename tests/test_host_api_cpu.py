@@ -266,3 +266,28 @@ def test_library_exports_every_declared_symbol():
     handle.pare_w4a16_workspace_bytes.restype = ctypes.c_size_t
     assert handle.pare_w4a16_workspace_bytes(1, 4096, 4096, 128) >= 65536
     assert handle.pare_w4a16_workspace_bytes(0, 1, 1, 1) == 0
+
+
+def test_rope_helpers_agree_with_the_oracle():
+    """``rope_table`` / ``apply_rope`` (host side of the rotary step the attention kernel performs) against the numpy
+    restatement: the same table up to libm rounding, the same rotation bit for bit, norm-preserving per pair,
+    identity at position 0."""
+    import numpy as np
+    from oracle import kivi as ok
+    from pare_b200.kv_cache import apply_rope, rope_table
+
+    table = rope_table(300, 128, 500000.0)
+    rows = ok.rope_rows(np.arange(300), 128, 500000.0)
+    assert table.shape == (300, 128) and table.dtype == torch.float32
+    assert np.allclose(table.numpy(), rows, rtol=0, atol=2e-6)
+    x = torch.randn(2, 3, 5, 128, generator=torch.Generator().manual_seed(0))
+    for dtype in (torch.float16, torch.bfloat16):
+        xd = x.to(dtype)
+        got = apply_rope(xd, table[100:105])
+        ref = torch.from_numpy(ok.apply_rope(xd.float().numpy(), table[100:105].numpy())).to(dtype)
+        assert torch.equal(got, ref)
+        assert torch.equal(apply_rope(xd, table[0]), xd)
+    y = ok.apply_rope(x.numpy(), rows[200])
+    n0 = x.numpy()[..., :64] ** 2 + x.numpy()[..., 64:] ** 2
+    n1 = y[..., :64] ** 2 + y[..., 64:] ** 2
+    assert np.allclose(n0, n1, rtol=1e-5, atol=1e-6)

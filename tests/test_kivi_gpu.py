@@ -265,3 +265,60 @@ def test_decode_attention_is_deterministic_and_steps(cuda_lib):
 
 def ok_t(a):
     return torch.from_numpy(a)
+
+
+# ---- rotary embedding inside the attention launch ------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("ctx", [200, 160])
+def test_decode_attention_rotates_q_and_new_key(ctx, dtype, cuda_lib):
+    """``attend(..., rope=row)``: q and the newest key get the rotary embedding inside the launch.  The stored key is
+    bit-exact the oracle's rotation rounded to the dtype; the attention output meets the usual bars against the oracle
+    on rotated inputs.  ctx = 200: the kernel appends (and rotates) the key itself; ctx = 160: the append compresses a
+    group first, so the host side rotates the key and the kernel only the query."""
+    from pare_b200.kv_cache import apply_rope, rope_table
+    bsz, hkv, hq = 2, 2, 8
+    g = torch.Generator().manual_seed(ctx)
+    k = torch.randn(bsz, hkv, ctx, D, generator=g)
+    v = torch.randn(bsz, hkv, ctx, D, generator=g)
+    k[..., 5] *= 10.0
+    q = torch.randn(bsz, hq, 1, D, generator=g)
+    k, v, q = k.to(dtype).cuda(), v.to(dtype).cuda(), q.to(dtype).cuda()
+    table = rope_table(ctx + 8, D, 500000.0, device="cuda")
+    rows = ok.rope_rows(np.arange(ctx + 8), D, 500000.0)
+    assert np.allclose(table.cpu().numpy(), rows, rtol=0, atol=2e-6)   # libm vs torch cos / sin of float64 angles
+    rows = table.cpu().numpy()
+    pos = ctx - 1
+    cache = QuantizedKVCache(1, KVCacheConfig(bits=4, group_size=32, residual_length=128), max_seq_len=ctx + 256)
+    cache.update(0, k[:, :, :-1], v[:, :, :-1])           # the older keys count as rotated already
+    n_comp_before = cache._stores[0].n_comp
+    out = cache.attend(0, q, k[:, :, -1:], v[:, :, -1:], rope=table[pos])
+    assert (cache._stores[0].n_comp > n_comp_before) == (ctx == 160)
+
+    cast = lambda a: torch.from_numpy(a).to(dtype).float().numpy()
+    k_rot = cast(ok.apply_rope(k[:, :, -1:].float().cpu().numpy(), rows[pos]))
+    q_rot = cast(ok.apply_rope(q.float().cpu().numpy(), rows[pos]))
+    assert np.array_equal(cache._residual_k[0][:, :, -1:].float().cpu().numpy(), k_rot)     # stored key: bit-exact
+    assert np.array_equal(apply_rope(k[:, :, -1:], table[pos]).float().cpu().numpy(), k_rot)  # the torch helper too
+    k_all = np.concatenate([k[:, :, :-1].float().cpu().numpy(), k_rot], axis=2)
+    ref_cache = ok.Cache(4, 32, 128)
+    ref_cache.update(k_all[:, :, :-1], v[:, :, :-1].float().cpu().numpy())
+    rk, rv = ref_cache.update(k_all[:, :, -1:], v[:, :, -1:].float().cpu().numpy())
+    _check_attn(out.float().cpu().numpy(), ok.decode_attention(q_rot, cast(rk), cast(rv)), ok.decode_attention(q_rot, rk, rv), dtype)
+    # position 0 is the identity
+    cache2 = QuantizedKVCache(1, KVCacheConfig(bits=4, group_size=32, residual_length=128), max_seq_len=64)
+    o_id = cache2.attend(0, q, k[:, :, :1], v[:, :, :1], rope=table[0])
+    cache3 = QuantizedKVCache(1, KVCacheConfig(bits=4, group_size=32, residual_length=128), max_seq_len=64)
+    assert torch.equal(o_id, cache3.attend(0, q, k[:, :, :1], v[:, :, :1]))
+
+
+def test_rope_argument_checks(cuda_lib):
+    from pare_b200.kv_cache import rope_table
+    k, v = _kv(4, b=1, h=2)
+    q = torch.randn(1, 4, 1, D).half().cuda()
+    table = rope_table(16, D, device="cuda")
+    cache = QuantizedKVCache(1, KVCacheConfig(bits=4, group_size=32, residual_length=128), max_seq_len=64)
+    with pytest.raises(ValueError):
+        cache.attend(0, q, k[:, :, :2], v[:, :, :2], rope=table[1])      # two new tokens
+    with pytest.raises(ValueError):
+        cache.attend(0, q, k[:, :, :1], v[:, :, :1], rope=table[1].half())
