@@ -320,16 +320,21 @@ def prefill_table(stack, batches=(64, 256)) -> dict:
     return table
 
 
-def attention_table(dtype, device, peak: float, cases=((1, 4096, 32, 4), (16, 4096, 8, 4), (16, 4096, 8, 2))) -> dict:
+def attention_table(dtype, device, peak: float,
+                    cases=((1, 4096, 32, 4), (16, 4096, 8, 4), (16, 4096, 8, 2), (16, 4096, 8, 4, 32))) -> dict:
     """Fused KIVI decode attention alone (8 KV heads, 32 query heads, D = 128, g32, residual window 128):
     one CUDA graph over ``layers`` distinct caches (larger than L2 together), us per call and fraction of the HBM
     peak by the bytes the call must read (168 B per compressed token and KV head at 4 bits, 104 B at 2 bits,
-    512 B per window token)."""
+    512 B per window token; with values in 32-channel groups -- a fifth element 32 in the case -- 24 B more per
+    compressed token)."""
     from pare_b200.kv_cache import KVCacheConfig, QuantizedKVCache
 
     table = {}
-    for batch, ctx, layers, bits in cases:
-        cache = QuantizedKVCache(layers, KVCacheConfig(bits=bits, group_size=32, residual_length=128), max_seq_len=ctx + 256)
+    for case in cases:
+        batch, ctx, layers, bits = case[:4]
+        v_group = case[4] if len(case) > 4 else None
+        cache = QuantizedKVCache(layers, KVCacheConfig(bits=bits, group_size=32, residual_length=128, v_group_size=v_group),
+                                 max_seq_len=ctx + 256)
         g = torch.Generator(device=device).manual_seed(0)
         n0 = 128 + ((ctx - 128) // 32) * 32
         for layer in range(layers):
@@ -350,8 +355,9 @@ def attention_table(dtype, device, peak: float, cases=((1, 4096, 32, 4), (16, 40
         sec = time_events(gr.replay, reps, 3, 1)
         us = sec / (reps * layers) * 1e6
         st = cache._stores[0]
-        nbytes = batch * 8 * (st.n_comp * (168 if bits == 4 else 104) + (st.r_len + 1) * 512) + batch * 32 * 128 * 4
-        table[f"b{batch}_ctx{ctx}_{bits}bit"] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peak, 4)}
+        per_token = (168 if bits == 4 else 104) + (24 if v_group else 0)
+        nbytes = batch * 8 * (st.n_comp * per_token + (st.r_len + 1) * 512) + batch * 32 * 128 * 4
+        table[f"b{batch}_ctx{ctx}_{bits}bit" + (f"_vg{v_group}" if v_group else "")] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peak, 4)}
         del gr, cache
     return table
 

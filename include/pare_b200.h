@@ -144,8 +144,13 @@ int pare_w4a16_forward_produced(int producer, const void* a, const void* b, cons
  *                                           in which the decode-attention kernel reads it
  *   v_codes [B][H][cap/128][D][128*bits/8]  uint8, packed along tokens inside 128-token blocks
  *                                           (token t of the block at bit t*bits of row d)
- *   v_scale, v_zero [B][H][cap]             fp32, per token (min/max over all D channels)
- * bits in {2,4,8}; group in {16,32,64,128}; D % 32 == 0, D <= 256.
+ *   v_scale, v_zero [B][H][cap][D/v_group]  fp32, per (token, group of v_group channels): min/max over the
+ *                                           group.  v_group == D (or 0) is the reference's form, one pair per
+ *                                           token over all D channels; v_group == 32 is the finer grouping
+ *                                           of the KIVI paper (not in the reference: _quantize_values with
+ *                                           the channel axis viewed as [D/32][32])
+ * bits in {2,4,8}; group in {16,32,64,128}; D % 32 == 0, D <= 256; v_group a multiple of 32 that divides D
+ * (the fused attention takes v_group in {0, D, 32}).
  * Codes, scales and zeros are bit-identical to the reference's (same fp32 operation order).
  */
 
@@ -157,7 +162,7 @@ int pare_kivi_append(const void* k_src, const void* v_src, int src_dtype,
                      int n_tokens, int t0,
                      uint8_t* k_codes, float* k_scale, float* k_zero,
                      uint8_t* v_codes, float* v_scale, float* v_zero,
-                     int B, int H, int D, int bits, int group, int cap, void* stream);
+                     int B, int H, int D, int bits, int group, int v_group, int cap, void* stream);
 
 /* Dense reconstruction code*scale+zero of compressed tokens 0..n_comp-1 into
  * out_k / out_v [B][H][>=n_comp][D] (out_dtype F16/BF16/F32, element strides given).
@@ -165,7 +170,7 @@ int pare_kivi_append(const void* k_src, const void* v_src, int src_dtype,
  * compressed store). */
 int pare_kivi_dequant(const uint8_t* k_codes, const float* k_scale, const float* k_zero,
                       const uint8_t* v_codes, const float* v_scale, const float* v_zero,
-                      int B, int H, int D, int bits, int group, int cap, int n_comp,
+                      int B, int H, int D, int bits, int group, int v_group, int cap, int n_comp,
                       void* out_k, void* out_v, int out_dtype,
                       int64_t stride_b, int64_t stride_h, int64_t stride_t, void* stream);
 
@@ -204,7 +209,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
                           const float* rope,
                           void* out, int64_t out_stride_b, int64_t out_stride_h, void* prepared_out,
                           float softmax_scale,
-                          int B, int Hq, int H, int D, int bits, int group, int cap,
+                          int B, int Hq, int H, int D, int bits, int group, int v_group, int cap,
                           void* workspace, size_t workspace_bytes, void* stream);
 
 /* Tuning override for experiments: compressed tokens per CTA (multiple of 128, <= 512); 0 = auto. */

@@ -35,9 +35,20 @@ def quantize_keys(k: np.ndarray, bits: int, group_size: int):
     return q.reshape(b, h, n, d), scale[:, :, :, 0, :], lo[:, :, :, 0, :]
 
 
-def quantize_values(v: np.ndarray, bits: int, group_size: int):
-    """``v [B,H,n,D]`` fp32 → codes ``[B,H,n,D]``, scale/zero ``[B,H,n,1]`` (one pair per token)."""
+def quantize_values(v: np.ndarray, bits: int, group_size: int, v_group: int | None = None):
+    """``v [B,H,n,D]`` fp32 → codes ``[B,H,n,D]``, scale/zero ``[B,H,n,1]`` (one pair per token).
+
+    ``v_group`` (not in the reference; the finer grouping of the KIVI paper): the same function with the channel
+    axis viewed as ``[D/v_group, v_group]`` -- one pair per token and group of ``v_group`` channels, scale/zero
+    ``[B,H,n,D/v_group]``."""
     v = np.asarray(v, dtype=_F)
+    if v_group is not None and v_group != v.shape[3]:
+        b, h, n, d = v.shape
+        vg = v.reshape(b, h, n, d // v_group, v_group)
+        lo = vg.min(axis=4, keepdims=True)
+        hi = vg.max(axis=4, keepdims=True)
+        q, scale = _affine_codes(vg, lo, hi, bits)
+        return q.reshape(b, h, n, d), scale[..., 0], lo[..., 0]
     lo = v.min(axis=3, keepdims=True)
     hi = v.max(axis=3, keepdims=True)
     q, scale = _affine_codes(v, lo, hi, bits)
@@ -51,6 +62,10 @@ def dequantize_keys(q: np.ndarray, scale: np.ndarray, zero: np.ndarray, group_si
 
 
 def dequantize_values(q: np.ndarray, scale: np.ndarray, zero: np.ndarray) -> np.ndarray:
+    if scale.shape[3] > 1:   # [B,H,n,D/v_group]: one pair per group of channels
+        b, h, n, d = q.shape
+        qg = q.astype(_F).reshape(b, h, n, scale.shape[3], -1)
+        return (qg * scale[..., None] + zero[..., None]).reshape(b, h, n, d).astype(_F)
     return (q.astype(_F) * scale + zero).astype(_F)
 
 
@@ -62,8 +77,8 @@ class Cache:
     final cast to the input dtype).
     """
 
-    def __init__(self, bits: int = 4, group_size: int = 32, residual_length: int = 128):
-        self.bits, self.G, self.R = bits, group_size, residual_length
+    def __init__(self, bits: int = 4, group_size: int = 32, residual_length: int = 128, v_group: int | None = None):
+        self.bits, self.G, self.R, self.v_group = bits, group_size, residual_length, v_group
         self.comp = None   # (kq, ks, kz, vq, vs, vz)
         self.rk = None
         self.rv = None
@@ -75,7 +90,7 @@ class Cache:
         groups = max(0, rk.shape[2] - self.R) // self.G
         if groups > 0:
             n = groups * self.G
-            new = quantize_keys(rk[:, :, :n], self.bits, self.G) + quantize_values(rv[:, :, :n], self.bits, self.G)
+            new = quantize_keys(rk[:, :, :n], self.bits, self.G) + quantize_values(rv[:, :, :n], self.bits, self.G, self.v_group)
             self.comp = new if self.comp is None else tuple(
                 np.concatenate([a, b], axis=2) for a, b in zip(self.comp, new))
             rk, rv = rk[:, :, n:], rv[:, :, n:]

@@ -49,6 +49,9 @@ constexpr int kAttnWarps = 8;
 constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kD = 128;
 constexpr int kHeads = 8;
+constexpr int kMaxVG = 4;        // value scale / zero groups per token at most (32 channels each)
+// bytes of shared memory in front of q: mbarrier, flag, statistics [2 + vg][8]
+__host__ __device__ constexpr int attn_header(int vg) { return vg == 1 ? 128 : 256; }
 constexpr int kMaxChunk = 512;
 constexpr int kResChunk = 64;            // residual tokens per split
 constexpr int kResPitch = 320;           // bytes per staged residual row (256 + 64: conflict-free 16-byte reads down a column)
@@ -105,6 +108,7 @@ struct AttnParams {
   float4* prep_tab;
   float sm_scale;
   int B, Hq, H, rep, group, cap, n_comp;
+  int vg;        // value scale / zero groups per token (1: one per token; 4: one per 32 channels)
   int chunk, n_csplit, n_split;
   int s_stride;  // floats per score row
   int p_stride;  // bytes per probability row
@@ -138,8 +142,8 @@ __device__ __forceinline__ uint32_t pair_to_h2<__nv_bfloat16>(uint32_t raw) {
 __device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // bytes of the operand stage of a compressed split
-__host__ __device__ inline int stage_bytes(int chunk, int group, int bits) {
-  return chunk * (kD * bits / 8) + 2 * (chunk / group) * kD * 4 + (chunk / 128) * kD * (128 * bits / 8) + 2 * chunk * 4;
+__host__ __device__ inline int stage_bytes(int chunk, int group, int bits, int vg) {
+  return chunk * (kD * bits / 8) + 2 * (chunk / group) * kD * 4 + (chunk / 128) * kD * (128 * bits / 8) + 2 * chunk * 4 * vg;
 }
 
 // codes - CENTER of one word as exact fp16 pairs: four pairs (c_k, c_k+4) at 4 bits, eight pairs (c_j, c_j+8) at 2 bits
@@ -149,7 +153,7 @@ __device__ __forceinline__ void unpack_exact(uint32_t w, uint32_t (&p)[BITS == 4
   else unpack_codes2_exact<CENTER>(w, p);
 }
 
-template <typename T, int BITS>
+template <typename T, int BITS, int VG>
 __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int NW = BITS == 4 ? 4 : 2;          // code words of the 32 channels / tokens a lane owns
@@ -169,12 +173,13 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
   int* s_last = reinterpret_cast<int*>(smem + 8);
   float* st_m = reinterpret_cast<float*>(smem + 16);                // [8]
   float* st_l = st_m + kHeads;
-  float* st_c = st_l + kHeads;
-  float* qf = reinterpret_cast<float*>(smem + 128);                 // [8][kQS], channels in q_pos order
+  float* st_c = st_l + kHeads;                                      // [vg][8]
+  float* qf = reinterpret_cast<float*>(smem + attn_header(VG));         // [8][kQS], channels in q_pos order
   float* S = qf + kHeads * kQS;                                     // [8][s_stride]
-  unsigned char* P = reinterpret_cast<unsigned char*>(S + kHeads * p.s_stride);  // [8][p_stride] fp16 hi parts
-  unsigned char* P2 = P + kHeads * p.p_stride;                                   // [8][p_stride] fp16 lo parts
-  unsigned char* stage = P2 + kHeads * p.p_stride;   // 128-byte aligned by construction of the strides
+  // per value group: [8][p_stride] fp16 hi parts, then [8][p_stride] fp16 lo parts
+  unsigned char* P = reinterpret_cast<unsigned char*>(S + kHeads * p.s_stride);
+  const int pgs = 2 * kHeads * p.p_stride;           // bytes per value group
+  unsigned char* stage = P + VG * pgs;             // 128-byte aligned by construction of the strides
   const uint32_t bar = smem_u32(bar_p);
   int* status = p.counters + kStatusIndex;
 
@@ -193,7 +198,7 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
   float* kz_s = ks_s + ngr_full * kD;
   unsigned char* vc_s = reinterpret_cast<unsigned char*>(kz_s + ngr_full * kD);
   float* vs_s = reinterpret_cast<float*>(vc_s + (p.chunk / 128) * kD * VROW);
-  float* vz_s = vs_s + p.chunk;
+  float* vz_s = vs_s + p.chunk * VG;               // [token][vg] both
 
   if (!is_res) {
     chunk_start = split * p.chunk;
@@ -202,13 +207,13 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       // the compressed cache does not change during a decode step: fetch before the dependency wait
       const int ngroups = valid / p.group, nblk = (valid + 127) >> 7;
       const size_t grow = bh * (p.cap / p.group) + chunk_start / p.group;
-      mbar_expect_tx(bar, valid * KROW + 2 * ngroups * kD * 4 + nblk * kD * VROW + 2 * valid * 4);
+      mbar_expect_tx(bar, valid * KROW + 2 * ngroups * kD * 4 + nblk * kD * VROW + 2 * valid * 4 * VG);
       bulk_load(smem_u32(kc_s), p.k_codes + (bh * p.cap + chunk_start) * (size_t)KROW, valid * KROW, bar);
       bulk_load(smem_u32(ks_s), p.k_scale + grow * kD, ngroups * kD * 4, bar);
       bulk_load(smem_u32(kz_s), p.k_zero + grow * kD, ngroups * kD * 4, bar);
       bulk_load(smem_u32(vc_s), p.v_codes + (bh * (p.cap / 128) + (chunk_start >> 7)) * (size_t)(kD * VROW), nblk * kD * VROW, bar);
-      bulk_load(smem_u32(vs_s), p.v_scale + bh * p.cap + chunk_start, valid * 4, bar);
-      bulk_load(smem_u32(vz_s), p.v_zero + bh * p.cap + chunk_start, valid * 4, bar);
+      bulk_load(smem_u32(vs_s), p.v_scale + (bh * p.cap + chunk_start) * VG, valid * 4 * VG, bar);
+      bulk_load(smem_u32(vz_s), p.v_zero + (bh * p.cap + chunk_start) * VG, valid * 4 * VG, bar);
     }
   }
   __syncthreads();   // the barrier is initialised for everybody
@@ -376,16 +381,13 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       float m = kNegBig;
       for (int t = lane; t < valid; t += 32) m = fmaxf(m, srow[t]);
       m = warp_max(m);
-      float l = 0.f, z = 0.f;
+      float l = 0.f, z[VG] = {};
       unsigned char* prow = P + warp * p.p_stride;
       for (int t = lane; t < nblk * 128; t += 32) {
-        float pv = 0.f;
+        float e = 0.f;
         if (t < valid) {
-          const float e = __expf(srow[t] - m);
+          e = __expf(srow[t] - m);
           l += e;
-          const float sc = vs_s[t];
-          z = fmaf(e, fmaf((float)VCENTER, sc, vz_s[t]), z);   // value codes are centred in phase C
-          pv = e * sc;
         }
         // operand layout of a 128-token block: [4 operand quads][lane quad 0..3] chunks of 8 halves = four pairs, in the
         // order the pairs of the value code words come out of the unpack (4 bits: (t_k, t_k+4) per 8 tokens; 2 bits:
@@ -399,17 +401,31 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
           const int e = tl & 15, j = e & 7;
           off = (t >> 7) * 256 + ((((tl >> 4) & 1) * 2 + (j >> 2)) * 64) + (tl >> 5) * 16 + (((j & 3) * 2 + (e >> 3)) * 2);
         }
-        // two-term fp16 expansion of p * scale (hi + residual): keeps P.V at fp32-level accuracy
-        const __half hv = __float2half_rn(pv);
-        *reinterpret_cast<__half*>(prow + off) = hv;
-        *reinterpret_cast<__half*>(prow + kHeads * p.p_stride + off) = __float2half_rn(pv - __half2float(hv));
+#pragma unroll
+        for (int g = 0; g < VG; ++g) {
+          {
+            float pv = 0.f;
+            if (t < valid) {
+              const float sc = vs_s[t * VG + g];
+              z[g] = fmaf(e, fmaf((float)VCENTER, sc, vz_s[t * VG + g]), z[g]);   // value codes are centred in phase C
+              pv = e * sc;
+            }
+            // two-term fp16 expansion of p * scale (hi + residual): keeps P.V at fp32-level accuracy
+            const __half hv = __float2half_rn(pv);
+            *reinterpret_cast<__half*>(prow + g * pgs + off) = hv;
+            *reinterpret_cast<__half*>(prow + g * pgs + kHeads * p.p_stride + off) = __float2half_rn(pv - __half2float(hv));
+          }
+        }
       }
       l = warp_sum(l);
-      z = warp_sum(z);
+#pragma unroll
+      for (int g = 0; g < VG; ++g) z[g] = warp_sum(z[g]);
       if (lane == 0) {
         st_m[warp] = m;
         st_l[warp] = l;
-        st_c[warp] = z;
+#pragma unroll
+        for (int g = 0; g < VG; ++g)
+          st_c[g * kHeads + warp] = z[g];
       }
     }
     __syncthreads();
@@ -417,6 +433,7 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
     // ================= phase C: O^T[c][h] = sum_t code_v[t][c] * P'[t][h] =================
     {
       const int row = warp * 16 + gid;  // channel
+      const unsigned char* Pg = P + ((warp * 16 * VG) / kD) * pgs;   // probabilities scaled for this warp's channel group
       const unsigned char* vbase = vc_s + row * VROW + tig * LB;
       float o0[4] = {0.f, 0.f, 0.f, 0.f}, o1[4] = {0.f, 0.f, 0.f, 0.f};
       for (int blk = 0; blk < nblk; ++blk) {
@@ -442,8 +459,8 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
             const int i = w * (PW / 4) + q4;   // operand quad
             uint4 pf = make_uint4(0u, 0u, 0u, 0u), pl = make_uint4(0u, 0u, 0u, 0u);
             if (gid < p.rep) {
-              pf = *reinterpret_cast<const uint4*>(P + gid * p.p_stride + blk * 256 + i * 64 + tig * 16);
-              pl = *reinterpret_cast<const uint4*>(P2 + gid * p.p_stride + blk * 256 + i * 64 + tig * 16);
+              pf = *reinterpret_cast<const uint4*>(Pg + gid * p.p_stride + blk * 256 + i * 64 + tig * 16);
+              pl = *reinterpret_cast<const uint4*>(Pg + kHeads * p.p_stride + gid * p.p_stride + blk * 256 + i * 64 + tig * 16);
             }
             mma16816<__half>(o0, pa[q4 * 4], pb[q4 * 4], pa[q4 * 4 + 1], pb[q4 * 4 + 1], pf.x, pf.y);
             mma16816<__half>(o1, pa[q4 * 4 + 2], pb[q4 * 4 + 2], pa[q4 * 4 + 3], pb[q4 * 4 + 3], pf.z, pf.w);
@@ -462,7 +479,7 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int hh = tig * 2 + (i & 1), c = row + 8 * (i >> 1);
-        if (hh < p.rep) __stcg(po + hh * kD + c, o_acc[i] + st_c[hh]);
+        if (hh < p.rep) __stcg(po + hh * kD + c, o_acc[i] + st_c[((warp * 16 * VG) / kD) * kHeads + hh]);
       }
     }
   } else {
@@ -684,7 +701,7 @@ struct AttnPlan {
   size_t smem;
 };
 
-AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group, int bits) {
+AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group, int bits, int vg) {
   AttnPlan a;
   a.chunk = pick_chunk(B, H, n_comp, group);
   a.n_csplit = (n_comp + a.chunk - 1) / a.chunk;
@@ -694,9 +711,9 @@ AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group, int bits
   a.s_stride = span + 4;
   a.p_stride = (span / 128) * 256 + 64;
   if (a.p_stride < 512) a.p_stride = 512;   // the residual branch reuses the buffer for an [8][128] fp32 reduction
-  const int st = stage_bytes(a.chunk, group, bits), rs = 2 * kResChunk * kResPitch;
-  a.smem = 128 + (size_t)kHeads * kQS * sizeof(float) + (size_t)kHeads * a.s_stride * sizeof(float) +
-           2 * (size_t)kHeads * a.p_stride + (size_t)(st > rs ? st : rs);
+  const int st = stage_bytes(a.chunk, group, bits, vg), rs = 2 * kResChunk * kResPitch;
+  a.smem = attn_header(vg) + (size_t)kHeads * kQS * sizeof(float) + (size_t)kHeads * a.s_stride * sizeof(float) +
+           2 * (size_t)kHeads * a.p_stride * vg + (size_t)(st > rs ? st : rs);
   return a;
 }
 
@@ -720,8 +737,10 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
                           int64_t res_stride_h, int64_t res_stride_t, int n_res, const void* new_k, const void* new_v,
                           int64_t new_stride_b, int64_t new_stride_h, const float* rope, void* out, int64_t out_stride_b,
                           int64_t out_stride_h, void* prepared_out, float softmax_scale, int B, int Hq, int H, int D,
-                          int bits, int group, int cap, void* workspace, size_t workspace_bytes, void* stream) {
+                          int bits, int group, int v_group, int cap, void* workspace, size_t workspace_bytes, void* stream) {
   using namespace pare;
+  PARE_REQUIRE(v_group == 0 || v_group == D || v_group == 32, PARE_ERR_UNSUPPORTED);
+  const int vg = (v_group == 0 || v_group == D) ? 1 : D / v_group;
   PARE_REQUIRE(B > 0 && Hq > 0 && H > 0 && Hq % H == 0, PARE_ERR_SHAPE);
   PARE_REQUIRE(D == kD && (bits == 4 || bits == 2), PARE_ERR_UNSUPPORTED);
   PARE_REQUIRE(Hq / H <= kHeads, PARE_ERR_UNSUPPORTED);
@@ -751,7 +770,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
                      aligned16(v_zero),
                  PARE_ERR_ALIGN);
 
-  const AttnPlan plan = make_attn_plan(B, H, n_comp, n_res, group, bits);
+  const AttnPlan plan = make_attn_plan(B, H, n_comp, n_res, group, bits, vg);
   PARE_REQUIRE(plan.chunk % 128 == 0 && plan.chunk % group == 0 && plan.chunk <= kMaxChunk, PARE_ERR_UNSUPPORTED);
   PARE_REQUIRE(plan.smem <= kAttnSmemCap && (size_t)plan.n_split * 2 * kHeads * sizeof(float) <= 16384, PARE_ERR_UNSUPPORTED);
 
@@ -770,6 +789,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
   }
   p.sm_scale = softmax_scale;
   p.B = B; p.Hq = Hq; p.H = H; p.rep = Hq / H; p.group = group; p.cap = cap; p.n_comp = n_comp;
+  p.vg = vg;
   p.chunk = plan.chunk; p.n_csplit = plan.n_csplit; p.n_split = plan.n_split;
   p.s_stride = plan.s_stride; p.p_stride = plan.p_stride;
   const size_t need = kCounterBytes + (size_t)B * H * p.n_split * (kHeads * kD + kHeads * 2) * sizeof(float);
@@ -792,8 +812,12 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess ? PARE_OK : PARE_ERR_CUDA;
   };
-  if (bits == 4) return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 4>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 4>);
-  return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 2>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 2>);
+  if (vg == 1) {
+    if (bits == 4) return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 4, 1>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 4, 1>);
+    return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 2, 1>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 2, 1>);
+  }
+  if (bits == 4) return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 4, kMaxVG>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 4, kMaxVG>);
+  return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 2, kMaxVG>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 2, kMaxVG>);
 }
 
 }  // extern "C"

@@ -7,7 +7,8 @@
 //                                            position kmeta_pos(c, D) of the row (common.cuh)
 //   v_codes [B][H][cap/128][D][128*bits/8]   codes packed along TOKENS inside blocks of 128 tokens:
 //                                            token t of the block sits at bit (t*bits) of row d
-//   v_scale, v_zero [B][H][cap]              fp32 per token
+//   v_scale, v_zero [B][H][cap][D/v_group]   fp32 per (token, group of v_group channels); v_group == D (one per
+//                                            token, the reference's form) or 32
 // The two code layouts follow the two contractions of attention: q.K^T contracts channels,
 // P.V contracts tokens, so each packs along the axis its consumer reads 128 bits at a time.
 //
@@ -30,6 +31,7 @@ struct CachePtrs {
   float* v_scale;
   float* v_zero;
   int B, H, D, bits, group, cap;
+  int v_group;   // channels that share a value scale / zero: D, or a multiple of 32 that divides D
 };
 
 template <typename T>
@@ -56,8 +58,9 @@ __global__ void kivi_append_kernel(const void* k_src, const void* v_src, int64_t
   const size_t bh = (size_t)b * c.H + h;
 
   uint8_t* codes = smem;                                                   // [G][D]
-  float* v_lo = reinterpret_cast<float*>(smem + (size_t)G * D);            // [G]
-  float* v_sc = v_lo + G;                                                  // [G]
+  const int VG = D / c.v_group;                                            // value groups per token
+  float* v_lo = reinterpret_cast<float*>(smem + (size_t)G * D);            // [G][VG]
+  float* v_sc = v_lo + G * VG;                                             // [G][VG]
 
   // ---- keys: per channel over the G tokens of the group ----
   {
@@ -90,22 +93,24 @@ __global__ void kivi_append_kernel(const void* k_src, const void* v_src, int64_t
   }
   __syncthreads();
 
-  // ---- values: per token over all D channels ----
+  // ---- values: per token over each group of v_group channels (all D of them in the reference's form) ----
   for (int t = warp; t < G; t += nwarps) {
-    float lo = INFINITY, hi = -INFINITY;
-    for (int cc = lane; cc < D; cc += 32) {
-      const float x = load_as_float<T>(v_src, src0 + (int64_t)t * st + cc);
-      lo = fminf(lo, x);
-      hi = fmaxf(hi, x);
-    }
-    lo = warp_min(lo);
-    hi = warp_max(hi);
-    const float scale = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), qmax), 1e-8f);
-    if (lane == 0) {
-      v_lo[t] = lo;
-      v_sc[t] = scale;
-      c.v_scale[bh * c.cap + tok0 + t] = scale;
-      c.v_zero[bh * c.cap + tok0 + t] = lo;
+    for (int vg = 0; vg < VG; ++vg) {
+      float lo = INFINITY, hi = -INFINITY;
+      for (int cc = vg * c.v_group + lane; cc < (vg + 1) * c.v_group; cc += 32) {
+        const float x = load_as_float<T>(v_src, src0 + (int64_t)t * st + cc);
+        lo = fminf(lo, x);
+        hi = fmaxf(hi, x);
+      }
+      lo = warp_min(lo);
+      hi = warp_max(hi);
+      const float scale = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), qmax), 1e-8f);
+      if (lane == 0) {
+        v_lo[t * VG + vg] = lo;
+        v_sc[t * VG + vg] = scale;
+        c.v_scale[(bh * c.cap + tok0 + t) * VG + vg] = scale;
+        c.v_zero[(bh * c.cap + tok0 + t) * VG + vg] = lo;
+      }
     }
   }
   __syncthreads();
@@ -117,7 +122,7 @@ __global__ void kivi_append_kernel(const void* k_src, const void* v_src, int64_t
       for (int e = 0; e < per_byte; ++e) {
         const int t = tb + e;
         const float x = load_as_float<T>(v_src, src0 + (int64_t)t * st + d);
-        v |= (uint32_t)affine_code(x, v_lo[t], v_sc[t], qmax) << (e * bits);
+        v |= (uint32_t)affine_code(x, v_lo[t * VG + d / c.v_group], v_sc[t * VG + d / c.v_group], qmax) << (e * bits);
       }
       const int tok = tok0 + tb;
       uint8_t* row = c.v_codes + ((bh * (c.cap / 128) + tok / 128) * D + d) * (size_t)row_bytes;
@@ -146,7 +151,7 @@ __global__ void kivi_dequant_kernel(CachePtrs c, int n_comp, void* out_k, void* 
     const int tl = t & 127;
     const uint8_t vb = vrow[tl * bits >> 3];
     const float vq = (float)((vb >> ((tl * bits) & 7)) & mask);
-    const size_t vi = bh * c.cap + t;
+    const size_t vi = (bh * c.cap + t) * (D / c.v_group) + d / c.v_group;
     ov[(int64_t)t * ot + d] = from_float<T>(__fadd_rn(__fmul_rn(vq, c.v_scale[vi]), c.v_zero[vi]));
   }
 }
@@ -157,6 +162,7 @@ int check_cache(const CachePtrs& c) {
   PARE_REQUIRE(c.bits == 2 || c.bits == 4 || c.bits == 8, PARE_ERR_UNSUPPORTED);
   PARE_REQUIRE(c.group == 16 || c.group == 32 || c.group == 64 || c.group == 128, PARE_ERR_UNSUPPORTED);
   PARE_REQUIRE(c.cap % 128 == 0, PARE_ERR_SHAPE);
+  PARE_REQUIRE(c.v_group > 0 && c.v_group % 32 == 0 && c.D % c.v_group == 0, PARE_ERR_UNSUPPORTED);
   PARE_REQUIRE(c.k_codes && c.k_scale && c.k_zero && c.v_codes && c.v_scale && c.v_zero, PARE_ERR_SHAPE);
   return PARE_OK;
 }
@@ -170,15 +176,15 @@ extern "C" {
 
 int pare_kivi_append(const void* k_src, const void* v_src, int src_dtype, int64_t stride_b, int64_t stride_h,
                      int64_t stride_t, int n_tokens, int t0, uint8_t* k_codes, float* k_scale, float* k_zero,
-                     uint8_t* v_codes, float* v_scale, float* v_zero, int B, int H, int D, int bits, int group, int cap,
-                     void* stream) {
-  CachePtrs c{k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, B, H, D, bits, group, cap};
+                     uint8_t* v_codes, float* v_scale, float* v_zero, int B, int H, int D, int bits, int group, int v_group,
+                     int cap, void* stream) {
+  CachePtrs c{k_codes, k_scale, k_zero, v_codes, v_scale, v_zero, B, H, D, bits, group, cap, v_group > 0 ? v_group : D};
   const int rc = pare::check_cache(c);
   if (rc != PARE_OK) return rc;
   PARE_REQUIRE(k_src && v_src && n_tokens > 0, PARE_ERR_SHAPE);
   PARE_REQUIRE(n_tokens % group == 0 && t0 >= 0 && t0 % group == 0 && t0 + n_tokens <= cap, PARE_ERR_SHAPE);
   const dim3 grid(n_tokens / group, H, B);
-  const size_t smem = (size_t)group * D + 2 * group * sizeof(float);
+  const size_t smem = (size_t)group * D + 2 * group * (D / c.v_group) * sizeof(float);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (src_dtype) {
     case PARE_F16:
@@ -197,12 +203,12 @@ int pare_kivi_append(const void* k_src, const void* v_src, int src_dtype, int64_
 }
 
 int pare_kivi_dequant(const uint8_t* k_codes, const float* k_scale, const float* k_zero, const uint8_t* v_codes,
-                      const float* v_scale, const float* v_zero, int B, int H, int D, int bits, int group, int cap,
-                      int n_comp, void* out_k, void* out_v, int out_dtype, int64_t stride_b, int64_t stride_h,
+                      const float* v_scale, const float* v_zero, int B, int H, int D, int bits, int group, int v_group,
+                      int cap, int n_comp, void* out_k, void* out_v, int out_dtype, int64_t stride_b, int64_t stride_h,
                       int64_t stride_t, void* stream) {
   CachePtrs c{const_cast<uint8_t*>(k_codes), const_cast<float*>(k_scale), const_cast<float*>(k_zero),
               const_cast<uint8_t*>(v_codes), const_cast<float*>(v_scale), const_cast<float*>(v_zero),
-              B, H, D, bits, group, cap};
+              B, H, D, bits, group, cap, v_group > 0 ? v_group : D};
   const int rc = pare::check_cache(c);
   if (rc != PARE_OK) return rc;
   PARE_REQUIRE(out_k && out_v && n_comp >= 0 && n_comp <= cap && n_comp % group == 0, PARE_ERR_SHAPE);

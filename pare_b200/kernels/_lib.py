@@ -40,15 +40,15 @@ SIGNATURES: dict[str, tuple] = {
                                          _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                          _i, _i, _i, _i, _vp, _sz, _vp]),
     "pare_kivi_append": (_i, [_vp, _vp, _i, _i64, _i64, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp,
-                              _i, _i, _i, _i, _i, _i, _vp]),
-    "pare_kivi_dequant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
+                              _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "pare_kivi_dequant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
                                _vp, _vp, _i, _i64, _i64, _i64, _vp]),
     "pare_kivi_attn_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "pare_kivi_decode_attn": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i,
                                    _vp, _vp, _i64, _i64, _i64, _i,
                                    _vp, _vp, _i64, _i64, _vp,
                                    _vp, _i64, _i64, _vp, C.c_float,
-                                   _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+                                   _i, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "pare_kivi_attn_set_tuning": (None, [_i]),
     "pare_rmsnorm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, C.c_float, _i, _vp]),
     "pare_silu_mul": (_i, [_vp, _vp, _vp, _i, _i, _i64, _i, _vp]),

@@ -38,11 +38,13 @@ _V_BLOCK = 128  # tokens per block of the value-code layout
 
 @dataclass
 class KVCacheConfig:
-    """``bits`` per code (2, 4 or 8), tokens per key group, tokens kept in full precision."""
+    """``bits`` per code (2, 4 or 8), tokens per key group, tokens kept in full precision; ``v_group_size``: channels
+    that share a value scale / zero -- ``None`` = the whole head_dim (the reference), 32 = the KIVI paper's groups."""
 
     bits: int = 4
     group_size: int = 32
     residual_length: int = 128
+    v_group_size: int | None = None
 
 
 def rope_table(max_positions: int, head_dim: int, theta: float = 10000.0, device=None) -> Tensor:
@@ -93,6 +95,9 @@ class _LayerStore:
 
     def __init__(self, B: int, H: int, D: int, cfg: KVCacheConfig, cap: int, device, dtype) -> None:
         self.B, self.H, self.D, self.cfg, self.device, self.dtype = B, H, D, cfg, device, dtype
+        self.v_group = cfg.v_group_size or D          # channels per value scale / zero
+        if self.v_group % 32 or D % self.v_group:
+            raise ValueError("v_group_size must be a multiple of 32 that divides the head dimension")
         self.n_comp = 0
         self.r_len = 0
         self.r_cap = _roundup(cfg.residual_length + 2 * cfg.group_size, 8)
@@ -104,14 +109,15 @@ class _LayerStore:
     def _alloc(self, cap: int) -> None:
         cap = _roundup(max(cap, _V_BLOCK), math.lcm(_V_BLOCK, self.cfg.group_size))
         B, H, D, bits, G = self.B, self.H, self.D, self.cfg.bits, self.cfg.group_size
+        vg = D // self.v_group
         dev = self.device
         new = dict(
             k_codes=torch.empty(B, H, cap, D * bits // 8, dtype=torch.uint8, device=dev),
             k_scale=torch.empty(B, H, cap // G, D, dtype=torch.float32, device=dev),
             k_zero=torch.empty(B, H, cap // G, D, dtype=torch.float32, device=dev),
             v_codes=torch.empty(B, H, cap // _V_BLOCK, D, _V_BLOCK * bits // 8, dtype=torch.uint8, device=dev),
-            v_scale=torch.empty(B, H, cap, dtype=torch.float32, device=dev),
-            v_zero=torch.empty(B, H, cap, dtype=torch.float32, device=dev),
+            v_scale=torch.empty(B, H, cap, vg, dtype=torch.float32, device=dev),
+            v_zero=torch.empty(B, H, cap, vg, dtype=torch.float32, device=dev),
         )
         if self.cap:  # growing: carry the compressed tokens over
             n, nb = self.n_comp, _roundup(self.n_comp, _V_BLOCK) // _V_BLOCK
@@ -134,7 +140,7 @@ class _LayerStore:
                 self.v_codes.data_ptr(), self.v_scale.data_ptr(), self.v_zero.data_ptr())
 
     def geometry(self) -> tuple:
-        return (self.B, self.H, self.D, self.cfg.bits, self.cfg.group_size, self.cap)
+        return (self.B, self.H, self.D, self.cfg.bits, self.cfg.group_size, self.v_group, self.cap)
 
 
 class _CompressedKV:
@@ -175,11 +181,11 @@ class _CompressedKV:
 
     @property
     def v_scale(self) -> Tensor:
-        return self._s.v_scale[:, :, : self._s.n_comp].unsqueeze(-1)
+        return self._s.v_scale[:, :, : self._s.n_comp]   # [B, H, n, D / v_group]: [.., 1] in the reference's form
 
     @property
     def v_zero(self) -> Tensor:
-        return self._s.v_zero[:, :, : self._s.n_comp].unsqueeze(-1)
+        return self._s.v_zero[:, :, : self._s.n_comp]
 
     def __iter__(self):
         return iter((self.k_quant, self.k_scale, self.k_zero, self.v_quant, self.v_scale, self.v_zero))
@@ -343,7 +349,7 @@ class QuantizedKVCache:
             _lib.ptr(out), out.stride(0) if out is not None else 0, out.stride(1) if out is not None else 0,
             prepared_out.data_ptr() if prepared_out is not None else None,
             float(scale if scale is not None else 1.0 / math.sqrt(D)),
-            B, Hq, st.H, D, self.config.bits, self.config.group_size, st.cap,
+            B, Hq, st.H, D, self.config.bits, self.config.group_size, st.v_group, st.cap,
             ws.data_ptr(), ws.numel(), _lib.current_stream(st.device),
         )
         _lib.check(status, "pare_kivi_decode_attn")
@@ -367,7 +373,7 @@ class QuantizedKVCache:
         if st is None:
             return {"compressed": 0, "residual": 0, "total": 0}
         bh, n, G = st.B * st.H, st.n_comp, self.config.group_size
-        comp = bh * (2 * n * st.D * self.config.bits // 8 + 2 * (n // G) * st.D * 4 + 2 * n * 4)
+        comp = bh * (2 * n * st.D * self.config.bits // 8 + 2 * (n // G) * st.D * 4 + 2 * n * 4 * (st.D // st.v_group))
         res = 2 * bh * st.r_len * st.D * st.res_k.element_size()
         return {"compressed": comp, "residual": res, "total": comp + res}
 
@@ -377,13 +383,13 @@ class QuantizedKVCache:
 # (pare/kv_cache.py:75-156).  They run the same kernels as the cache.
 # ----------------------------------------------------------------------------------------
 
-def _quantize_block(k: Tensor, v: Tensor, bits: int, group_size: int) -> _CompressedKV:
+def _quantize_block(k: Tensor, v: Tensor, bits: int, group_size: int, v_group_size: int | None = None) -> _CompressedKV:
     if not k.is_cuda:
         raise RuntimeError("the KIVI primitives run on CUDA tensors only")
     B, H, n, D = k.shape
     if n % group_size:
         raise ValueError(f"n={n} must be divisible by group_size={group_size}")
-    st = _LayerStore(B, H, D, KVCacheConfig(bits, group_size, 0), n, k.device, k.dtype)
+    st = _LayerStore(B, H, D, KVCacheConfig(bits, group_size, 0, v_group_size), n, k.device, k.dtype)
     k, v = k.contiguous(), v.contiguous()
     status = _lib.lib().pare_kivi_append(
         k.data_ptr(), v.data_ptr(), _lib.dtype_code(k.dtype), k.stride(0), k.stride(1), k.stride(2),
@@ -398,8 +404,8 @@ def _quantize_keys(k: Tensor, bits: int, group_size: int) -> tuple[Tensor, Tenso
     return c.k_quant, c.k_scale, c.k_zero
 
 
-def _quantize_values(v: Tensor, bits: int, group_size: int) -> tuple[Tensor, Tensor, Tensor]:
-    c = _quantize_block(v, v, bits, group_size)
+def _quantize_values(v: Tensor, bits: int, group_size: int, v_group_size: int | None = None) -> tuple[Tensor, Tensor, Tensor]:
+    c = _quantize_block(v, v, bits, group_size, v_group_size)
     return c.v_quant, c.v_scale, c.v_zero
 
 
@@ -412,4 +418,8 @@ def _dequantize_keys(k_quant: Tensor, k_scale: Tensor, k_zero: Tensor, group_siz
 
 
 def _dequantize_values(v_quant: Tensor, v_scale: Tensor, v_zero: Tensor) -> Tensor:
+    if v_scale.shape[-1] > 1:   # one pair per group of channels
+        B, H, n, D = v_quant.shape
+        q = v_quant.float().reshape(B, H, n, v_scale.shape[-1], -1)
+        return (q * v_scale.unsqueeze(-1) + v_zero.unsqueeze(-1)).reshape(B, H, n, D)
     return v_quant.float() * v_scale + v_zero

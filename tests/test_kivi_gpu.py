@@ -222,6 +222,15 @@ def test_decode_attention_two_bit_cache(bsz, hkv, hq, ctx, group, dtype, cuda_li
     _check_attn(out.float().cpu().numpy(), ref, ref32, dtype)
 
 
+@pytest.mark.parametrize("bits", [4, 2])
+def test_decode_attention_longest_benchmark_context(bits, cuda_lib):
+    """The longest context of the benchmark grid (32768 tokens, 28 query / 4 KV heads, 128 compressed-token splits per
+    head) against the oracle, same bars."""
+    out, ref, cache, ref32 = _attn_case(1, 4, 28, 32768, torch.float16, bits=bits, seed=11)
+    assert cache._stores[0].n_comp >= 32768 - 128 - 32
+    _check_attn(out.float().cpu().numpy(), ref, ref32, torch.float16)
+
+
 def _check_attn(o, ref, ref32, dtype):
     """Two bars.  (1) Tight, against fp32 attention over the reference's reconstruction BEFORE its final
     cast (``_reconstruct``, pare/kv_cache.py:315-325): max <= 1e-2, mean <= 1e-3 (2.5e-3 for bf16
@@ -322,3 +331,69 @@ def test_rope_argument_checks(cuda_lib):
         cache.attend(0, q, k[:, :, :2], v[:, :, :2], rope=table[1])      # two new tokens
     with pytest.raises(ValueError):
         cache.attend(0, q, k[:, :, :1], v[:, :, :1], rope=table[1].half())
+
+
+# ---- values quantized in 32-channel groups -------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_value_channel_groups_bit_exact_vs_oracle(bits, dtype, cuda_lib):
+    """One (scale, zero) per token and 32 channels: codes, scales, zeros bit-exact against the oracle's
+    ``quantize_values`` on the channel axis viewed as [D/32][32]; ``v_group_size = D`` is the reference's form."""
+    _, v = _kv(128, seed=bits, b=2, h=3, dtype=dtype)
+    vq, vs, vz = _quantize_values(v, bits, 32, v_group_size=32)
+    assert vq.shape == (2, 3, 128, D) and vs.shape == (2, 3, 128, D // 32) and vz.shape == vs.shape
+    for got, ref in zip((vq, vs, vz), ok.quantize_values(v.float().cpu().numpy(), bits, 32, 32)):
+        assert np.array_equal(got.cpu().numpy(), ref)
+    rec = _dequantize_values(vq, vs, vz)
+    assert np.array_equal(rec.cpu().numpy(), ok.dequantize_values(vq.cpu().numpy(), vs.cpu().numpy(), vz.cpu().numpy()))
+    whole = _quantize_values(v, bits, 32)
+    same = _quantize_values(v, bits, 32, v_group_size=D)
+    for a, b in zip(whole, same):
+        assert torch.equal(a, b)
+    err_g = ((rec - v.float()) ** 2).mean().item()
+    err_w = ((_dequantize_values(*whole) - v.float()) ** 2).mean().item()
+    assert err_g <= err_w                                   # finer groups never reconstruct worse
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits", [4, 2])
+@pytest.mark.parametrize("bsz,hkv,hq,ctx", [(1, 4, 28, 1000), (2, 2, 16, 4096), (1, 1, 8, 160)])
+def test_value_channel_groups_cache_and_attention(bsz, hkv, hq, ctx, bits, dtype, cuda_lib):
+    """The cache with 32-channel value groups: ``update()`` bit-exact against the oracle state machine, fused
+    attention within the usual bars of fp32 attention over the oracle's reconstruction."""
+    g = torch.Generator().manual_seed(ctx + bits)
+    k = torch.randn(bsz, hkv, ctx, D, generator=g)
+    v = torch.randn(bsz, hkv, ctx, D, generator=g)
+    v[..., 40:44] *= 6.0                                    # a few loud value channels: where the finer groups matter
+    k[..., 9] *= 10.0
+    q = torch.randn(bsz, hq, 1, D, generator=g)
+    k, v, q = k.to(dtype).cuda(), v.to(dtype).cuda(), q.to(dtype).cuda()
+    cache = QuantizedKVCache(1, KVCacheConfig(bits=bits, group_size=32, residual_length=128, v_group_size=32), max_seq_len=ctx + 256)
+    fk, fv = cache.update(0, k[:, :, :-1], v[:, :, :-1])
+    ref_cache = ok.Cache(bits, 32, 128, v_group=32)
+    rk, rv = ref_cache.update(k[:, :, :-1].float().cpu().numpy(), v[:, :, :-1].float().cpu().numpy())
+    cast = (lambda a: torch.from_numpy(a).to(dtype).float().numpy())
+    assert np.array_equal(fk.float().cpu().numpy(), cast(rk)) and np.array_equal(fv.float().cpu().numpy(), cast(rv))
+    out = cache.attend(0, q, k[:, :, -1:], v[:, :, -1:])
+    rk, rv = ref_cache.update(k[:, :, -1:].float().cpu().numpy(), v[:, :, -1:].float().cpu().numpy())
+    qf = q.float().cpu().numpy()
+    _check_attn(out.float().cpu().numpy(), ok.decode_attention(qf, cast(rk), cast(rv)), ok.decode_attention(qf, rk, rv), dtype)
+    assert torch.equal(out, cache.attend(0, q, k[:, :, :0], v[:, :, :0]))     # deterministic
+    m = cache.memory_bytes(0)
+    n = cache._stores[0].n_comp
+    assert m["compressed"] == bsz * hkv * (2 * n * D * bits // 8 + 2 * (n // 32) * D * 4 + 2 * n * 4 * 4)
+
+
+def test_value_channel_group_argument_checks(cuda_lib):
+    from pare_b200.kernels import _lib
+    k, v = _kv(8, b=1, h=2)
+    with pytest.raises(ValueError):
+        QuantizedKVCache(1, KVCacheConfig(v_group_size=48)).update(0, k, v)
+    cache = QuantizedKVCache(1, KVCacheConfig(bits=4, group_size=32, residual_length=0, v_group_size=64), max_seq_len=256)
+    k, v = _kv(64, b=1, h=2)
+    fk, fv = cache.update(0, k, v)                          # the cache itself takes any multiple of 32
+    assert fv.shape == v.shape
+    q = torch.randn(1, 4, 1, D).half().cuda()
+    with pytest.raises(_lib.KernelLibraryError):            # the fused attention only 32 or the whole head
+        cache.attend(0, q, k[:, :, :0], v[:, :, :0])

@@ -66,3 +66,24 @@ def test_kivi_dequant_roundtrip_error_bound():
     q, s, z = kivi.quantize_keys(k, 4, 32)
     rec = kivi.dequantize_keys(q, s, z, 32)
     assert np.abs(rec - k).max() <= 0.5 * s.max() * (1 + 1e-5)
+
+
+def test_value_channel_groups_restatement():
+    """``quantize_values(.., v_group)`` is the reference's per-token function on the channel axis viewed as
+    [D/v_group][v_group]: each group's codes / scale / zero equal the whole-row function applied to that slice."""
+    import numpy as np
+    from oracle import kivi as ok
+    rng = np.random.default_rng(3)
+    v = rng.standard_normal((2, 3, 64, 128)).astype(np.float32)
+    for bits in (2, 4, 8):
+        q, s, z = ok.quantize_values(v, bits, 32, 32)
+        assert q.shape == v.shape and s.shape == (2, 3, 64, 4) and z.shape == s.shape
+        for g in range(4):
+            qg, sg, zg = ok.quantize_values(v[..., g * 32:(g + 1) * 32], bits, 32)
+            assert np.array_equal(q[..., g * 32:(g + 1) * 32], qg)
+            assert np.array_equal(s[..., g:g + 1], sg) and np.array_equal(z[..., g:g + 1], zg)
+        whole = ok.quantize_values(v, bits, 32)
+        for a, b in zip(whole, ok.quantize_values(v, bits, 32, 128)):
+            assert np.array_equal(a, b)
+        rec = ok.dequantize_values(q, s, z)
+        assert np.abs(rec - v).max() <= np.abs(ok.dequantize_values(*whole) - v).max() + 1e-6
