@@ -212,6 +212,20 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
                           int B, int Hq, int H, int D, int bits, int group, int v_group, int cap,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* Attention of Tq new tokens over Tk >= Tq full-precision keys / values (the new tokens are the last Tq of them):
+ *   out[b][hq][i] = softmax_j(q[b][hq][i] . k[b][hq / (Hq/H)][j] * softmax_scale) . v[b][hq / (Hq/H)][j],
+ * with causal != 0 over the keys j <= i + (Tk - Tq) only.  This is the prompt's attention BEFORE the cache
+ * compresses the tokens: the reference's caller runs scaled_dot_product_attention on update()'s return
+ * (pare/kv_cache.py:183-186, 205-252), which for a prompt is mostly the lossy reconstruction.
+ *   q, out [B][Hq][Tq][D], k, v [B][H][Tk][D]; dtype F16/BF16; element strides per tensor (multiples of 8),
+ *   channels contiguous, 16-byte aligned; D == 128.  No workspace. */
+int pare_prefill_attn(const void* q, const void* k, const void* v, void* out, int dtype,
+                      int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
+                      int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
+                      int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t,
+                      int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t,
+                      int B, int Hq, int H, int Tq, int Tk, int D, float softmax_scale, int causal, void* stream);
+
 /* Tuning override for experiments: compressed tokens per CTA (multiple of 128, <= 512); 0 = auto. */
 void pare_kivi_attn_set_tuning(int chunk);
 

@@ -153,3 +153,27 @@ def apply_rope(x: np.ndarray, rows: np.ndarray) -> np.ndarray:
     cos, sin = rows[..., :half].astype(_F), rows[..., half:].astype(_F)
     a, b = x[..., :half], x[..., half:]
     return np.concatenate([a * cos - b * sin, b * cos + a * sin], axis=-1).astype(_F)
+
+
+def causal_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float | None = None, causal: bool = True) -> np.ndarray:
+    """``softmax(q k^T * scale) v`` in fp32 for ``q [B,Hq,Tq,D]`` over ``k/v [B,Hkv,Tk,D]``, ``Tk >= Tq``: the queries are
+    the last ``Tq`` tokens, query i sees keys ``j <= i + (Tk - Tq)`` -- what ``scaled_dot_product_attention(...,
+    is_causal=True)`` gives a caller of the reference for a prompt (pare/kv_cache.py:183-186), with the grouped-query
+    ``repeat_interleave`` folded in."""
+    q = np.asarray(q, dtype=_F)
+    k = np.asarray(k, dtype=_F)
+    v = np.asarray(v, dtype=_F)
+    b, hq, tq, d = q.shape
+    tk = k.shape[2]
+    rep = hq // k.shape[1]
+    scale = _F(1.0 / np.sqrt(d)) if scale is None else _F(scale)
+    out = np.empty_like(q)
+    visible = (np.arange(tk)[None, :] <= np.arange(tq)[:, None] + (tk - tq)) if causal else np.ones((tq, tk), dtype=bool)
+    for h in range(hq):
+        s = np.einsum("bqd,btd->bqt", q[:, h], k[:, h // rep]) * scale
+        s = np.where(visible[None], s, -np.inf)
+        s = s - s.max(axis=-1, keepdims=True)
+        p = np.exp(s)
+        p = p / p.sum(axis=-1, keepdims=True)
+        out[:, h] = np.einsum("bqt,btd->bqd", p, v[:, h // rep])
+    return out.astype(_F)

@@ -50,6 +50,8 @@ SIGNATURES: dict[str, tuple] = {
                                    _vp, _i64, _i64, _vp, C.c_float,
                                    _i, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "pare_kivi_attn_set_tuning": (None, [_i]),
+    "pare_prefill_attn": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                               _i, _i, _i, _i, _i, _i, C.c_float, _i, _vp]),
     "pare_rmsnorm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, C.c_float, _i, _vp]),
     "pare_silu_mul": (_i, [_vp, _vp, _vp, _i, _i, _i64, _i, _vp]),
     "pare_peer_buffer_create": (_i, [_sz, C.POINTER(C.c_void_p), C.c_char_p]),

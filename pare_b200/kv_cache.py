@@ -67,6 +67,34 @@ def apply_rope(x: Tensor, rows: Tensor) -> Tensor:
     return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1).to(x.dtype)
 
 
+def prefill_attention(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None, causal: bool = True) -> Tensor:
+    """``softmax(q k^T * scale) v`` for ``q [B, Hq, Tq, D]`` over full-precision ``k, v [B, H, Tk, D]`` (``Tk >= Tq``; the
+    queries are the last ``Tq`` tokens; grouped-query sharing; causal by default), float16 / bfloat16, ``D = 128``:
+    the attention of a prompt before the cache compresses it.  Returns a tensor shaped like ``q``."""
+    if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("prefill_attention needs q, k, v in the same 16-bit float dtype")
+    if not q.is_cuda:
+        raise RuntimeError("prefill_attention runs on CUDA tensors only")
+    if q.dim() != 4 or k.dim() != 4 or k.shape != v.shape or k.shape[0] != q.shape[0] or k.shape[3] != q.shape[3]:
+        raise ValueError("q [B, Hq, Tq, D], k / v [B, H, Tk, D]")
+
+    def usable(t: Tensor) -> Tensor:
+        ok = t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
+        return t if ok else t.contiguous()
+
+    q, k, v = usable(q), usable(k), usable(v)
+    B, Hq, Tq, D = q.shape
+    H, Tk = k.shape[1], k.shape[2]
+    out = torch.empty(B, Hq, Tq, D, device=q.device, dtype=q.dtype)
+    status = _lib.lib().pare_prefill_attn(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _lib.dtype_code(q.dtype),
+        q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2),
+        out.stride(0), out.stride(1), out.stride(2), B, Hq, H, Tq, Tk, D,
+        float(scale if scale is not None else 1.0 / math.sqrt(D)), 1 if causal else 0, _lib.current_stream(q.device))
+    _lib.check(status, "pare_prefill_attn")
+    return out
+
+
 def plan_update(r_len: int, n_new: int, residual_length: int, group_size: int) -> tuple[int, int]:
     """Compression schedule of one ``update`` (reference: ``pare/kv_cache.py:231-244``).
 
@@ -354,6 +382,25 @@ class QuantizedKVCache:
         )
         _lib.check(status, "pare_kivi_decode_attn")
         return None if out is None else out.reshape(q.shape)
+
+    def prefill(self, layer_idx: int, q: Tensor, new_k: Tensor, new_v: Tensor, scale: float | None = None,
+                rope: Tensor | None = None) -> Tensor:
+        """Causal attention of a prompt's ``q [B, Hq, T, D]`` over its own ``new_k, new_v [B, H, T, D]`` in full precision,
+        then the append of those tokens (whole groups beyond the window are compressed).  On a cache that already
+        holds tokens the older ones come from :meth:`update`'s dense return, as a caller of the reference would attend
+        to them.  ``rope``: rows ``[T, D]`` of a :func:`rope_table` for the new tokens' positions, applied to ``q`` and
+        ``new_k`` first (the keys are stored rotated)."""
+        if rope is not None:
+            q, new_k = apply_rope(q, rope), apply_rope(new_k, rope)
+        if self.seq_len(layer_idx) == 0:
+            out = prefill_attention(q, new_k, new_v, scale, causal=True)
+            self._append(layer_idx, new_k, new_v)
+            return out
+        full_k, full_v = self.update(layer_idx, new_k, new_v)
+        n_new = new_k.shape[2]
+        full_k[:, :, -n_new:] = new_k          # the new tokens themselves at full precision
+        full_v[:, :, -n_new:] = new_v
+        return prefill_attention(q, full_k, full_v, scale, causal=True)
 
     def reset(self, layer_idx: int | None = None) -> None:
         """Forget one layer or all layers (buffers are released and reallocated on next use)."""

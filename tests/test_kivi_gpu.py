@@ -397,3 +397,83 @@ def test_value_channel_group_argument_checks(cuda_lib):
     q = torch.randn(1, 4, 1, D).half().cuda()
     with pytest.raises(_lib.KernelLibraryError):            # the fused attention only 32 or the whole head
         cache.attend(0, q, k[:, :, :0], v[:, :, :0])
+
+
+# ---- prefill attention over full-precision K / V ---------------------------------------------------
+
+def _bars_prefill(o, ref, dtype):
+    mx, mean = rel_err(o, ref)
+    assert mx <= 1e-2 and mean <= (2.5e-3 if dtype == torch.bfloat16 else 1e-3), (mx, mean)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bsz,hkv,hq,tq,tk,causal", [(1, 2, 8, 256, 256, True), (2, 1, 4, 100, 100, True), (1, 4, 28, 333, 333, True),
+                                                      (1, 2, 4, 64, 200, True), (1, 1, 2, 1, 130, True), (2, 2, 2, 70, 70, False),
+                                                      (1, 1, 1, 17, 17, True)])
+def test_prefill_attention_matches_oracle(bsz, hkv, hq, tq, tk, causal, dtype, cuda_lib):
+    """fp32 attention of the oracle on the same 16-bit inputs: max rel err <= 1e-2, mean <= 1e-3 (2.5e-3 for bf16
+    outputs); ragged lengths, grouped-query sharing, queries that are the tail of a longer key sequence, and the
+    first rows of a causal prompt (one or two visible keys) among the cases."""
+    from pare_b200.kv_cache import prefill_attention
+    g = torch.Generator().manual_seed(tq * 7 + tk)
+    q = torch.randn(bsz, hq, tq, D, generator=g).to(dtype).cuda()
+    k = torch.randn(bsz, hkv, tk, D, generator=g).to(dtype).cuda()
+    v = torch.randn(bsz, hkv, tk, D, generator=g).to(dtype).cuda()
+    out = prefill_attention(q, k, v, causal=causal)
+    assert out.shape == q.shape and out.dtype == dtype
+    ref = ok.causal_attention(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), causal=causal)
+    _bars_prefill(out.float().cpu().numpy(), ref, dtype)
+    assert torch.equal(out, prefill_attention(q, k, v, causal=causal))          # deterministic
+    # strided views (a fused q|k|v projection output) give the same bits
+    qkv = torch.randn(bsz, max(tq, tk), (hq + 2 * hkv) * D, generator=g).to(dtype).cuda()
+    q2 = qkv[:, :tq, : hq * D].unflatten(2, (hq, D)).transpose(1, 2)
+    k2 = qkv[:, :tk, hq * D:(hq + hkv) * D].unflatten(2, (hkv, D)).transpose(1, 2)
+    v2 = qkv[:, :tk, (hq + hkv) * D:].unflatten(2, (hkv, D)).transpose(1, 2)
+    assert torch.equal(prefill_attention(q2, k2, v2, causal=causal),
+                       prefill_attention(q2.contiguous(), k2.contiguous(), v2.contiguous(), causal=causal))
+
+
+def test_prefill_attention_long_prompt(cuda_lib):
+    """2048-token prompt (32 query tiles per head, 32 key tiles for the last of them): same bars."""
+    from pare_b200.kv_cache import prefill_attention
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(1, 8, 2048, D, generator=g).half().cuda()
+    k = torch.randn(1, 2, 2048, D, generator=g).half().cuda()
+    v = torch.randn(1, 2, 2048, D, generator=g).half().cuda()
+    out = prefill_attention(q, k, v)
+    ref = ok.causal_attention(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy())
+    _bars_prefill(out.float().cpu().numpy(), ref, torch.float16)
+
+
+def test_cache_prefill_then_decode(cuda_lib):
+    """``prefill()`` = full-precision causal attention of the prompt + append; the decode step that follows sees the
+    same cache as after ``update()``; a second chunk attends to the older tokens through the cache's reconstruction."""
+    from pare_b200.kv_cache import apply_rope, rope_table
+    g = torch.Generator().manual_seed(9)
+    T = 300
+    q = torch.randn(1, 8, T, D, generator=g).half().cuda()
+    k = torch.randn(1, 2, T, D, generator=g).half().cuda()
+    v = torch.randn(1, 2, T, D, generator=g).half().cuda()
+    table = rope_table(T + 80, D, 500000.0, device="cuda")
+    cfg = KVCacheConfig(bits=4, group_size=32, residual_length=128)
+    a, b = QuantizedKVCache(1, cfg, max_seq_len=1024), QuantizedKVCache(1, cfg, max_seq_len=1024)
+    out = a.prefill(0, q, k, v, rope=table[:T])
+    kr, qr = apply_rope(k, table[:T]), apply_rope(q, table[:T])
+    ref = ok.causal_attention(qr.float().cpu().numpy(), kr.float().cpu().numpy(), v.float().cpu().numpy())
+    _bars_prefill(out.float().cpu().numpy(), ref, torch.float16)
+    b.update(0, kr, v)
+    assert a.seq_len(0) == b.seq_len(0) == T and a._stores[0].n_comp == b._stores[0].n_comp
+    q1 = torch.randn(1, 8, 1, D, generator=g).half().cuda()
+    k1 = torch.randn(1, 2, 1, D, generator=g).half().cuda()
+    v1 = torch.randn(1, 2, 1, D, generator=g).half().cuda()
+    assert torch.equal(a.attend(0, q1, k1, v1, rope=table[T]), b.attend(0, q1, k1, v1, rope=table[T]))
+    # second chunk of 64 tokens on the non-empty cache
+    q2 = torch.randn(1, 8, 64, D, generator=g).half().cuda()
+    k2 = torch.randn(1, 2, 64, D, generator=g).half().cuda()
+    v2 = torch.randn(1, 2, 64, D, generator=g).half().cuda()
+    fk, fv = b.update(0, k2, v2)
+    fk[:, :, -64:], fv[:, :, -64:] = k2, v2
+    ref2 = ok.causal_attention(q2.float().cpu().numpy(), fk.float().cpu().numpy(), fv.float().cpu().numpy())
+    out2 = a.prefill(0, q2, k2, v2)
+    _bars_prefill(out2.float().cpu().numpy(), ref2, torch.float16)
+    assert a.seq_len(0) == b.seq_len(0) == T + 1 + 64
