@@ -320,6 +320,25 @@ def prefill_table(stack, batches=(64, 256)) -> dict:
     return table
 
 
+def prefill_attention_table(dtype, device, lengths=(2048, 8192)) -> dict:
+    """Causal prefill attention over full-precision K / V (32 query / 8 KV heads, D = 128, batch 1): ms per call,
+    TFLOP/s by the 2 T^2 D Hq flops of the causal half, and the fraction of the measured dense bf16 peak (a
+    warp-level mma.sync kernel: the tensor-core generation before tcgen05, so the fraction is modest by construction)."""
+    from pare_b200.kv_cache import prefill_attention
+
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tf_peak = float(peaks.get("bf16_tflops", 1590.0))
+    table = {}
+    for t in lengths:
+        q = torch.randn(1, 32, t, 128, device=device).to(dtype)
+        k = torch.randn(1, 8, t, 128, device=device).to(dtype)
+        v = torch.randn(1, 8, t, 128, device=device).to(dtype)
+        sec = time_events(lambda: prefill_attention(q, k, v), 10, 3, 1) / 10
+        tf = 2.0 * t * t * 128 * 32 / sec / 1e12
+        table[f"t{t}"] = {"ms": round(sec * 1e3, 3), "tflops": round(tf, 1), "frac_tensor": round(tf / tf_peak, 4)}
+    return table
+
+
 def attention_table(dtype, device, peak: float,
                     cases=((1, 4096, 32, 4), (16, 4096, 8, 4), (16, 4096, 8, 2), (16, 4096, 8, 4, 32))) -> dict:
     """Fused KIVI decode attention alone (8 KV heads, 32 query heads, D = 128, g32, residual window 128):
@@ -425,6 +444,7 @@ def run_ours(args) -> None:
         line["layers"] = table
         line["attention"] = {} if args.skip_layer_table else attention_table(dtype, stack.device, peak)
         line["prefill_layers"] = {} if args.skip_layer_table else prefill_table(stack)
+        line["prefill_attention"] = {} if args.skip_layer_table else prefill_attention_table(dtype, stack.device)
         key = f"gate_up_{blk.gate_up.out_features}x{blk.gate_up.in_features}_m{args.batch}"
         if key in table:
             achieved = table[key]["gbs"]

@@ -151,6 +151,32 @@ class DecodeStack(nn.Module):
             self.cache.reset(layer)
             self.cache._append(layer, k.to(self.dtype), v.to(self.dtype))
 
+    # ---- the prompt -----------------------------------------------------------------------
+    @torch.no_grad()
+    def prefill(self, x: Tensor) -> Tensor:
+        """``x [B, T, hidden]``: hidden states of a prompt's tokens -> same shape, and the caches hold the prompt.
+
+        Per block: RMSNorm, q|k|v linear (``B T`` rows: the tensor-core path for long prompts), rotary embedding, causal
+        attention over the full-precision keys / values of the prompt (``QuantizedKVCache.prefill``, which then
+        compresses what lies beyond the window), o linear, RMSNorm, gate|up linear, SwiGLU, down linear.  A later
+        call continues the sequence (chunked prefill)."""
+        B, T, hidden = x.shape
+        pos0 = self.cache.seq_len(0)
+        rope = self.rope[pos0:pos0 + T] if self.rope is not None else None
+        resid = x.reshape(B * T, hidden).clone()
+        delta = None
+        for i, blk in enumerate(self.blocks):
+            d, hq, hkv = blk.d, blk.hq, blk.hkv
+            qkv = blk.qkv(self._rmsnorm(resid, delta, blk.norm1, store_residual=delta is not None)).view(B, T, -1)
+            q = qkv[..., : hq * d].unflatten(2, (hq, d)).transpose(1, 2)                    # [B, hq, T, d] views
+            k = qkv[..., hq * d:(hq + hkv) * d].unflatten(2, (hkv, d)).transpose(1, 2)
+            v = qkv[..., (hq + hkv) * d:].unflatten(2, (hkv, d)).transpose(1, 2)
+            attn = self.cache.prefill(i, q, k, v, scale=1.0 / math.sqrt(d), rope=rope)      # [B, hq, T, d]
+            o = self._all_reduce(blk.o(attn.transpose(1, 2).reshape(B * T, hq * d)))
+            h2 = self._rmsnorm(resid, o, blk.norm2, store_residual=True)
+            delta = self._all_reduce(blk.down(self._silu_mul(blk.gate_up(h2), blk.ffn)))
+        return (resid + delta).view(B, T, hidden)
+
     # ---- one decode step ---------------------------------------------------------------
     @torch.no_grad()
     def forward(self, x: Tensor) -> Tensor:
@@ -162,7 +188,7 @@ class DecodeStack(nn.Module):
         linear (applies the SwiGLU gate itself).  Larger M takes plain tensors and stand-alone glue kernels.
         """
         m = x.shape[0]
-        resid = x.clone()
+        resid = x.clone(memory_format=torch.contiguous_format)   # a one-row slice of a larger tensor keeps its odd row stride otherwise
         delta = None
         blk0 = self.blocks[0]
         fused = all(l.supports_prepared(m) for l in (blk0.qkv, blk0.o, blk0.gate_up, blk0.down))

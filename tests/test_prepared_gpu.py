@@ -229,3 +229,29 @@ def test_produced_rejects_aliasing_and_odd_shapes(cuda_lib):
     with pytest.raises(AssertionError):              # the stream must not be normalised in place
         w4a16_forward_produced(_lib.PRODUCER_RMSNORM, x, packed, scale, zero, 128, norm_weight=torch.ones(1024, device="cuda").half(),
                                resid_out=x)
+
+
+def test_decode_stack_prefill_equals_token_by_token(cuda_lib):
+    """A 72-token prompt (shorter than the residual window, so nothing is compressed and both routes see the same
+    keys) through ``prefill()`` -- tensor-core linears, prefill attention -- against the same tokens fed one decode step
+    at a time: hidden states within the kernels' tolerance, and the decode step that follows agrees too."""
+    shape = (1024, 2048, 8, 2, 128, 2)
+    T = 72
+    x = torch.randn(1, T, 1024, generator=torch.Generator().manual_seed(11)).half().cuda()
+    a = DecodeStack(shape, dtype=torch.float16, max_seq_len=512, seed=3)
+    b = DecodeStack(shape, dtype=torch.float16, max_seq_len=512, seed=3)
+    ya = a.prefill(x)
+    yb = torch.cat([b(x[:, t]) for t in range(T)], dim=0).view(1, T, 1024)
+    assert a.cache.seq_len(0) == b.cache.seq_len(1) == T
+    mx, mean = ow.rel_err(ya.float().cpu().numpy(), yb.float().cpu().numpy())
+    assert mx <= 3e-2 and mean <= 3e-3, (mx, mean)           # two blocks of 16-bit round trips on either route
+    ka, kb = a.cache._residual_k[1].float(), b.cache._residual_k[1].float()
+    assert torch.allclose(ka, kb, rtol=2e-2, atol=2e-2)
+    nxt = torch.randn(1, 1024, generator=torch.Generator().manual_seed(12)).half().cuda()
+    mx, mean = ow.rel_err(a(nxt).float().cpu().numpy(), b(nxt).float().cpu().numpy())
+    assert mx <= 3e-2 and mean <= 3e-3, (mx, mean)
+    # chunked prefill continues the sequence
+    c = DecodeStack(shape, dtype=torch.float16, max_seq_len=512, seed=3)
+    yc = torch.cat([c.prefill(x[:, :40]), c.prefill(x[:, 40:])], dim=1)
+    mx, mean = ow.rel_err(yc.float().cpu().numpy(), ya.float().cpu().numpy())
+    assert mx <= 3e-2 and mean <= 3e-3, (mx, mean)
