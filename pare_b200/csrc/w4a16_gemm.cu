@@ -8,8 +8,9 @@
 //
 // One CTA = 128 output rows x one tile of up to 128 activation rows x one K range.  Warp roles:
 //   warps 0-7  dequantize (two threads per weight row), then run the epilogue
-//   warp 8     producer: packed codes by row-contiguous bulk copies (cp.async.bulk, 256 B per row
-//              and stage) into a ring; activation tiles by TMA (cp.async.bulk.tensor.2d, 128B swizzle)
+//   warp 8     producer, two lanes: packed codes by TMA (cp.async.bulk.tensor.2d over the [N][K/2] byte matrix,
+//              two 128-row x 128-byte boxes per 512-column stage, 128B swizzle) into a two-stage ring, requested a
+//              whole stage ahead; activation tiles by TMA (128B swizzle) four blocks ahead of the MMA
 //   warp 9     one elected thread issues tcgen05.mma (UMMA 128 x MT x 16, fp32 accumulate in TMEM)
 // Per 64-column block a dequantizing thread reads 16 bytes of codes, turns them into exact
 // integers in the 16-bit float type by the mantissa trick of common.cuh, multiplies by the group
@@ -30,7 +31,7 @@ namespace {
 constexpr int kRows = 128;             // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 64;            // columns per MMA stage: 128 bytes of 16-bit elements = one swizzle row
 constexpr int kRawK = 512;             // columns per raw (packed) stage
-constexpr int kRawPitch = kRawK / 2 + 16;   // bytes; +16 keeps the 16-byte reads of 8 rows in distinct banks
+constexpr int kRawHalf = kRows * 128;  // bytes of half a raw stage: 128 rows x 128 bytes (256 columns), 128B swizzle
 constexpr int kRawStages = 2;
 constexpr int kStages = 4;             // operand ring depth
 constexpr int kDequantThreads = 256;
@@ -84,11 +85,6 @@ __device__ __forceinline__ void bar_wait(uint32_t bar, uint32_t parity, int* sta
     if (bar_test(bar, parity)) return;
   dead = true;
   if (status) atomicExch(status, PARE_ERR_TIMEOUT);
-}
-__device__ __forceinline__ void bulk_row(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
 }
 __device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
@@ -201,13 +197,14 @@ __device__ __forceinline__ uint4 dequant_word<__nv_bfloat16>(uint32_t w, float z
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
+__global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                                                                 const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* a_ring = smem;                                   // kStages x 16 KB
   unsigned char* b_ring = a_ring + kStages * 16384;               // kStages x 16 KB (mt <= 128 rows x 128 B)
-  unsigned char* raw = b_ring + kStages * 16384;                  // kRawStages x 128 x kRawPitch
-  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + kRawStages * kRows * kRawPitch);
+  unsigned char* raw = b_ring + kStages * 16384;                  // kRawStages x 2 halves x 16 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + kRawStages * 2 * kRawHalf);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
   const uint32_t raw_full = s_u32(bars), raw_empty = s_u32(bars + 2), a_full = s_u32(bars + 4), b_full = s_u32(bars + 8),
                  ab_empty = s_u32(bars + 12), acc_full = s_u32(bars + 16);
@@ -246,32 +243,27 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
 
   if (warp == 8) {
     // ================= producer =================
-    const int nraw = nkb / 8;
-    int rs = 0;  // raw stages issued
-    for (int kb = 0; kb < nkb; ++kb) {
-      if ((kb & 7) == 0) {  // a new raw stage: 128 rows x 256 bytes, four rows per lane
+    // Two independent lanes: lane 1 keeps the raw ring full (a stage is requested as soon as its slot is free, a
+    // whole stage before the dequantizing threads reach it), lane 0 feeds the activation ring four blocks ahead
+    // of the MMA.  A raw stage is two tensor-map copies of 128 rows x 128 bytes.
+    if (lane == 1) {
+      for (int rs = 0; rs < nkb / 8; ++rs) {
         const int slot = rs % kRawStages;
         bar_wait(raw_empty + slot * 8, ((rs / kRawStages) & 1) ^ 1, status, dead);
-        if (lane == 0) bar_expect(raw_full + slot * 8, kRows * (kRawK / 2));
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int r = lane * 4 + j;
-          const int gr = min(row0 + r, p.N - 1);
-          bulk_row(s_u32(raw) + (slot * kRows + r) * kRawPitch,
-                   p.packed + (size_t)gr * (p.K >> 1) + (size_t)(kb0 + kb) * (kBlockK / 2), kRawK / 2, raw_full + slot * 8);
-        }
-        ++rs;
+        bar_expect(raw_full + slot * 8, 2 * kRawHalf);
+        const int xb = (kb0 + rs * 8) * (kBlockK / 2);   // byte column of the stage
+        tma_tile(s_u32(raw) + (slot * 2) * kRawHalf, &tm_w, xb, row0, raw_full + slot * 8);
+        tma_tile(s_u32(raw) + (slot * 2 + 1) * kRawHalf, &tm_w, xb + 128, row0, raw_full + slot * 8);
       }
-      if (lane == 0) {  // activation tile of this block
+    } else if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {  // activation tile of each block
         const int s = kb % kStages;
         bar_wait(ab_empty + s * 8, ((kb / kStages) & 1) ^ 1, status, dead);
         bar_expect(b_full + s * 8, p.mt * 128);
         tma_tile(s_u32(b_ring) + s * 16384, &tm_x, (kb0 + kb) * kBlockK, m0, b_full + s * 8);
       }
-      __syncwarp();
     }
-    (void)nraw;
+    __syncwarp();
   } else if (warp == 9) {
     // ================= MMA issuer =================
     if (lane == 0) {
@@ -298,22 +290,34 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
     const int gr = min(row0 + r, p.N - 1);
     const int spg = p.group_size / 128;                     // raw-stage quarters per group
     const uint32_t a_row = (r >> 3) * 1024 + (r & 7) * 128;
-    float sc[4], zc[4];
+    float sc[4], zc[4], sc_n[4], zc_n[4];
+    // scale / zero of the four 128-column quarters of a raw stage: a row-strided (one line per thread) read that
+    // often comes from DRAM, so the next stage's values are requested a whole stage before they are needed
+    auto load_meta = [&](int kb, float (&s4)[4], float (&z4)[4]) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int g = min(((kb0 + kb) / 2 + i) / spg, p.ngroups - 1);
+        s4[i] = __ldg(p.scale + (size_t)gr * p.ngroups + g);
+        z4[i] = __ldg(p.zero + (size_t)gr * p.ngroups + g);
+      }
+    };
+    load_meta(0, sc_n, zc_n);
     for (int kb = 0; kb < nkb; ++kb) {
       const int rsi = kb >> 3, slot = rsi % kRawStages;
       if ((kb & 7) == 0) {
-        // scale / zero of the four 128-column quarters of this raw stage
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int g = ((kb0 + kb) / 2 + i) / spg;
-          sc[i] = __ldg(p.scale + (size_t)gr * p.ngroups + g);
-          zc[i] = __ldg(p.zero + (size_t)gr * p.ngroups + g);
+          sc[i] = sc_n[i];
+          zc[i] = zc_n[i];
         }
+        if (kb + 8 < nkb) load_meta(kb + 8, sc_n, zc_n);
         bar_wait(raw_full + slot * 8, (rsi / kRawStages) & 1, status, dead);
       }
       const int s = kb % kStages;
       bar_wait(ab_empty + s * 8, ((kb / kStages) & 1) ^ 1, status, dead);
-      const uint4 codes = ld_s128(s_u32(raw) + (slot * kRows + r) * kRawPitch + (kb & 7) * 32 + h * 16);
+      // 16-byte chunk (kb & 3) * 2 + h of row r in half (kb & 7) >> 2 of the stage, where the 128B swizzle put it
+      const uint4 codes = ld_s128(s_u32(raw) + (slot * 2 + ((kb & 7) >> 2)) * kRawHalf + r * 128 +
+                                  ((((kb & 3) * 2 + h) ^ (r & 7)) << 4));
       const int quarter = (kb & 7) >> 1;
       const float sq = quarter == 0 ? sc[0] : (quarter == 1 ? sc[1] : (quarter == 2 ? sc[2] : sc[3]));
       const float z = quarter == 0 ? zc[0] : (quarter == 1 ? zc[1] : (quarter == 2 ? zc[2] : zc[3]));
@@ -416,7 +420,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-constexpr size_t kGemmSmem = 1024 + 2 * kStages * 16384 + kRawStages * kRows * kRawPitch + 25 * 8 + 64;
+constexpr size_t kGemmSmem = 1024 + 2 * kStages * 16384 + kRawStages * 2 * kRawHalf + 25 * 8 + 64;
 
 struct GemmPlan {
   int mt, mtiles, mpad, splits, kblocks_per_split;
@@ -488,6 +492,16 @@ int gemm_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
                PARE_ERR_CUDA);
 
+  // tensor map over the packed codes [N][K/2] bytes, box 128 bytes x 128 rows, 128B swizzle (rows beyond N read as zeros)
+  CUtensorMap tw;
+  const cuuint64_t wdims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)N};
+  const cuuint64_t wstrides[1] = {(cuuint64_t)(K / 2)};
+  const cuuint32_t wbox[2] = {128u, (cuuint32_t)kRows};
+  PARE_REQUIRE(enc(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(packed), wdims, wstrides, wbox, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
+               PARE_ERR_CUDA);
+
   GemmParams p{};
   p.packed = packed;
   p.scale = scale;
@@ -510,7 +524,7 @@ int gemm_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   auto launch = [&](auto kern) -> int {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem) != cudaSuccess)
       return PARE_ERR_CUDA;
-    kern<<<grid, kGemmThreads, kGemmSmem, stream>>>(tm, p);
+    kern<<<grid, kGemmThreads, kGemmSmem, stream>>>(tm, tw, p);
     return launch_status();
   };
   return x_dtype == PARE_F16 ? launch(w4a16_gemm_kernel<__half>) : launch(w4a16_gemm_kernel<__nv_bfloat16>);
