@@ -7,7 +7,8 @@
 // every instruction:   Y^T[n][m] = sum_k W[n][k] * X[m][k].
 //
 // One CTA = 128 output rows x one tile of up to 128 activation rows x one K range.  Warp roles:
-//   warps 0-7  dequantize (two threads per weight row), then run the epilogue
+//   warps 0-7  dequantize (two groups of four warps on alternate operand stages, one thread per weight row), then
+//              run the epilogue
 //   warp 8     producer, two lanes: packed codes by TMA (cp.async.bulk.tensor.2d over the [N][K/2] byte matrix,
 //              two 128-row x 128-byte boxes per 512-column stage, 128B swizzle) into a two-stage ring, requested a
 //              whole stage ahead; activation tiles by TMA (128B swizzle) four blocks ahead of the MMA
@@ -224,7 +225,10 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
       bar_init(raw_empty + i * 8, kDequantThreads / 32);
     }
     for (int i = 0; i < kStages; ++i) {
-      bar_init(a_full + i * 8, kDequantThreads / 32);
+      // one barrier per operand stage for both operands: the four warps of the dequantizing group that writes A, and
+      // the producer's expect-tx arrival for the activation tile (a wait costs the MMA thread ~230 cycles even when
+      // the phase is complete, and that thread's loop is what paces the kernel)
+      bar_init(a_full + i * 8, kDequantThreads / 64 + 1);
       bar_init(b_full + i * 8, 1);
       bar_init(ab_empty + i * 8, 1);
     }
@@ -259,8 +263,8 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
       for (int kb = 0; kb < nkb; ++kb) {  // activation tile of each block
         const int s = kb % kStages;
         bar_wait(ab_empty + s * 8, ((kb / kStages) & 1) ^ 1, status, dead);
-        bar_expect(b_full + s * 8, p.mt * 128);
-        tma_tile(s_u32(b_ring) + s * 16384, &tm_x, (kb0 + kb) * kBlockK, m0, b_full + s * 8);
+        bar_expect(a_full + s * 8, p.mt * 128);
+        tma_tile(s_u32(b_ring) + s * 16384, &tm_x, (kb0 + kb) * kBlockK, m0, a_full + s * 8);
       }
     }
     __syncwarp();
@@ -273,7 +277,6 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
         const int s = kb % kStages;
         const uint32_t par = (kb / kStages) & 1;
         bar_wait(a_full + s * 8, par, status, dead);
-        bar_wait(b_full + s * 8, par, status, dead);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_addr = s_u32(a_ring) + s * 16384, b_addr = s_u32(b_ring) + s * 16384;
 #pragma unroll
@@ -286,7 +289,10 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
     __syncwarp();
   } else {
     // ================= dequantize =================
-    const int r = threadIdx.x & 127, h = threadIdx.x >> 7;  // row of the tile, 32-column half of the block
+    // Two groups of four warps, one thread per weight row; group g takes the blocks kb = g (mod 2), so two operand
+    // stages are being written at any time and a thread's fixed cost per stage (barrier wait, arrival, loop: more
+    // cycles than its arithmetic) is spread over 64 weights instead of 32.
+    const int r = threadIdx.x & 127, grp = threadIdx.x >> 7;
     const int gr = min(row0 + r, p.N - 1);
     const int spg = p.group_size / 128;                     // raw-stage quarters per group
     const uint32_t a_row = (r >> 3) * 1024 + (r & 7) * 128;
@@ -302,40 +308,41 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
       }
     };
     load_meta(0, sc_n, zc_n);
-    for (int kb = 0; kb < nkb; ++kb) {
+    for (int kb = grp; kb < nkb; kb += 2) {
       const int rsi = kb >> 3, slot = rsi % kRawStages;
-      if ((kb & 7) == 0) {
+      if ((kb & 7) == grp) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           sc[i] = sc_n[i];
           zc[i] = zc_n[i];
         }
-        if (kb + 8 < nkb) load_meta(kb + 8, sc_n, zc_n);
+        if (kb - grp + 8 < nkb) load_meta(kb - grp + 8, sc_n, zc_n);
         bar_wait(raw_full + slot * 8, (rsi / kRawStages) & 1, status, dead);
       }
       const int s = kb % kStages;
       bar_wait(ab_empty + s * 8, ((kb / kStages) & 1) ^ 1, status, dead);
-      // 16-byte chunk (kb & 3) * 2 + h of row r in half (kb & 7) >> 2 of the stage, where the 128B swizzle put it
-      const uint4 codes = ld_s128(s_u32(raw) + (slot * 2 + ((kb & 7) >> 2)) * kRawHalf + r * 128 +
-                                  ((((kb & 3) * 2 + h) ^ (r & 7)) << 4));
+      // 16-byte chunks (kb & 3) * 2 and + 1 of row r in half (kb & 7) >> 2 of the stage, where the 128B swizzle put them
+      const uint32_t raw_row = s_u32(raw) + (slot * 2 + ((kb & 7) >> 2)) * kRawHalf + r * 128;
+      const uint4 codes0 = ld_s128(raw_row + ((((kb & 3) * 2) ^ (r & 7)) << 4));
+      const uint4 codes1 = ld_s128(raw_row + ((((kb & 3) * 2 + 1) ^ (r & 7)) << 4));
       const int quarter = (kb & 7) >> 1;
       const float sq = quarter == 0 ? sc[0] : (quarter == 1 ? sc[1] : (quarter == 2 ? sc[2] : sc[3]));
       const float z = quarter == 0 ? zc[0] : (quarter == 1 ? zc[1] : (quarter == 2 ? zc[2] : zc[3]));
       const float sp = sq * Pair<T>::kPre;
       const typename Pair<T>::V s_hi = Pair<T>::splat(sp);
       const typename Pair<T>::V s_lo = Pair<T>::splat(sp - to_float<T>(from_float<T>(sp)));
-      const uint32_t wv[4] = {codes.x, codes.y, codes.z, codes.w};
+      const uint32_t wv[8] = {codes0.x, codes0.y, codes0.z, codes0.w, codes1.x, codes1.y, codes1.z, codes1.w};
       const uint32_t dst = s_u32(a_ring) + s * 16384 + a_row;
 #pragma unroll
-      for (int wi = 0; wi < 4; ++wi) {
+      for (int wi = 0; wi < 8; ++wi) {
         const uint4 v = dequant_word<T>(wv[wi], z, s_hi, s_lo);
-        st_s128(dst + (((h * 4 + wi) ^ (r & 7)) << 4), v.x, v.y, v.z, v.w);
+        st_s128(dst + ((wi ^ (r & 7)) << 4), v.x, v.y, v.z, v.w);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // make the tile visible to the MMA unit
       __syncwarp();
       if (lane == 0) {
         bar_arrive(a_full + s * 8);
-        if ((kb & 7) == 7) bar_arrive(raw_empty + slot * 8);
+        if ((kb & 7) == 6 + grp) bar_arrive(raw_empty + slot * 8);   // this group's last block of the raw stage
       }
     }
 
