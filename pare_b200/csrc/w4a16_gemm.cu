@@ -440,13 +440,23 @@ GemmPlan gemm_plan(int M, int N, int K) {
   g.mpad = g.mtiles * g.mt;
   const int row_tiles = (N + kRows - 1) / kRows;
   const int raw_stages = K / kRawK;
-  int splits = (148 + row_tiles * g.mtiles - 1) / (row_tiles * g.mtiles);
-  if (splits > raw_stages) splits = raw_stages;
-  if (splits > 16) splits = 16;
-  if (splits < 1) splits = 1;
-  const int per = (raw_stages + splits - 1) / splits;
-  g.splits = (raw_stages + per - 1) / per;
-  g.kblocks_per_split = per * 8;
+  // K splits by a cost model in microseconds: whole waves of one CTA per SM, each CTA a fixed part (launch, first
+  // loads, epilogue: ~10) plus ~0.35 per 64-column block, plus the cross-CTA sum when K is split (~2).  What it
+  // avoids is a second, nearly empty wave: 48 row tiles take 3 splits (144 CTAs), not 4 (192).
+  const int tiles = row_tiles * g.mtiles;
+  int best_per = raw_stages;
+  double best_cost = 1e30;
+  for (int s = 1; s <= 16 && s <= raw_stages; ++s) {
+    const int per = (raw_stages + s - 1) / s, s_eff = (raw_stages + per - 1) / per;
+    const int waves = (tiles * s_eff + 147) / 148;
+    const double cost = waves * (10.0 + per * 8 * 0.35) + (s_eff > 1 ? 2.0 : 0.0);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best_per = per;
+    }
+  }
+  g.splits = (raw_stages + best_per - 1) / best_per;
+  g.kblocks_per_split = best_per * 8;
   return g;
 }
 
