@@ -273,15 +273,19 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (Pair<T>::kFmt << 7) | (Pair<T>::kFmt << 10) | ((uint32_t)(p.mt >> 3) << 17) |
                              ((uint32_t)(kRows >> 4) << 24);
+      // This thread's loop paces the kernel (every instruction waits for the one before), so it carries as little
+      // as possible: descriptors of stage 0 built once, a stage or a 16-column step further is an addition to the
+      // descriptor's address field (units of 16 bytes).
+      const uint64_t a_desc0 = umma_desc(s_u32(a_ring)), b_desc0 = umma_desc(s_u32(b_ring));
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % kStages;
         const uint32_t par = (kb / kStages) & 1;
         bar_wait(a_full + s * 8, par, status, dead);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = s_u32(a_ring) + s * 16384, b_addr = s_u32(b_ring) + s * 16384;
+        const uint64_t a_desc = a_desc0 + (uint64_t)(s * (16384 >> 4)), b_desc = b_desc0 + (uint64_t)(s * (16384 >> 4));
+        umma_f16(tmem_acc, a_desc, b_desc, idesc, kb != 0);
 #pragma unroll
-        for (int j = 0; j < kBlockK / 16; ++j)
-          umma_f16(tmem_acc, umma_desc(a_addr + j * 32), umma_desc(b_addr + j * 32), idesc, (kb | j) != 0);
+        for (int j = 1; j < kBlockK / 16; ++j) umma_f16(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc, 1u);
         umma_commit(ab_empty + s * 8);  // frees the operand stage when these MMAs have read it
       }
       umma_commit(acc_full);
