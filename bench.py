@@ -295,7 +295,7 @@ def layer_table(stack, peak: float, batches=(1, 4, 16)) -> dict:
 
 
 def prefill_table(stack, batches=(64, 256)) -> dict:
-    """Tensor-core path (tcgen05 tiles over dequantized operands, M > 48): us per layer, TFLOP/s and the fraction of
+    """Tensor-core path (tcgen05 tiles over dequantized operands, M > 16): us per layer, TFLOP/s and the fraction of
     the measured dense bf16 peak (burst figure: each projection is timed alone)."""
     peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
     tf_peak = float(peaks.get("bf16_tflops", 1590.0))

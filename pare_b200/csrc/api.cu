@@ -62,11 +62,10 @@ int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* p
   PARE_REQUIRE(x_dtype == PARE_F16 || x_dtype == PARE_BF16, PARE_ERR_DTYPE);
   PARE_REQUIRE(x && packed && y && (meta_h2 || (scale && zero)), PARE_ERR_SHAPE);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  // M > 16: tensor-core tiles -- except that up to 48 rows are still faster as three passes of the
-  // persistent streaming kernel where it applies (measured on 28672 x 4096: 40 us per 16 rows
-  // against 129 us for one tensor-core pass, whose dequantization stage is the limit)
-  const bool chunked = M <= 48 && pare::gemv_persist_supported(16, N, K, group_size);
-  if (!chunked && pare::gemm_supported(M, K, group_size, scale, zero))
+  // M > 16: tensor-core tiles where they apply (measured on the 8B shapes: from 24 rows on they beat passes of 16
+  // rows through the streaming kernel on every projection, at 17 rows they are within 10 % either way); otherwise,
+  // and always for M <= 16, the streaming kernel in passes of at most 16 rows
+  if (M > 16 && pare::gemm_supported(M, K, group_size, scale, zero))
     return pare::gemm_forward(x, x_dtype, ldx, packed, scale, zero, col_perm, input_scale, bias, y, ldy, M, N, K,
                               group_size, workspace, workspace_bytes, s);
   const size_t esz = 2;

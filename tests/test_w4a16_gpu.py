@@ -258,12 +258,6 @@ def test_tensor_core_path_matches_oracle(shape, m, dtype, cuda_lib):
     y = w4a16_forward(x, ql.packed_weight, ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous(), 128,
                       bias=ql.bias.detach().to(dtype))
     assert y.shape == (m, n) and y.dtype == dtype
-    if m <= 48 and shape == (4096, 4096):
-        # up to 48 rows of a layer the persistent streaming kernel serves go through it in passes of 16 rows
-        # (faster than one tensor-core pass): exact fp32-weight semantics, the bars of the decode path apply
-        ref = oracle_y(ql, x) - ql.bias.detach().float().cpu().numpy() + ql.bias.detach().to(dtype).float().cpu().numpy()
-        check(y, ref, dtype)
-        return
     # bar 1: the reference's eager semantics (weights cast to the activation dtype, fp32 accumulate).  Mean
     # bars as everywhere else (1e-3 fp16, 2.5e-3 bf16).  The max bar is 2e-2 / 2e-1: a fraction of a percent
     # of the weights land one ulp of the 16-bit type off the reference's cast (the scale goes through a
