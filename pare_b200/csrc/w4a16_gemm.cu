@@ -7,7 +7,7 @@
 // every instruction:   Y^T[n][m] = sum_k W[n][k] * X[m][k].
 //
 // One CTA = 128 output rows x one tile of up to 128 activation rows x one K range.  Warp roles:
-//   warps 0-7  dequantize (two groups of four warps on alternate operand stages, one thread per weight row), then
+//   warps 0-7  dequantize (two groups of four warps, one per 64-column block of a 128-column stage, one thread per weight row), then
 //              run the epilogue
 //   warp 8     producer, two lanes: packed codes by TMA (cp.async.bulk.tensor.2d over the [N][K/2] byte matrix,
 //              two 128-row x 128-byte boxes per 512-column stage, 128B swizzle) into a two-stage ring, requested a
@@ -34,7 +34,8 @@ constexpr int kBlockK = 64;            // columns per MMA stage: 128 bytes of 16
 constexpr int kRawK = 512;             // columns per raw (packed) stage
 constexpr int kRawHalf = kRows * 128;  // bytes of half a raw stage: 128 rows x 128 bytes (256 columns), 128B swizzle
 constexpr int kRawStages = 2;
-constexpr int kStages = 4;             // operand ring depth
+constexpr int kStages = 2;             // operand ring depth, in stages of two 64-column blocks (one barrier round per 128 columns)
+constexpr int kStageBytes = 32768;     // per operand and stage: two K-major 128B-swizzled tiles of up to 128 rows
 constexpr int kDequantThreads = 256;
 constexpr int kGemmThreads = kDequantThreads + 64;
 constexpr uint32_t kSpin = 1u << 22;
@@ -202,9 +203,9 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
                                                                  const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* a_ring = smem;                                   // kStages x 16 KB
-  unsigned char* b_ring = a_ring + kStages * 16384;               // kStages x 16 KB (mt <= 128 rows x 128 B)
-  unsigned char* raw = b_ring + kStages * 16384;                  // kRawStages x 2 halves x 16 KB
+  unsigned char* a_ring = smem;                                   // kStages x 2 blocks x 16 KB
+  unsigned char* b_ring = a_ring + kStages * kStageBytes;         // kStages x 2 blocks x 16 KB (mt <= 128 rows x 128 B)
+  unsigned char* raw = b_ring + kStages * kStageBytes;            // kRawStages x 2 halves x 16 KB
   uint64_t* bars = reinterpret_cast<uint64_t*>(raw + kRawStages * 2 * kRawHalf);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
   const uint32_t raw_full = s_u32(bars), raw_empty = s_u32(bars + 2), a_full = s_u32(bars + 4), b_full = s_u32(bars + 8),
@@ -225,10 +226,10 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
       bar_init(raw_empty + i * 8, kDequantThreads / 32);
     }
     for (int i = 0; i < kStages; ++i) {
-      // one barrier per operand stage for both operands: the four warps of the dequantizing group that writes A, and
-      // the producer's expect-tx arrival for the activation tile (a wait costs the MMA thread ~230 cycles even when
-      // the phase is complete, and that thread's loop is what paces the kernel)
-      bar_init(a_full + i * 8, kDequantThreads / 64 + 1);
+      // one barrier per operand stage for both operands: the eight dequantizing warps that write A (one group per
+      // 64-column block) and the producer's expect-tx arrival for the two activation tiles (a wait costs the MMA
+      // thread ~230 cycles even when the phase is complete, and that thread's loop is what paces the kernel)
+      bar_init(a_full + i * 8, kDequantThreads / 32 + 1);
       bar_init(b_full + i * 8, 1);
       bar_init(ab_empty + i * 8, 1);
     }
@@ -260,11 +261,12 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
         tma_tile(s_u32(raw) + (slot * 2 + 1) * kRawHalf, &tm_w, xb + 128, row0, raw_full + slot * 8);
       }
     } else if (lane == 0) {
-      for (int kb = 0; kb < nkb; ++kb) {  // activation tile of each block
-        const int s = kb % kStages;
-        bar_wait(ab_empty + s * 8, ((kb / kStages) & 1) ^ 1, status, dead);
-        bar_expect(a_full + s * 8, p.mt * 128);
-        tma_tile(s_u32(b_ring) + s * 16384, &tm_x, (kb0 + kb) * kBlockK, m0, a_full + s * 8);
+      for (int kd = 0; kd < nkb / 2; ++kd) {  // the two activation tiles of each stage
+        const int s = kd % kStages;
+        bar_wait(ab_empty + s * 8, ((kd / kStages) & 1) ^ 1, status, dead);
+        bar_expect(a_full + s * 8, 2 * p.mt * 128);
+        tma_tile(s_u32(b_ring) + s * kStageBytes, &tm_x, (kb0 + 2 * kd) * kBlockK, m0, a_full + s * 8);
+        tma_tile(s_u32(b_ring) + s * kStageBytes + 16384, &tm_x, (kb0 + 2 * kd + 1) * kBlockK, m0, a_full + s * 8);
       }
     }
     __syncwarp();
@@ -277,15 +279,18 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
       // as possible: descriptors of stage 0 built once, a stage or a 16-column step further is an addition to the
       // descriptor's address field (units of 16 bytes).
       const uint64_t a_desc0 = umma_desc(s_u32(a_ring)), b_desc0 = umma_desc(s_u32(b_ring));
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % kStages;
-        const uint32_t par = (kb / kStages) & 1;
+      for (int kd = 0; kd < nkb / 2; ++kd) {
+        const int s = kd % kStages;
+        const uint32_t par = (kd / kStages) & 1;
         bar_wait(a_full + s * 8, par, status, dead);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t a_desc = a_desc0 + (uint64_t)(s * (16384 >> 4)), b_desc = b_desc0 + (uint64_t)(s * (16384 >> 4));
-        umma_f16(tmem_acc, a_desc, b_desc, idesc, kb != 0);
+        const uint64_t a_desc = a_desc0 + (uint64_t)(s * (kStageBytes >> 4)), b_desc = b_desc0 + (uint64_t)(s * (kStageBytes >> 4));
+        umma_f16(tmem_acc, a_desc, b_desc, idesc, kd != 0);
 #pragma unroll
-        for (int j = 1; j < kBlockK / 16; ++j) umma_f16(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc, 1u);
+        for (int j = 1; j < 2 * (kBlockK / 16); ++j) {   // the second block's tiles start 16 KB after the first's
+          const uint64_t o = (uint64_t)((j >> 2) * (16384 >> 4) + (j & 3) * 2);
+          umma_f16(tmem_acc, a_desc + o, b_desc + o, idesc, 1u);
+        }
         umma_commit(ab_empty + s * 8);  // frees the operand stage when these MMAs have read it
       }
       umma_commit(acc_full);
@@ -293,9 +298,9 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
     __syncwarp();
   } else {
     // ================= dequantize =================
-    // Two groups of four warps, one thread per weight row; group g takes the blocks kb = g (mod 2), so two operand
-    // stages are being written at any time and a thread's fixed cost per stage (barrier wait, arrival, loop: more
-    // cycles than its arithmetic) is spread over 64 weights instead of 32.
+    // Two groups of four warps, one thread per weight row; group g writes block g of every stage (the blocks
+    // kb = g mod 2), so a thread's fixed cost per stage (barrier wait, arrival, loop: more cycles than its
+    // arithmetic) is spread over 64 weights.
     const int r = threadIdx.x & 127, grp = threadIdx.x >> 7;
     const int gr = min(row0 + r, p.N - 1);
     const int spg = p.group_size / 128;                     // raw-stage quarters per group
@@ -323,8 +328,8 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
         if (kb - grp + 8 < nkb) load_meta(kb - grp + 8, sc_n, zc_n);
         bar_wait(raw_full + slot * 8, (rsi / kRawStages) & 1, status, dead);
       }
-      const int s = kb % kStages;
-      bar_wait(ab_empty + s * 8, ((kb / kStages) & 1) ^ 1, status, dead);
+      const int kd = kb >> 1, s = kd % kStages;   // this group writes block grp of stage kd
+      bar_wait(ab_empty + s * 8, ((kd / kStages) & 1) ^ 1, status, dead);
       // 16-byte chunks (kb & 3) * 2 and + 1 of row r in half (kb & 7) >> 2 of the stage, where the 128B swizzle put them
       const uint32_t raw_row = s_u32(raw) + (slot * 2 + ((kb & 7) >> 2)) * kRawHalf + r * 128;
       const uint4 codes0 = ld_s128(raw_row + ((((kb & 3) * 2) ^ (r & 7)) << 4));
@@ -336,7 +341,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
       const typename Pair<T>::V s_hi = Pair<T>::splat(sp);
       const typename Pair<T>::V s_lo = Pair<T>::splat(sp - to_float<T>(from_float<T>(sp)));
       const uint32_t wv[8] = {codes0.x, codes0.y, codes0.z, codes0.w, codes1.x, codes1.y, codes1.z, codes1.w};
-      const uint32_t dst = s_u32(a_ring) + s * 16384 + a_row;
+      const uint32_t dst = s_u32(a_ring) + s * kStageBytes + grp * 16384 + a_row;
 #pragma unroll
       for (int wi = 0; wi < 8; ++wi) {
         const uint4 v = dequant_word<T>(wv[wi], z, s_hi, s_lo);
@@ -431,7 +436,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-constexpr size_t kGemmSmem = 1024 + 2 * kStages * 16384 + kRawStages * 2 * kRawHalf + 25 * 8 + 64;
+constexpr size_t kGemmSmem = 1024 + 2 * kStages * kStageBytes + kRawStages * 2 * kRawHalf + 25 * 8 + 64;
 
 struct GemmPlan {
   int mt, mtiles, mpad, splits, kblocks_per_split;
