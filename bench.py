@@ -339,6 +339,30 @@ def prefill_attention_table(dtype, device, lengths=(2048, 8192)) -> dict:
     return table
 
 
+def prompt_table(args, dtype, device, lengths=(512, 2048)) -> dict:
+    """The whole prompt path of the stack (``DecodeStack.prefill``: RMSNorm, tensor-core linears, rotary embedding,
+    causal attention at full precision, cache append with compression, SwiGLU) on a fresh stack of 4 blocks:
+    ms per block and prompt tokens/s extrapolated to the stack's block count."""
+    from pare_b200.decode import SHAPES, DecodeStack
+
+    n_blocks = 4
+    total_blocks = args.layers or SHAPES[args.shape][5]
+    stack = DecodeStack(args.shape, device=device, dtype=dtype, n_layers=n_blocks, max_seq_len=max(lengths) + 256)
+    table = {}
+    for t in lengths:
+        x = torch.randn(1, t, stack.hidden, device=device).to(dtype)
+
+        def run():
+            stack.cache.reset()
+            stack.prefill(x)
+
+        sec = time_events(run, 5, 2, 1) / 5
+        table[f"t{t}"] = {"ms_per_block": round(sec / n_blocks * 1e3, 3),
+                          "tok_s": round(t / (sec / n_blocks * total_blocks), 1)}
+    del stack
+    return table
+
+
 def attention_table(dtype, device, peak: float,
                     cases=((1, 4096, 32, 4), (16, 4096, 8, 4), (16, 4096, 8, 2), (16, 4096, 8, 4, 32))) -> dict:
     """Fused KIVI decode attention alone (8 KV heads, 32 query heads, D = 128, g32, residual window 128):
@@ -445,6 +469,7 @@ def run_ours(args) -> None:
         line["attention"] = {} if args.skip_layer_table else attention_table(dtype, stack.device, peak)
         line["prefill_layers"] = {} if args.skip_layer_table else prefill_table(stack)
         line["prefill_attention"] = {} if args.skip_layer_table else prefill_attention_table(dtype, stack.device)
+        line["prompt"] = {} if args.skip_layer_table else prompt_table(args, dtype, stack.device)
         key = f"gate_up_{blk.gate_up.out_features}x{blk.gate_up.in_features}_m{args.batch}"
         if key in table:
             achieved = table[key]["gbs"]
