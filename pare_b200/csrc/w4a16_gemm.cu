@@ -10,8 +10,8 @@
 //   warps 0-7  dequantize (two groups of four warps, one per 64-column block of a 128-column stage, one thread per weight row), then
 //              run the epilogue
 //   warp 8     producer, two lanes: packed codes by TMA (cp.async.bulk.tensor.2d over the [N][K/2] byte matrix,
-//              two 128-row x 128-byte boxes per 512-column stage, 128B swizzle) into a two-stage ring, requested a
-//              whole stage ahead; activation tiles by TMA (128B swizzle) four blocks ahead of the MMA
+//              one 128-row x 128-byte box per 256-column stage, 128B swizzle) into a four-stage ring, requested up
+//              to three stages ahead; activation tiles by TMA (128B swizzle) one operand stage ahead of the MMA
 //   warp 9     one elected thread issues tcgen05.mma (UMMA 128 x MT x 16, fp32 accumulate in TMEM)
 // Per 64-column block a dequantizing thread reads 16 bytes of codes, turns them into exact
 // integers in the 16-bit float type by the mantissa trick of common.cuh, multiplies by the group
@@ -31,9 +31,10 @@ namespace {
 
 constexpr int kRows = 128;             // weight rows per CTA (UMMA M)
 constexpr int kBlockK = 64;            // columns per MMA stage: 128 bytes of 16-bit elements = one swizzle row
-constexpr int kRawK = 512;             // columns per raw (packed) stage
-constexpr int kRawHalf = kRows * 128;  // bytes of half a raw stage: 128 rows x 128 bytes (256 columns), 128B swizzle
-constexpr int kRawStages = 2;
+constexpr int kRawK = 256;             // columns per raw (packed) stage: four 64-column blocks, one tensor-map box
+constexpr int kRawBytes = kRows * 128; // bytes of a raw stage: 128 rows x 128 bytes, 128B swizzle
+constexpr int kRawStages = 4;          // three stages (3 x 1.2 us of work) in flight cover the 2.5 - 3.5 us a box takes to arrive
+constexpr int kRawKb = kRawK / kBlockK;
 constexpr int kStages = 2;             // operand ring depth, in stages of two 64-column blocks (one barrier round per 128 columns)
 constexpr int kStageBytes = 32768;     // per operand and stage: two K-major 128B-swizzled tiles of up to 128 rows
 constexpr int kDequantThreads = 256;
@@ -205,18 +206,18 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* a_ring = smem;                                   // kStages x 2 blocks x 16 KB
   unsigned char* b_ring = a_ring + kStages * kStageBytes;         // kStages x 2 blocks x 16 KB (mt <= 128 rows x 128 B)
-  unsigned char* raw = b_ring + kStages * kStageBytes;            // kRawStages x 2 halves x 16 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + kRawStages * 2 * kRawHalf);
+  unsigned char* raw = b_ring + kStages * kStageBytes;            // kRawStages x 16 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + kRawStages * kRawBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
-  const uint32_t raw_full = s_u32(bars), raw_empty = s_u32(bars + 2), a_full = s_u32(bars + 4), b_full = s_u32(bars + 8),
-                 ab_empty = s_u32(bars + 12), acc_full = s_u32(bars + 16);
+  const uint32_t raw_full = s_u32(bars), raw_empty = s_u32(bars + 4), a_full = s_u32(bars + 8), b_full = s_u32(bars + 12),
+                 ab_empty = s_u32(bars + 16), acc_full = s_u32(bars + 20);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = blockIdx.x * kRows;
   const int m0 = blockIdx.z * p.mt;
   const int kb_total = p.K / kBlockK;
   const int kb0 = blockIdx.y * p.kblocks_per_split;
-  const int nkb = min(p.kblocks_per_split, kb_total - kb0);       // multiple of 8 (host guarantees)
+  const int nkb = min(p.kblocks_per_split, kb_total - kb0);       // multiple of 4 (host guarantees)
   int* status = p.counters ? p.counters + kStatusIndex : nullptr;
   bool dead = false;
 
@@ -250,15 +251,14 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
     // ================= producer =================
     // Two independent lanes: lane 1 keeps the raw ring full (a stage is requested as soon as its slot is free, a
     // whole stage before the dequantizing threads reach it), lane 0 feeds the activation ring four blocks ahead
-    // of the MMA.  A raw stage is two tensor-map copies of 128 rows x 128 bytes.
+    // of the MMA.  A raw stage is one tensor-map copy of 128 rows x 128 bytes.
     if (lane == 1) {
-      for (int rs = 0; rs < nkb / 8; ++rs) {
+      for (int rs = 0; rs < nkb / kRawKb; ++rs) {
         const int slot = rs % kRawStages;
         bar_wait(raw_empty + slot * 8, ((rs / kRawStages) & 1) ^ 1, status, dead);
-        bar_expect(raw_full + slot * 8, 2 * kRawHalf);
-        const int xb = (kb0 + rs * 8) * (kBlockK / 2);   // byte column of the stage
-        tma_tile(s_u32(raw) + (slot * 2) * kRawHalf, &tm_w, xb, row0, raw_full + slot * 8);
-        tma_tile(s_u32(raw) + (slot * 2 + 1) * kRawHalf, &tm_w, xb + 128, row0, raw_full + slot * 8);
+        bar_expect(raw_full + slot * 8, kRawBytes);
+        const int xb = (kb0 + rs * kRawKb) * (kBlockK / 2);   // byte column of the stage
+        tma_tile(s_u32(raw) + slot * kRawBytes, &tm_w, xb, row0, raw_full + slot * 8);
       }
     } else if (lane == 0) {
       for (int kd = 0; kd < nkb / 2; ++kd) {  // the two activation tiles of each stage
@@ -303,14 +303,14 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
     // arithmetic) is spread over 64 weights.
     const int r = threadIdx.x & 127, grp = threadIdx.x >> 7;
     const int gr = min(row0 + r, p.N - 1);
-    const int spg = p.group_size / 128;                     // raw-stage quarters per group
+    const int spg = p.group_size / 128;                     // 128-column halves of a raw stage per group
     const uint32_t a_row = (r >> 3) * 1024 + (r & 7) * 128;
-    float sc[4], zc[4], sc_n[4], zc_n[4];
-    // scale / zero of the four 128-column quarters of a raw stage: a row-strided (one line per thread) read that
+    float sc[2], zc[2], sc_n[2], zc_n[2];
+    // scale / zero of the two 128-column halves of a raw stage: a row-strided (one line per thread) read that
     // often comes from DRAM, so the next stage's values are requested a whole stage before they are needed
-    auto load_meta = [&](int kb, float (&s4)[4], float (&z4)[4]) {
+    auto load_meta = [&](int kb, float (&s4)[2], float (&z4)[2]) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < 2; ++i) {
         const int g = min(((kb0 + kb) / 2 + i) / spg, p.ngroups - 1);
         s4[i] = __ldg(p.scale + (size_t)gr * p.ngroups + g);
         z4[i] = __ldg(p.zero + (size_t)gr * p.ngroups + g);
@@ -318,25 +318,25 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
     };
     load_meta(0, sc_n, zc_n);
     for (int kb = grp; kb < nkb; kb += 2) {
-      const int rsi = kb >> 3, slot = rsi % kRawStages;
-      if ((kb & 7) == grp) {
+      const int rsi = kb / kRawKb, slot = rsi % kRawStages;
+      if ((kb & (kRawKb - 1)) == grp) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 2; ++i) {
           sc[i] = sc_n[i];
           zc[i] = zc_n[i];
         }
-        if (kb - grp + 8 < nkb) load_meta(kb - grp + 8, sc_n, zc_n);
+        if (kb - grp + kRawKb < nkb) load_meta(kb - grp + kRawKb, sc_n, zc_n);
         bar_wait(raw_full + slot * 8, (rsi / kRawStages) & 1, status, dead);
       }
       const int kd = kb >> 1, s = kd % kStages;   // this group writes block grp of stage kd
       bar_wait(ab_empty + s * 8, ((kd / kStages) & 1) ^ 1, status, dead);
-      // 16-byte chunks (kb & 3) * 2 and + 1 of row r in half (kb & 7) >> 2 of the stage, where the 128B swizzle put them
-      const uint32_t raw_row = s_u32(raw) + (slot * 2 + ((kb & 7) >> 2)) * kRawHalf + r * 128;
+      // 16-byte chunks (kb & 3) * 2 and + 1 of row r of the stage, where the 128B swizzle put them
+      const uint32_t raw_row = s_u32(raw) + slot * kRawBytes + r * 128;
       const uint4 codes0 = ld_s128(raw_row + ((((kb & 3) * 2) ^ (r & 7)) << 4));
       const uint4 codes1 = ld_s128(raw_row + ((((kb & 3) * 2 + 1) ^ (r & 7)) << 4));
-      const int quarter = (kb & 7) >> 1;
-      const float sq = quarter == 0 ? sc[0] : (quarter == 1 ? sc[1] : (quarter == 2 ? sc[2] : sc[3]));
-      const float z = quarter == 0 ? zc[0] : (quarter == 1 ? zc[1] : (quarter == 2 ? zc[2] : zc[3]));
+      const bool second = (kb & 2) != 0;   // which 128-column half of the stage
+      const float sq = second ? sc[1] : sc[0];
+      const float z = second ? zc[1] : zc[0];
       const float sp = sq * Pair<T>::kPre;
       const typename Pair<T>::V s_hi = Pair<T>::splat(sp);
       const typename Pair<T>::V s_lo = Pair<T>::splat(sp - to_float<T>(from_float<T>(sp)));
@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
       __syncwarp();
       if (lane == 0) {
         bar_arrive(a_full + s * 8);
-        if ((kb & 7) == 6 + grp) bar_arrive(raw_empty + slot * 8);   // this group's last block of the raw stage
+        if ((kb & (kRawKb - 1)) == kRawKb - 2 + grp) bar_arrive(raw_empty + slot * 8);   // this group's last block of the raw stage
       }
     }
 
@@ -436,7 +436,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-constexpr size_t kGemmSmem = 1024 + 2 * kStages * kStageBytes + kRawStages * 2 * kRawHalf + 25 * 8 + 64;
+constexpr size_t kGemmSmem = 1024 + 2 * kStages * kStageBytes + kRawStages * kRawBytes + 25 * 8 + 64;
 
 struct GemmPlan {
   int mt, mtiles, mpad, splits, kblocks_per_split;
@@ -458,21 +458,22 @@ GemmPlan gemm_plan(int M, int N, int K) {
   for (int s = 1; s <= 16 && s <= raw_stages; ++s) {
     const int per = (raw_stages + s - 1) / s, s_eff = (raw_stages + per - 1) / per;
     const int waves = (tiles * s_eff + 147) / 148;
-    const double cost = waves * (10.0 + per * 8 * 0.35) + (s_eff > 1 ? 2.0 : 0.0);
+    const double cost = waves * (10.0 + per * kRawKb * 0.35) + (s_eff > 1 ? 2.0 : 0.0);
     if (cost < best_cost - 1e-9) {
       best_cost = cost;
       best_per = per;
     }
   }
   g.splits = (raw_stages + best_per - 1) / best_per;
-  g.kblocks_per_split = best_per * 8;
+  g.kblocks_per_split = best_per * kRawKb;
   return g;
 }
 
 }  // namespace
 
 bool gemm_supported(int M, int K, int G, const float* scale, const float* zero) {
-  return M > 16 && (K % kRawK) == 0 && (G % 128) == 0 && scale != nullptr && zero != nullptr;
+  // 512 rather than the raw stage's 256: shapes between the two keep the streaming kernel's fp32-weight semantics
+  return M > 16 && (K % 512) == 0 && (G % 128) == 0 && scale != nullptr && zero != nullptr;
 }
 
 size_t gemm_workspace_bytes(int M, int N, int K) {
