@@ -365,16 +365,40 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
     const T* bias = reinterpret_cast<const T*>(p.bias);
     const float bv = (bias && n < p.N && p.splits == 1) ? to_float<T>(bias[n]) : 0.f;
     float* part = p.splits > 1 ? p.partial + (size_t)blockIdx.y * p.M * p.N : nullptr;
-    for (int c = chalf * cpw; c < (chalf + 1) * cpw; c += 8) {
-      uint32_t v[8];
+    // Whole-K tiles with an aligned output go through a per-warp transpose in shared memory (the operand ring is
+    // free by now): a lane holds ONE output column n for 16 activation rows, i.e. 2-byte stores 64 bytes per
+    // instruction; after the transpose a lane stores 8 consecutive n of one row as 16 bytes.
+    const bool vec_out = part == nullptr && (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0 && (p.ldy & 7) == 0 && row0 + kRows <= p.N;
+    const uint32_t tbuf = s_u32(a_ring) + warp * 1024;   // [16 activation rows][32 n] of T
+    for (int c = chalf * cpw; c < (chalf + 1) * cpw; c += 16) {
+      uint32_t v[16];
       const uint32_t taddr = tmem_acc + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c;
-      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                   : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                   : "r"(taddr));
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+            "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+          : "r"(taddr));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (n < p.N && !dead) {
+      if (vec_out) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 16; ++i) {
+          const T h = from_float<T>(__uint_as_float(v[i]) * (1.f / Pair<T>::kPre) + bv);
+          asm volatile("st.shared.u16 [%0], %1;" ::"r"(tbuf + (i * 32 + lane) * 2), "h"(*reinterpret_cast<const unsigned short*>(&h)) : "memory");
+        }
+        __syncwarp();
+        if (!dead) {
+#pragma unroll
+          for (int pass = 0; pass < 2; ++pass) {
+            const int mi = pass * 8 + (lane >> 2), seg = lane & 3;
+            const int m = m0 + c + mi;
+            const uint4 o = ld_s128(tbuf + (mi * 32 + seg * 8) * 2);
+            if (m < p.M) *reinterpret_cast<uint4*>(yg + (size_t)m * p.ldy + row0 + q4 * 32 + seg * 8) = o;
+          }
+        }
+        __syncwarp();
+      } else if (n < p.N && !dead) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
           const int m = m0 + c + i;
           if (m < p.M) {
             const float f = __uint_as_float(v[i]) * (1.f / Pair<T>::kPre);
