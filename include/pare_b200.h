@@ -85,11 +85,6 @@ int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx,
                        void* workspace, size_t workspace_bytes,
                        void* stream);
 
-/* Tuning override for experiments (host state, process-wide, not thread-safe): schedule (-1 = tile kernel only,
- * 1 / 2 = 16-row blocks per tile CTA, 0 = automatic), columns per tile CTA (multiple of 256) and warps per tile
- * CTA (4 or 8); 0 = choose automatically. */
-void pare_w4a16_set_tuning(int schedule, int columns_per_cta, int warps_per_cta);
-
 /* ------------------------------------------------------------------------
  * Prepared activations: the M <= 16 path of pare_w4a16_forward in two halves, so that the
  * kernel which computes an activation (RMSNorm, SwiGLU, attention: below) can hand it to the
@@ -225,9 +220,6 @@ int pare_prefill_attn(const void* q, const void* k, const void* v, void* out, in
                       int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t,
                       int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t,
                       int B, int Hq, int H, int Tq, int Tk, int D, float softmax_scale, int causal, void* stream);
-
-/* Tuning override for experiments: compressed tokens per CTA (multiple of 128, <= 512); 0 = auto. */
-void pare_kivi_attn_set_tuning(int chunk);
 
 /* ------------------------------------------------------------------------
  * Decode-step glue (no counterpart in the reference library: model code around the two hot

@@ -18,7 +18,6 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
                  size_t workspace_bytes, cudaStream_t stream, const void* prepared, const ProducerArgs* prod);
 int gemv_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_perm, const float* input_scale, int M, int K,
                  void* prepared, cudaStream_t stream);
-void gemv_set_tuning(int rb, int splits, int pf);
 bool gemv_persist_supported(int M, int N, int K, int G, bool producer = false);
 bool gemm_supported(int M, int K, int G, const float* scale, const float* zero);
 size_t gemm_workspace_bytes(int M, int N, int K);
@@ -140,10 +139,6 @@ int pare_w4a16_forward_produced(int producer, const void* a, const void* b, cons
   if (rc != PARE_OK) return rc;
   return pare::gemv_forward(nullptr, x_dtype, K, packed, scale, zero, meta_h2, nullptr, nullptr, bias, y, ldy, M, N, K,
                             group_size, workspace, workspace_bytes, s, prepared, nullptr);
-}
-
-void pare_w4a16_set_tuning(int row_blocks, int k_splits, int prefetch) {
-  pare::gemv_set_tuning(row_blocks, k_splits, prefetch);
 }
 
 }  // extern "C"

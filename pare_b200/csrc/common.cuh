@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "pare_b200.h"
 
 namespace pare {
@@ -19,6 +21,37 @@ namespace pare {
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? PARE_OK : PARE_ERR_CUDA; }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Streaming multiprocessors of the current device (cached per device; 148 on a B200).  Schedules are sized by it;
+// nothing depends on it for correctness.
+inline int sm_count() {
+  static std::mutex mu;
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    cached[dev] = v;
+  }
+  return cached[dev];
+}
+
+// cudaFuncSetAttribute(max dynamic shared memory) once per (kernel, device), thread-safe.
+template <typename Kern>
+inline bool ensure_smem_attr(Kern kern, int bytes) {
+  static std::mutex mu;
+  static bool done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!done[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+    done[dev] = true;
+  }
+  return true;
+}
 
 // ---- programmatic dependent launch ------------------------------------------
 // A kernel launched with the programmatic-stream-serialization attribute may start

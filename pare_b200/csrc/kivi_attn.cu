@@ -676,20 +676,16 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
   if (threadIdx.x == 0) p.counters[bh] = 0;
 }
 
-int g_attn_chunk = 0;
-
 int pick_chunk(int B, int H, int n_comp, int group) {
   int chunk;
-  if (g_attn_chunk) {
-    chunk = g_attn_chunk;
-  } else {
+  {
     // 256 tokens per CTA: every warp has a 32-token group to score, three CTAs stay resident per SM (what overlaps
     // one CTA's copies with another's arithmetic once the grid is larger than the machine), and the merge of
     // a 4096-token context reads each split's partial output in one round trip
     chunk = n_comp <= 128 ? 128 : 256;
     // a grid that does not even fill the machine is all latency: longer chunks mean fewer splits to merge
     // (measured at batch 1, 4096 tokens: 11.6 us with 512-token chunks, 12.9 us with 256)
-    if ((long long)B * H * ((n_comp + 255) / 256) <= 148 && n_comp > 256) chunk = 512;
+    if ((long long)B * H * ((n_comp + 255) / 256) <= sm_count() && n_comp > 256) chunk = 512;
     while (chunk < kMaxChunk && (n_comp + chunk - 1) / chunk > 96) chunk += 128;   // bound the merge
   }
   if (chunk % group) chunk = (chunk + group - 1) / group * group;
@@ -728,8 +724,6 @@ size_t pare_kivi_attn_workspace_bytes(int B, int H, int n_comp, int n_res) {
   const size_t n_split = (size_t)(n_comp + 127) / 128 + (size_t)(n_res + pare::kResChunk - 1) / pare::kResChunk + 1;
   return pare::kCounterBytes + (size_t)B * H * n_split * (pare::kHeads * pare::kD + pare::kHeads * 2) * sizeof(float);
 }
-
-void pare_kivi_attn_set_tuning(int chunk) { pare::g_attn_chunk = chunk; }
 
 int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t q_stride_h, const uint8_t* k_codes,
                           const float* k_scale, const float* k_zero, const uint8_t* v_codes, const float* v_scale,

@@ -11,9 +11,12 @@
 //
 // Exchange buffer of a rank (allocated by pare_peer_buffer_create, mapped into the peers with
 // CUDA IPC):  [0, 4096): header -- epoch[kMaxCtas] ints, status word; [4096, ...): data[2][world][slot].
-// Slots are double-buffered by the parity of a per-CTA epoch that the kernel itself advances, so a
-// captured CUDA graph can be replayed: a rank can only be one call ahead of a peer (it needs the
-// peer's data of the current call to finish), so a slot is never overwritten while it is being read.
+// Slots are double-buffered by the parity of an epoch that the kernel itself advances, so a captured CUDA
+// graph can be replayed.  Every call launches all kMaxCtas CTAs (those without units only advance their
+// epoch word), so every CTA's word equals the number of calls made so far whatever the calls' shapes were:
+// a unit's marks grow by one per call no matter which CTA owned it in which call, and a rank can only be
+// one call ahead of a peer (it needs the peer's data of the current call to finish), so a slot is never
+// overwritten while it is being read and a mark of an older call is never mistaken for the current one.
 // A wait that runs out sets PARE_ERR_TIMEOUT in the header's status word and the call returns
 // whatever it has (the host reads the word with pare_peer_status).
 
@@ -167,12 +170,13 @@ int pare_peer_allreduce(const void* x, int64_t ldx, void* y, int64_t ldy, int ro
   const size_t units = (size_t)rows * cols / 4;
   PARE_REQUIRE(units * 16 <= p.slot_bytes, PARE_ERR_WORKSPACE);
   p.x = x; p.y = y; p.ldx = ldx; p.ldy = ldy; p.rows = rows; p.cols = cols; p.rank = rank; p.world = world;
-  int ctas = (int)((units + 2 * kThreads - 1) / (2 * kThreads));   // two units per thread
+  int ctas = (int)((units + 2 * kThreads - 1) / (2 * kThreads));   // CTAs that get units: two units per thread
   ctas = ctas < 1 ? 1 : (ctas > kMaxCtas ? kMaxCtas : ctas);
   p.units_per_cta = (int)((units + ctas - 1) / ctas);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  return dtype == PARE_F16 ? launch_pdl(peer_allreduce_kernel<__half>, dim3(ctas), dim3(kThreads), 0, s, p)
-                           : launch_pdl(peer_allreduce_kernel<__nv_bfloat16>, dim3(ctas), dim3(kThreads), 0, s, p);
+  // always the full grid: the CTAs beyond `ctas` find no units and only advance their epoch word (see the header)
+  return dtype == PARE_F16 ? launch_pdl(peer_allreduce_kernel<__half>, dim3(kMaxCtas), dim3(kThreads), 0, s, p)
+                           : launch_pdl(peer_allreduce_kernel<__nv_bfloat16>, dim3(kMaxCtas), dim3(kThreads), 0, s, p);
 }
 
 }  // extern "C"

@@ -13,12 +13,11 @@
 //              one 128-row x 128-byte box per 256-column stage, 128B swizzle) into a four-stage ring, requested up
 //              to three stages ahead; activation tiles by TMA (128B swizzle) one operand stage ahead of the MMA
 //   warp 9     one elected thread issues tcgen05.mma (UMMA 128 x MT x 16, fp32 accumulate in TMEM)
-// Per 64-column block a dequantizing thread reads 16 bytes of codes, turns them into exact
-// integers in the 16-bit float type by the mantissa trick of common.cuh, multiplies by the group
-// scale and writes four 16-byte chunks of the K-major, 128B-swizzled operand tile that the MMA
-// reads through a shared-memory descriptor.  Weights therefore reach the tensor core as
-// dtype((q - zero) * scale), which is what the reference's own dequantize-then-matmul path feeds
-// its GEMM (pare/layers/linear.py:129).
+// Per 64-column block a dequantizing thread reads 16 bytes of codes, computes (q - zero) * scale in fp32 (packed
+// two-wide fp32 instructions, codes read in place as subnormal floats: dequant_word below), rounds to the 16-bit
+// type and writes four 16-byte chunks of the K-major, 128B-swizzled operand tile that the MMA reads through a
+// shared-memory descriptor.  Weights therefore reach the tensor core as exactly dtype(fp32((q - zero) * scale)),
+// bit for bit what the reference's own dequantize-then-matmul path feeds its GEMM (pare/layers/linear.py:112-118, 129).
 // All mbarrier waits are bounded; on expiry the CTA records PARE_ERR_TIMEOUT, stops waiting,
 // frees its tensor memory and returns.
 
@@ -142,59 +141,77 @@ template <typename T>
 struct Pair;
 template <>
 struct Pair<__half> {
-  using V = __half2;
   static constexpr uint32_t kFmt = 0;
-  // fp16 operand tiles hold 256 * w: the low term of the scale expansion (~2^-12 of the scale) would
-  // otherwise be a subnormal half with a few significant bits.  A power of two does not change any
-  // rounding (|w| < 256), and the epilogue multiplies the accumulator by 2^-8 exactly.
-  static constexpr float kPre = 256.f;
-  __device__ static V splat(float f) { return __float2half2_rn(f); }
+  // (lo, hi) fp32 -> one word of two fp16, round to nearest even
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+  }
 };
 template <>
 struct Pair<__nv_bfloat16> {
-  using V = __nv_bfloat162;
   static constexpr uint32_t kFmt = 1;
-  static constexpr float kPre = 1.f;
-  __device__ static V splat(float f) { return __float2bfloat162_rn(f); }
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+  }
 };
 
-// one 32-bit word of codes -> 8 dequantized 16-bit values (slot order 0,4,1,5,2,6,3,7) as one 16-byte chunk.
-// The scale comes as a two-term expansion hi + lo in the 16-bit type; fma(d, hi, d * lo) rounds the exact
-// product d * (hi + lo) once, so the result is the 16-bit rounding of (q - zero) * scale computed in fp32 —
-// the weight the reference's eager path feeds its GEMM.
-template <typename T>
-__device__ __forceinline__ uint4 dequant_word(uint32_t w, float z, typename Pair<T>::V s_hi, typename Pair<T>::V s_lo);
-
-template <>
-__device__ __forceinline__ uint4 dequant_word<__half>(uint32_t w, float z, __half2 s_hi, __half2 s_lo) {
-  uint32_t p[4];
-  Nibbles<__half>::unpack(w, p);  // 1024+c (pairs 0,2), 1024+16c (pairs 1,3)
-  const __half2 off_lo = __float2half2_rn(1024.f + z), off_hi = __float2half2_rn(-(64.f + z));
-  const __half2 sixteenth = __float2half2_rn(0.0625f);
-  __half2 d[4];
-  d[0] = __hsub2(*reinterpret_cast<__half2*>(&p[0]), off_lo);
-  d[1] = __hfma2(*reinterpret_cast<__half2*>(&p[1]), sixteenth, off_hi);
-  d[2] = __hsub2(*reinterpret_cast<__half2*>(&p[2]), off_lo);
-  d[3] = __hfma2(*reinterpret_cast<__half2*>(&p[3]), sixteenth, off_hi);
-  uint32_t o[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __half2 v = __hfma2(d[i], s_hi, __hmul2(d[i], s_lo));
-    o[i] = *reinterpret_cast<const uint32_t*>(&v);
-  }
-  return make_uint4(o[0], o[1], o[2], o[3]);
+// Packed fp32 pairs (two independent IEEE operations per instruction).
+__device__ __forceinline__ void fma_pair(float& a, float& b, float m, float c) {   // (a, b) = (a, b) * m + c
+  asm("{\n\t.reg .b64 x, y, z;\n\t"
+      "mov.b64 x, {%0, %1};\n\t"
+      "mov.b64 y, {%2, %2};\n\t"
+      "mov.b64 z, {%3, %3};\n\t"
+      "fma.rn.f32x2 x, x, y, z;\n\t"
+      "mov.b64 {%0, %1}, x;\n\t}"
+      : "+f"(a), "+f"(b)
+      : "f"(m), "f"(c));
 }
-template <>
-__device__ __forceinline__ uint4 dequant_word<__nv_bfloat16>(uint32_t w, float z, __nv_bfloat162 s_hi, __nv_bfloat162 s_lo) {
-  uint32_t p[4];
-  Nibbles<__nv_bfloat16>::unpack(w, p);  // 128+c for all pairs
-  const __nv_bfloat162 off = __float2bfloat162_rn(128.f + z);
+__device__ __forceinline__ void mul_pair(float& a, float& b, float m) {   // (a, b) = (a, b) * m
+  asm("{\n\t.reg .b64 x, y;\n\t"
+      "mov.b64 x, {%0, %1};\n\t"
+      "mov.b64 y, {%2, %2};\n\t"
+      "mul.rn.f32x2 x, x, y;\n\t"
+      "mov.b64 {%0, %1}, x;\n\t}"
+      : "+f"(a), "+f"(b)
+      : "f"(m));
+}
+
+// Per (weight row, group) constants of the dequantization below.
+struct DqConst {
+  float zc[4];   // -zero * 2^(4k - 22)
+  float sc[4];   // scale * 2^(22 - 4k)
+  __device__ __forceinline__ void set(float scale, float zero) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      zc[k] = -zero * __int_as_float((127 + 4 * k - 22) << 23);
+      sc[k] = scale * __int_as_float((127 + 22 - 4 * k) << 23);
+    }
+  }
+};
+
+// One 32-bit word of codes -> 8 dequantized 16-bit values (slot order 0,4,1,5,2,6,3,7) as one 16-byte chunk, each
+// EXACTLY dtype(fp32((q - zero) * scale)): the weight the reference's eager path feeds its GEMM
+// (pare/layers/linear.py:112-118, 129: fp32 subtract, fp32 multiply, cast).  A code nibble left in place at bits
+// 4k .. 4k+3 and read as a float's bit pattern is the subnormal q * 2^(4k - 149); one fused multiply-add by 2^127 with
+// -zero * 2^(4k - 22) gives (q - zero) * 2^(4k - 22) with the single rounding of the reference's fp32 subtraction
+// (powers of two do not change a rounding; no rounding at all for the integer zero-points of the reference's
+// quantizers), one multiply by scale * 2^(22 - 4k) its fp32 product, one conversion per pair the cast.
+template <typename T>
+__device__ __forceinline__ uint4 dequant_word(uint32_t w, const DqConst& c) {
+  const uint32_t t = w >> 16;
+  constexpr float kTwo127 = 1.7014118346046923e38f;
   uint32_t o[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __nv_bfloat162 d = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&p[i]), off);
-    const __nv_bfloat162 v = __hfma2(d, s_hi, __hmul2(d, s_lo));
-    o[i] = *reinterpret_cast<const uint32_t*>(&v);
+  for (int k = 0; k < 4; ++k) {
+    float a = __uint_as_float(w & (0xFu << (4 * k)));   // code k
+    float b = __uint_as_float(t & (0xFu << (4 * k)));   // code k + 4
+    fma_pair(a, b, kTwo127, c.zc[k]);
+    mul_pair(a, b, c.sc[k]);
+    o[k] = Pair<T>::pack(a, b);
   }
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
@@ -335,16 +352,13 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
       const uint4 codes0 = ld_s128(raw_row + ((((kb & 3) * 2) ^ (r & 7)) << 4));
       const uint4 codes1 = ld_s128(raw_row + ((((kb & 3) * 2 + 1) ^ (r & 7)) << 4));
       const bool second = (kb & 2) != 0;   // which 128-column half of the stage
-      const float sq = second ? sc[1] : sc[0];
-      const float z = second ? zc[1] : zc[0];
-      const float sp = sq * Pair<T>::kPre;
-      const typename Pair<T>::V s_hi = Pair<T>::splat(sp);
-      const typename Pair<T>::V s_lo = Pair<T>::splat(sp - to_float<T>(from_float<T>(sp)));
+      DqConst dq;
+      dq.set(second ? sc[1] : sc[0], second ? zc[1] : zc[0]);
       const uint32_t wv[8] = {codes0.x, codes0.y, codes0.z, codes0.w, codes1.x, codes1.y, codes1.z, codes1.w};
       const uint32_t dst = s_u32(a_ring) + s * kStageBytes + grp * 16384 + a_row;
 #pragma unroll
       for (int wi = 0; wi < 8; ++wi) {
-        const uint4 v = dequant_word<T>(wv[wi], z, s_hi, s_lo);
+        const uint4 v = dequant_word<T>(wv[wi], dq);
         st_s128(dst + ((wi ^ (r & 7)) << 4), v.x, v.y, v.z, v.w);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // make the tile visible to the MMA unit
@@ -382,7 +396,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
       if (vec_out) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const T h = from_float<T>(__uint_as_float(v[i]) * (1.f / Pair<T>::kPre) + bv);
+          const T h = from_float<T>(__uint_as_float(v[i]) + bv);
           asm volatile("st.shared.u16 [%0], %1;" ::"r"(tbuf + (i * 32 + lane) * 2), "h"(*reinterpret_cast<const unsigned short*>(&h)) : "memory");
         }
         __syncwarp();
@@ -401,7 +415,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
         for (int i = 0; i < 16; ++i) {
           const int m = m0 + c + i;
           if (m < p.M) {
-            const float f = __uint_as_float(v[i]) * (1.f / Pair<T>::kPre);
+            const float f = __uint_as_float(v[i]);
             if (part)
               __stcg(part + (size_t)m * p.N + n, f);
             else
@@ -449,7 +463,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn encode_fn() {
+  static std::mutex mu;
   static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lock(mu);
   if (!fn) {
     void* sym = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -477,11 +493,12 @@ GemmPlan gemm_plan(int M, int N, int K) {
   // loads, epilogue: ~10) plus ~0.35 per 64-column block, plus the cross-CTA sum when K is split (~2).  What it
   // avoids is a second, nearly empty wave: 48 row tiles take 3 splits (144 CTAs), not 4 (192).
   const int tiles = row_tiles * g.mtiles;
+  const int sms = sm_count();
   int best_per = raw_stages;
   double best_cost = 1e30;
   for (int s = 1; s <= 16 && s <= raw_stages; ++s) {
     const int per = (raw_stages + s - 1) / s, s_eff = (raw_stages + per - 1) / per;
-    const int waves = (tiles * s_eff + 147) / 148;
+    const int waves = (tiles * s_eff + sms - 1) / sms;
     const double cost = waves * (10.0 + per * kRawKb * 0.35) + (s_eff > 1 ? 2.0 : 0.0);
     if (cost < best_cost - 1e-9) {
       best_cost = cost;

@@ -377,7 +377,6 @@ __global__ void w4a16_generic_kernel(const GemvParams p, const uint8_t* packed, 
 
 
 // ---- host side ----------------------------------------------------------------------
-int g_tune_kc = 0, g_tune_warps = 0;
 
 struct Plan {
   bool fast;
@@ -385,7 +384,6 @@ struct Plan {
   size_t smem;
 };
 
-constexpr int kSmCount = 148;
 constexpr size_t kSmemCap = 110 * 1024;
 
 size_t gemv_smem(int M, int MB, int nst, int warps, int rb) {
@@ -394,19 +392,18 @@ size_t gemv_smem(int M, int MB, int nst, int warps, int rb) {
          (size_t)warps * rb * MB * 128 * sizeof(float) + 256 + 16 + 128;
 }
 
-int g_tune_rb = 0;
-int g_tune_persist = 0;   // -1 disables the persistent schedule (experiments)
 
 Plan make_plan_rb(int M, int N, int K, int G, int rb_request);
 
 Plan make_plan(int M, int N, int K, int G) {
-  Plan pl = make_plan_rb(M, N, K, G, g_tune_rb);
+  Plan pl = make_plan_rb(M, N, K, G, 0);
   if (pl.fast && pl.rb == 2 && pl.smem > kSmemCap) pl = make_plan_rb(M, N, K, G, 1);  // tile too large with 32 rows
   return pl;
 }
 
 Plan make_plan_rb(int M, int N, int K, int G, int rb_request) {
   Plan pl{};
+  const int kSmCount = sm_count();
   pl.fast = (K % 256 == 0) && (G % 128 == 0);  // K ranges are cut in multiples of 256 columns (an even number of steps)
   if (!pl.fast) return pl;
   const int MB = M <= 8 ? 1 : 2;
@@ -417,10 +414,10 @@ Plan make_plan_rb(int M, int N, int K, int G, int rb_request) {
   if (rb != 1 && rb != 2) rb = 1;
   const int row_tiles = (N + 16 * rb - 1) / (16 * rb);
   // columns per CTA: bounded by the activation tile that must sit in shared memory beside the weights
-  int kc = g_tune_kc ? g_tune_kc : (M <= 4 ? 4096 : (M <= 8 ? 2048 : 1024));
+  int kc = M <= 4 ? 4096 : (M <= 8 ? 2048 : 1024);
   // very small layers only: cut K further until there is at least one CTA per SM (going through the
   // global split-K reduction costs more latency than it buys otherwise)
-  while (!g_tune_kc && kc > 512 && (long long)row_tiles * ((K + kc - 1) / kc) < kSmCount) kc >>= 1;
+  while (kc > 512 && (long long)row_tiles * ((K + kc - 1) / kc) < kSmCount) kc >>= 1;
   int cps = kc / 256;                     // 256-column chunks per CTA
   if (cps < 1) cps = 1;
   if (cps > chunks) cps = chunks;
@@ -435,8 +432,7 @@ Plan make_plan_rb(int M, int N, int K, int G, int rb_request) {
   const int max_steps = kMaxStepsPerWarp / rb;
   // enough CTAs to fill the machine three times over: fewer, longer warps (less per-warp overhead);
   // otherwise more warps per CTA to shorten each CTA's critical path
-  int warps = g_tune_warps ? g_tune_warps : ((nst >= 16 && (long long)row_tiles * splits < 3 * kSmCount) ? 8 : 4);
-  if (warps != 4 && warps != 8) warps = 4;
+  int warps = (nst >= 16 && (long long)row_tiles * splits < 3 * kSmCount) ? 8 : 4;
   if ((nst + warps - 1) / warps > max_steps || rb == 2) warps = 8;
   pl.warps = warps;
   pl.rb = rb;
@@ -449,13 +445,19 @@ Plan make_plan_rb(int M, int N, int K, int G, int rb_request) {
 template <typename T, int MB, int WARPS, bool META16, int RB, bool PROD = false>
 int launch_gemv(const GemvParams& p, const Plan& pl, cudaStream_t stream) {
   auto kern = w4a16_gemv_kernel<T, MB, WARPS, META16, RB, PROD>;
-  static bool attr_done[64] = {};  // per instantiation and device
+  // the shared-memory opt-in once per instantiation and device (a function-local static per template
+  // instantiation, guarded by a mutex: the entry points may be called from several host threads)
+  static std::mutex mu;
+  static bool attr_done[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return PARE_ERR_CUDA;
-  if (!attr_done[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemCap) != cudaSuccess)
-      return PARE_ERR_CUDA;
-    attr_done[dev] = true;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!attr_done[dev]) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemCap) != cudaSuccess)
+        return PARE_ERR_CUDA;
+      attr_done[dev] = true;
+    }
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.N + 16 * RB - 1) / (16 * RB), pl.splits, 1);
@@ -520,7 +522,7 @@ size_t gemv_workspace_bytes(int M, int N, int K, int G) {
   if (K % 256 == 0 && G % 128 == 0) splits = (size_t)(K / 256);  // upper bound on any plan
   if (splits > 64) splits = 64;
   // split-K partial sums of either schedule (the persistent one adds at most one 32-row block per SM)
-  return kCounterBytes + prep_bytes(m, K) + (splits * (size_t)m * N + (size_t)kSmCount * 32 * m) * sizeof(float);
+  return kCounterBytes + prep_bytes(m, K) + (splits * (size_t)m * N + (size_t)sm_count() * 32 * m) * sizeof(float);
 }
 
 // Called by pare_w4a16_forward for every chunk of at most 16 activation rows.
@@ -564,7 +566,7 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   PARE_REQUIRE((pl.steps_per_split + pl.warps - 1) / pl.warps <= kMaxStepsPerWarp / pl.rb, PARE_ERR_UNSUPPORTED);
   p.splits = pl.splits;
   p.steps_per_split = pl.steps_per_split;
-  const bool persist = g_tune_persist >= 0 && gemv_persist_supported(M, N, K, G, prod != nullptr);
+  const bool persist = gemv_persist_supported(M, N, K, G, prod != nullptr);
   const size_t need = kCounterBytes + prep_bytes(M, K) +
                       (persist ? gemv_persist_partial_floats(M, N, K) * sizeof(float)
                                : (pl.splits > 1 ? (size_t)pl.splits * M * N * sizeof(float) : 0));
@@ -634,15 +636,6 @@ int gemv_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_per
   const cudaError_t e = x_dtype == PARE_F16 ? cudaLaunchKernelEx(&cfg, w4a16_prep_kernel<__half>, p)
                                             : cudaLaunchKernelEx(&cfg, w4a16_prep_kernel<__nv_bfloat16>, p);
   return e == cudaSuccess ? PARE_OK : PARE_ERR_CUDA;
-}
-
-// Tuning override for experiments: schedule (-1 = tile kernel only, 1 / 2 = 16-row blocks per tile CTA, 0 = automatic),
-// columns per tile CTA (multiple of 256) and warps per tile CTA (4 or 8); 0 = automatic.
-void gemv_set_tuning(int schedule, int kc, int warps) {
-  g_tune_persist = schedule < 0 ? -1 : 0;
-  g_tune_rb = schedule == 1 || schedule == 2 ? schedule : 0;
-  g_tune_kc = kc;
-  g_tune_warps = warps;
 }
 
 }  // namespace pare

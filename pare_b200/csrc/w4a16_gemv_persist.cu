@@ -38,7 +38,6 @@ constexpr int kCW = 16;                // consumer warps
 constexpr int kEpi = 2;                // epilogue warps
 constexpr int kMaxRed = 4;             // exchange buffers at most
 constexpr int kThreads = (kCW + 1 + kEpi) * 32;   // consumers + producer + epilogue warps
-constexpr int kGrid = 148;
 
 struct StreamPlan {
   int n_tiles;    // row tiles
@@ -502,6 +501,7 @@ size_t persist_smem(int M, int sps, int depth, int rows, int red_bufs) {
 // nine to sixteen rows (two blocks: the activations take twice the shared memory, the tile half).
 StreamPlan make_stream_plan(int M, int N, int K) {
   StreamPlan pl{};
+  const int kGrid = sm_count();   // one resident CTA per SM
   const int steps = K >> 7;
   const int slice_steps = kCW * kStepsPW;
   pl.spw = kStepsPW;
@@ -547,7 +547,7 @@ constexpr int kPersistMinItems = 96;   // fewer items than this cannot occupy th
 bool gemv_persist_supported(int M, int N, int K, int G, bool producer) {
   if (G != 128 || M > 16 || (K % 256) != 0 || (N % kMaxRows) != 0 || N <= 0) return false;
   const StreamPlan pl = make_stream_plan(M, N, K);
-  if (pl.n_slices > kGrid) return false;
+  if (pl.n_slices > sm_count()) return false;
   if ((long long)(N / kMaxRows) * pl.n_slices < kPersistMinItems) return false;
   // Less than two whole items per CTA is all ramp (and cross-CTA reduction where pieces are involved): such
   // layers are faster as independent tiles at M <= 4 (measured: 6144 x 4096 takes 8.1 us here, 6.4 us

@@ -31,7 +31,6 @@ SIGNATURES: dict[str, tuple] = {
     "pare_w4a16_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "pare_w4a16_forward": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                 _i, _i, _i, _i, _vp, _sz, _vp]),
-    "pare_w4a16_set_tuning": (None, [_i, _i, _i]),
     "pare_w4a16_prepared_bytes": (_sz, [_i, _i]),
     "pare_w4a16_prepare": (_i, [_vp, _i, _i64, _vp, _vp, _i, _i, _vp, _vp]),
     "pare_w4a16_forward_prepared": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
@@ -49,7 +48,6 @@ SIGNATURES: dict[str, tuple] = {
                                    _vp, _vp, _i64, _i64, _vp,
                                    _vp, _i64, _i64, _vp, C.c_float,
                                    _i, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
-    "pare_kivi_attn_set_tuning": (None, [_i]),
     "pare_prefill_attn": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
                                _i, _i, _i, _i, _i, _i, C.c_float, _i, _vp]),
     "pare_rmsnorm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, C.c_float, _i, _vp]),

@@ -120,7 +120,10 @@ class QuantizedLinear(nn.Module):
             # per-token dynamic INT8 fake-quantization of the activations (SmoothQuant W8A8)
             step = x.abs().amax(dim=-1, keepdim=True).clamp(min=1e-6) / 127.0
             x = ((x / step).round().clamp(-128, 127) * step).to(x.dtype)
-        return nn.functional.linear(x, weight, self.bias)
+        bias = self.bias
+        if bias is not None and bias.dtype != x.dtype:   # e.g. an imported fp16 bias under fp32 activations
+            bias = bias.to(x.dtype)
+        return nn.functional.linear(x, weight, bias)
 
     # -- CUDA path -----------------------------------------------------------
     def _kernel_group_size(self) -> int:

@@ -16,6 +16,13 @@ holding seeded inputs and the outputs the reference produced for them on CPU:
   kivi_cache.npz       ``QuantizedKVCache.update`` over a 96-token prefill and 40 decode steps
                        (bits 4, G 32, residual 64): final dense K/V, token counts per step, and
                        fp32 grouped-query attention over the final cache
+  ref_ckpt/            a directory written by the reference's ``save_quantized`` (``model.safetensors`` +
+                       ``pare_config.json``) for a two-layer MLP (512 -> 768 -> 512, biases) quantized by the
+                       reference's ``pare.quantize`` (RTN INT4 g128), and ``ref_ckpt_io.npz``: inputs for 1 and 64
+                       rows with the outputs of the reference's own model on them (CPU, fp32)
+  awq_gemm_layer.npz   the AutoAWQ GEMM tensors the reference's exporter (``pare/model/export_awq.py:75-94``)
+                       makes of a 512 -> 256 layer with bias, the layer's own packed weight / scale / zero, inputs
+                       and the reference layer's fp32 outputs
 """
 
 from __future__ import annotations
@@ -102,6 +109,49 @@ def main(ref_root: str) -> None:
         HERE / "kivi_cache.npz",
         k_all=k_all.numpy(), v_all=v_all.numpy(), q=q.numpy(),
         full_k=fk.numpy(), full_v=fv.numpy(), counts=np.array(counts, dtype=np.int32), attn=attn.numpy(),
+    )
+    # ---- a checkpoint written by the reference's save_quantized ------------------------
+    import pare
+    from pare.model.io import save_quantized
+
+    class MLP(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up_proj = nn.Linear(512, 768, bias=True)
+            self.down_proj = nn.Linear(768, 512, bias=True)
+
+        def forward(self, x):
+            return self.down_proj(torch.relu(self.up_proj(x)))
+
+    torch.manual_seed(6)
+    model = MLP()
+    pare.quantize(model, QuantConfig(bits=4, scheme="rtn", granularity="per_group", group_size=128))
+    assert isinstance(model.up_proj, QuantizedLinear) and isinstance(model.down_proj, QuantizedLinear)
+    save_quantized(model, HERE / "ref_ckpt")
+    torch.manual_seed(7)
+    x1 = torch.randn(1, 512, dtype=torch.float16)
+    x64 = torch.randn(64, 512, dtype=torch.float16)
+    with torch.no_grad():
+        np.savez_compressed(HERE / "ref_ckpt_io.npz", x1=x1.numpy(), x64=x64.numpy(),
+                            y1=model(x1.float()).numpy(), y64=model(x64.float()).numpy(),
+                            up1=model.up_proj(x1.float()).numpy(), up64=model.up_proj(x64.float()).numpy())
+
+    # ---- the reference exporter's AutoAWQ GEMM tensors of one layer ------------------------
+    from pare.model.export_awq import _to_awq_linear
+
+    torch.manual_seed(8)
+    lin = nn.Linear(512, 256, bias=True)
+    ql = QuantizedLinear.from_linear(lin, QuantConfig(bits=4, scheme="rtn", granularity="per_group", group_size=128))
+    awq = _to_awq_linear(ql, 128)
+    torch.manual_seed(9)
+    x = torch.randn(64, 512, dtype=torch.float16)
+    with torch.no_grad():
+        y = ql.forward(x.float())
+    np.savez_compressed(
+        HERE / "awq_gemm_layer.npz",
+        qweight=awq.qweight.numpy(), qzeros=awq.qzeros.numpy(), scales=awq.scales.numpy(), bias=awq.bias.numpy(),
+        packed=ql.packed_weight.numpy(), scale=ql.scale.numpy(), zero=ql.zero.numpy(), bias32=ql.bias.detach().numpy(),
+        x=x.numpy(), y=y.numpy(),
     )
     print("fixtures written to", HERE)
 

@@ -231,6 +231,16 @@ def test_decode_attention_longest_benchmark_context(bits, cuda_lib):
     _check_attn(out.float().cpu().numpy(), ref, ref32, torch.float16)
 
 
+@pytest.mark.parametrize("bits", [4, 2])
+@pytest.mark.parametrize("bsz,ctx", [(16, 4096), (4, 16384)])
+def test_decode_attention_benchmark_grid_cells(bsz, ctx, bits, cuda_lib):
+    """Cells of the benchmark grid that the smaller cases do not reach: batch 16 at 4096 tokens and batch 4 at
+    16384 tokens, 28 query / 4 KV heads (seven query heads per KV head), 4- and 2-bit caches; same bars."""
+    out, ref, cache, ref32 = _attn_case(bsz, 4, 28, ctx, torch.float16, bits=bits, seed=bsz + ctx)
+    assert out.shape == (bsz, 28, 1, D)
+    _check_attn(out.float().cpu().numpy(), ref, ref32, torch.float16)
+
+
 def _check_attn(o, ref, ref32, dtype):
     """Two bars.  (1) Tight, against fp32 attention over the reference's reconstruction BEFORE its final
     cast (``_reconstruct``, pare/kv_cache.py:315-325): max <= 1e-2, mean <= 1e-3 (2.5e-3 for bf16

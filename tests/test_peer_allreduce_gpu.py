@@ -2,8 +2,9 @@
 
 Two child processes, one per GPU, NCCL only for the handle exchange.  Checks: the sum equals the fp32
 sum of the ranks' inputs rounded once to the tensor dtype (bit-exact: rank-order fp32 addition), identical
-on both ranks, over many back-to-back calls (double-buffered slots), eagerly and from a replayed CUDA graph,
-and the status word stays clean.
+on both ranks, over many back-to-back calls (double-buffered slots), over a queue of calls of different shapes
+with no host synchronisation between them while one rank launches late, eagerly and from a replayed CUDA
+graph, and the status word stays clean.
 """
 
 import os
@@ -37,6 +38,20 @@ for dtype in (torch.float16, torch.bfloat16):
             y = ar(parts[rank])
             ref = sum(p.float() for p in parts).to(dtype)
             ok &= bool(torch.equal(y, ref))
+# calls of different shapes queued back to back with no host synchronisation in between, one rank launching late:
+# a unit changes its owning CTA from call to call, every result must still be the exact sum
+import time
+seq = [(1, 2048), (1, 2048), (1, 2048), (1, 2400), (1, 2400), (16, 4096), (1, 2048), (3, 1024), (1, 2400)] * 3
+g = torch.Generator(device="cuda").manual_seed(7)
+ins = [[torch.randn(r, c, device="cuda", generator=g).half() for _ in range(world)] for r, c in seq]
+torch.cuda.synchronize(); dist.barrier()
+if rank == 1:
+    time.sleep(0.3)
+outs = [ar(parts[rank]) for parts in ins]
+torch.cuda.synchronize()
+for parts, y in zip(ins, outs):
+    ok &= bool(torch.equal(y, sum(p.float() for p in parts).half()))
+ok &= ar.status(torch.device("cuda", rank)) == 0
 # replayed graph: 20 replays of two chained all-reduces
 x = torch.randn(2, 4096, device="cuda").half() * (rank + 1)
 s = torch.cuda.Stream(); s.wait_stream(torch.cuda.current_stream())

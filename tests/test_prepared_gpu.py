@@ -255,3 +255,65 @@ def test_decode_stack_prefill_equals_token_by_token(cuda_lib):
     yc = torch.cat([c.prefill(x[:, :40]), c.prefill(x[:, 40:])], dim=1)
     mx, mean = ow.rel_err(yc.float().cpu().numpy(), ya.float().cpu().numpy())
     assert mx <= 3e-2 and mean <= 3e-3, (mx, mean)
+
+
+@pytest.mark.parametrize("m", [1, 3])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_decode_stack_step_against_fp32_restatement(m, dtype, cuda_lib):
+    """Two blocks of a small Llama-shaped stack, one decode step, against an fp32 restatement of the block written
+    here from the oracle's pieces (not against the stack's other route): RMSNorm -> q|k|v linear -> rotary embedding of
+    q and the new key -> KIVI cache update -> attention over the cache -> o linear -> residual add -> RMSNorm ->
+    gate|up linear -> SwiGLU -> down linear -> residual add.  Catches wiring errors both routes of the stack would
+    share (residual ping-pong, head slicing, rotary position).  The restatement keeps fp32 between the stages where
+    the kernels round to the activation dtype (eleven hand-overs in two blocks), hence max <= 3e-2, mean <= 3e-3
+    for fp16 and 1e-1 / 1.2e-2 for bf16 (8 significant bits per hand-over)."""
+    from oracle import kivi as ok
+    shape = (1024, 2048, 8, 2, 128, 2)
+    hidden, ffn, hq, hkv, d, layers = shape
+    ctx = 224 + 5                                              # 96 compressed tokens + a window that is not full
+    stack = DecodeStack(shape, dtype=dtype, max_seq_len=512, seed=3)
+    g = torch.Generator().manual_seed(21)
+    caches = []
+    for layer in range(layers):
+        k = torch.randn(m, hkv, ctx, d, generator=g)
+        v = torch.randn(m, hkv, ctx, d, generator=g)
+        k[..., 17] *= 10.0
+        k, v = k.to(dtype), v.to(dtype)
+        stack.cache._append(layer, k.cuda(), v.cuda())
+        c = ok.Cache(4, 32, 128)
+        c.update(k.float().numpy(), v.float().numpy())
+        caches.append(c)
+    for blk in stack.blocks:                                    # non-trivial norm weights
+        blk.norm1.copy_((1 + 0.1 * torch.randn(hidden, generator=g)).to(dtype))
+        blk.norm2.copy_((1 + 0.1 * torch.randn(hidden, generator=g)).to(dtype))
+    x = torch.randn(m, hidden, generator=g).to(dtype)
+    y = stack(x.cuda()).float().cpu().numpy()
+
+    rows = stack.rope.cpu().numpy()
+    pos = ctx
+
+    def rms(h, w):
+        return h / np.sqrt((h * h).mean(-1, keepdims=True) + 1e-5) * w
+
+    def lin(layer, a):
+        n = layer.out_features
+        return ow.linear(a, layer.packed_weight.cpu().numpy(), layer.scale.cpu().numpy().reshape(n, -1),
+                         layer.zero.cpu().numpy().reshape(n, -1))
+
+    h = x.float().numpy()
+    for i, blk in enumerate(stack.blocks):
+        qkv = lin(blk.qkv, rms(h, blk.norm1.float().cpu().numpy()))
+        q = qkv[:, : hq * d].reshape(m, hq, 1, d)
+        k1 = qkv[:, hq * d:(hq + hkv) * d].reshape(m, hkv, 1, d)
+        v1 = qkv[:, (hq + hkv) * d:].reshape(m, hkv, 1, d)
+        q, k1 = ok.apply_rope(q, rows[pos]), ok.apply_rope(k1, rows[pos])
+        fk, fv = caches[i].update(k1.astype(np.float32), v1.astype(np.float32))
+        attn = ok.decode_attention(q.astype(np.float32), fk, fv).reshape(m, hq * d)
+        h = h + lin(blk.o, attn)
+        gu = lin(blk.gate_up, rms(h, blk.norm2.float().cpu().numpy()))
+        gate, up = gu[:, :ffn], gu[:, ffn:]
+        h = h + lin(blk.down, gate / (1 + np.exp(-gate)) * up)
+    mx, mean = ow.rel_err(y, h)
+    bars = (3e-2, 3e-3) if dtype == torch.float16 else (1e-1, 1.2e-2)
+    assert mx <= bars[0] and mean <= bars[1], (mx, mean)
+    assert stack.cache.seq_len(0) == stack.cache.seq_len(1) == ctx + 1

@@ -247,6 +247,26 @@ def _oracle_rounded_weights(ql, x, dtype, **kw):
     return y
 
 
+def _check_tensor_core(y, ql, x, dtype, **kw):
+    """Bars of the tensor-core path.  (1) Against the reference's eager semantics (weights cast to the activation
+    dtype, pare/layers/linear.py:129; fp32 accumulation): the kernel's operand is exactly that cast, so the stated
+    bars hold as they are: max <= 1e-2, mean <= 1e-3 (2.5e-3 for bf16 outputs).  (2) Against the fp32-weight oracle
+    the reference's own cast is the dominant error (about 6e-4 mean / 2e-2 max in fp16, 5e-3 / 1.5e-1 in bf16 on
+    these layers); it is measured here, oracle against oracle, and the kernel must stay within 1.5x of it plus the
+    stated bars."""
+    yn = y.float().cpu().numpy()
+    ref_cast = _oracle_rounded_weights(ql, x, dtype, **kw)
+    mean_bar = 2.5e-3 if dtype == torch.bfloat16 else MEAN_REL
+    mx, mean = ow.rel_err(yn, ref_cast)
+    assert mx <= MAX_REL and mean <= mean_bar, (mx, mean)
+    ref32 = oracle_y(ql, x, **{k: v for k, v in kw.items() if k in ("g_idx", "input_scale")})
+    if ql.bias is not None:
+        ref32 = ref32 - ql.bias.detach().float().cpu().numpy() + ql.bias.detach().to(dtype).float().cpu().numpy()
+    noise_mx, noise_mean = ow.rel_err(ref_cast, ref32)
+    mx2, mean2 = ow.rel_err(yn, ref32)
+    assert mx2 <= 1.5 * noise_mx + MAX_REL and mean2 <= 1.5 * noise_mean + mean_bar, (mx2, mean2, noise_mx, noise_mean)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("m", [17, 32, 64, 100, 128, 200, 256])
 @pytest.mark.parametrize("shape", [(512, 1024), (1000, 512), (4096, 4096)])
@@ -258,34 +278,126 @@ def test_tensor_core_path_matches_oracle(shape, m, dtype, cuda_lib):
     y = w4a16_forward(x, ql.packed_weight, ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous(), 128,
                       bias=ql.bias.detach().to(dtype))
     assert y.shape == (m, n) and y.dtype == dtype
-    # bar 1: the reference's eager semantics (weights cast to the activation dtype, fp32 accumulate).  Mean
-    # bars as everywhere else (1e-3 fp16, 2.5e-3 bf16).  The max bar is 2e-2 / 2e-1: a fraction of a percent
-    # of the weights land one ulp of the 16-bit type off the reference's cast (the scale goes through a
-    # two-term 16-bit expansion), which only shows at outputs near zero.
-    mx, mean = ow.rel_err(y.float().cpu().numpy(), _oracle_rounded_weights(ql, x, dtype))
-    assert mx <= (2e-1 if dtype == torch.bfloat16 else 2e-2) and mean <= (2.5e-3 if dtype == torch.bfloat16 else MEAN_REL), (mx, mean)
-    # bar 2: the fp32-weight oracle.  Casting the weights to the activation dtype (what the reference's eager
-    # path does too) alone costs ~6e-4 mean / 2e-2 max in fp16 and ~5e-3 mean / 1.5e-1 max in bf16 here.
-    mx, mean = ow.rel_err(y.float().cpu().numpy(), oracle_y(ql, x) - ql.bias.detach().float().cpu().numpy()
-                          + ql.bias.detach().to(dtype).float().cpu().numpy())
-    assert mx <= (2e-1 if dtype == torch.bfloat16 else 3e-2) and mean <= (6e-3 if dtype == torch.bfloat16 else 1e-3), (mx, mean)
+    _check_tensor_core(y, ql, x, dtype)
     y2 = w4a16_forward(x, ql.packed_weight, ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous(), 128,
                        bias=ql.bias.detach().to(dtype))
     assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_tensor_core_operand_is_the_reference_cast_bit_for_bit(dtype, cuda_lib):
+    """One-hot activation rows pick single weights out of the tensor-core path: every output is one operand value,
+    so it must equal ``dtype(fp32((q - zero) * scale))`` -- the weight the reference's eager path casts
+    (pare/layers/linear.py:112-118, 129) -- exactly, for integer and for fractional zero-points."""
+    n, k = 256, 512
+    ql = make_ql(n, k, seed=77).cuda()
+    for fractional in (False, True):
+        scale = ql.scale.squeeze(-1).contiguous()
+        zero = ql.zero.squeeze(-1).contiguous()
+        if fractional:
+            zero = zero + torch.rand_like(zero) * 0.5
+        x = torch.eye(k, device="cuda", dtype=dtype)
+        y = w4a16_forward(x, ql.packed_weight, scale, zero, 128)           # [k, n] = W^T
+        w = ow.dequantize(ql.packed_weight.cpu().numpy(), scale.cpu().numpy(), zero.cpu().numpy())
+        want = torch.from_numpy(w).to(dtype).t().contiguous()
+        assert torch.equal(y.cpu(), want)
+
+
+def _act_order_layer(n, k, g, seed, device="cuda"):
+    """Random INT4 layer with a seeded random column -> group map (what GPTQ act-order stores): codes uniform,
+    zero-points 6..10, scales about 0.02 / 4.6 so that weights have standard deviation 0.02."""
+    gen = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(k, generator=gen)
+    g_idx = torch.empty(k, dtype=torch.int32)
+    g_idx[perm] = (torch.arange(k) // g).to(torch.int32)
+    codes = torch.randint(0, 16, (n, k), generator=gen, dtype=torch.int32)
+    scale = (0.02 / 4.61) * (0.75 + 0.5 * torch.rand(n, k // g, 1, generator=gen))
+    zero = torch.randint(6, 11, (n, k // g, 1), generator=gen).float()
+    ql = QuantizedLinear(codes, scale, zero, QuantConfig(bits=4, scheme="gptq", group_size=g, act_order=True),
+                         None, k, n, g_idx=g_idx).to(device)
+    ql.use_kernel = True
+    return ql, g_idx
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (1024, 4096), (4096, 14336)])
+def test_act_order_on_layer_shapes_over_the_row_sweep(shape, cuda_lib):
+    """GPTQ act-order (a seeded random permutation of the input channels mapped to groups) on the 8B-shaped
+    projections, fp16 activations, 1 to 256 rows: the streaming kernel up to 16 rows, the tensor-core kernel above."""
+    n, k = shape
+    ql, g_idx = _act_order_layer(n, k, 128, seed=n + k)
+    packed, s2, z2 = ql.packed_weight.cpu().numpy(), ql.scale.cpu().numpy().reshape(n, -1), ql.zero.cpu().numpy().reshape(n, -1)
+    w32 = ow.dequantize(packed, s2, z2, g_idx.numpy())
+    w16 = torch.from_numpy(w32).half().float().numpy()
+    for m in (1, 4, 16, 64, 128, 256):
+        torch.manual_seed(m)
+        x = torch.randn(m, k, device="cuda", dtype=torch.float16)
+        y = ql(x).float().cpu().numpy()
+        xn = x.float().cpu().numpy()
+        ref32 = xn @ w32.T
+        if m <= 16:
+            mx, mean = ow.rel_err(y, ref32)
+            assert mx <= MAX_REL and mean <= MEAN_REL, (m, mx, mean)
+        else:
+            ref_cast = xn @ w16.T
+            mx, mean = ow.rel_err(y, ref_cast)
+            assert mx <= MAX_REL and mean <= MEAN_REL, (m, mx, mean)
+            noise_mx, noise_mean = ow.rel_err(ref_cast, ref32)
+            mx2, mean2 = ow.rel_err(y, ref32)
+            assert mx2 <= 1.5 * noise_mx + MAX_REL and mean2 <= 1.5 * noise_mean + MEAN_REL, (m, mx2, mean2)
+
+
+@pytest.mark.parametrize("shape", [(8192, 8192), (57344, 8192), (8192, 28672), (10240, 8192)])
+def test_70b_shaped_layers(shape, cuda_lib):
+    """The 70B-shaped projections (hidden 8192, fused gate|up 2 x 28672, down over 28672 columns = seven K slices of
+    the persistent schedule, fused q|k|v 10240), bf16 activations as the decode stack runs them, 1 to 256 rows."""
+    from pare_b200.decode import synthetic_linear
+    n, k = shape
+    ql = synthetic_linear(n, k, seed=n + k, device="cuda")
+    s2, z2 = ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous()
+    packed = ql.packed_weight.cpu().numpy()
+    sn, zn = s2.cpu().numpy(), z2.cpu().numpy()
+    xs = {}
+    for m in (1, 4, 16, 64, 256):
+        torch.manual_seed(m)
+        xs[m] = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    ys = {m: w4a16_forward(x, ql.packed_weight, s2, z2, 128) for m, x in xs.items()}
+    assert all(torch.equal(ys[m], w4a16_forward(xs[m], ql.packed_weight, s2, z2, 128)) for m in (1, 16))
+    ref32 = {m: np.empty((m, n), dtype=np.float32) for m in xs}
+    ref_cast = {m: np.empty((m, n), dtype=np.float32) for m in xs if m > 16}
+    for r0 in range(0, n, 4096):                      # the oracle in row blocks: the fp32 weight never exists whole
+        w = ow.dequantize(packed[r0:r0 + 4096], sn[r0:r0 + 4096], zn[r0:r0 + 4096])
+        w16 = torch.from_numpy(w).to(torch.bfloat16).float().numpy()
+        for m, x in xs.items():
+            xn = x.float().cpu().numpy()
+            ref32[m][:, r0:r0 + 4096] = xn @ w.T
+            if m > 16:
+                ref_cast[m][:, r0:r0 + 4096] = xn @ w16.T
+    for m in xs:
+        y = ys[m].float().cpu().numpy()
+        if m <= 16:
+            mx, mean = ow.rel_err(y, ref32[m])
+            assert mx <= MAX_REL and mean <= 2.5e-3, (m, mx, mean)
+            assert ow.rel_err(y, torch.from_numpy(ref32[m]).to(torch.bfloat16).float().numpy())[1] <= MEAN_REL
+        else:
+            mx, mean = ow.rel_err(y, ref_cast[m])
+            assert mx <= MAX_REL and mean <= 2.5e-3, (m, mx, mean)
+            noise_mx, noise_mean = ow.rel_err(ref_cast[m], ref32[m])
+            mx2, mean2 = ow.rel_err(y, ref32[m])
+            assert mx2 <= 1.5 * noise_mx + MAX_REL and mean2 <= 1.5 * noise_mean + 2.5e-3, (m, mx2, mean2)
 
 
 def test_tensor_core_path_options(cuda_lib):
     """act-order gather, run-time input scale and per_channel groups through the tile kernel."""
     torch.manual_seed(21)
     n, k, m = 384, 1024, 96
-    ql = make_ql(n, k, seed=4)
+    ql, g_idx = _act_order_layer(n, k, 128, seed=4, device="cpu")
     s = torch.exp(torch.randn(k) * 0.3)
     ql.input_scale = s
     ql = ql.cuda()
     ql.use_kernel = True
     x = torch.randn(m, k, device="cuda", dtype=torch.float16)
-    check(ql(x), _oracle_rounded_weights(ql, x, torch.float16, input_scale=s.numpy()), torch.float16)
+    _check_tensor_core(ql(x), ql, x, torch.float16, input_scale=s.numpy(), g_idx=g_idx.numpy())
     qc = make_ql(256, 512, seed=6, granularity="per_channel").cuda()
     qc.use_kernel = True
     xc = torch.randn(40, 512, device="cuda", dtype=torch.float16)
-    check(qc(xc), _oracle_rounded_weights(qc, xc, torch.float16), torch.float16)
+    _check_tensor_core(qc(xc), qc, xc, torch.float16)
