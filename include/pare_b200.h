@@ -268,7 +268,7 @@ int pare_w4a16_forward_static(const void* x, int x_dtype, int64_t ldx,
  *                            64-byte CUDA IPC handle (to be sent to the peers by any host channel)
  *   pare_peer_buffer_open    maps a peer's buffer from its handle; _close unmaps; _destroy frees
  *   pare_peer_allreduce      y = sum over ranks of x, [rows][cols] F16/BF16, cols % 4 == 0,
- *                            rows*cols*4 <= (buffer_bytes - 4096) / (2 * world); buffers = HOST array
+ *                            rows*cols*4 <= (buffer_bytes - 4096) / 2 / (2 * world); buffers = HOST array
  *                            of `world` device pointers (own buffer at index `rank`); 2 <= world <= 8;
  *                            every rank makes the same sequence of calls; capturable in a CUDA graph
  *   pare_peer_status         0 or PARE_ERR_TIMEOUT (a wait for a peer ran out); synchronises `stream`
@@ -280,6 +280,29 @@ int pare_peer_buffer_destroy(void* ptr);
 int pare_peer_status(const void* own_buffer, void* stream);
 int pare_peer_allreduce(const void* x, int64_t ldx, void* y, int64_t ldy, int rows, int cols, int dtype,
                         int rank, int world, void* const* buffers, size_t buffer_bytes, void* stream);
+
+/* Row-parallel W4A16 linears of a tensor-parallel model with the sum over the ranks INSIDE the kernel: the
+ * prepared / produced forwards above (M <= 16), where the thread that finishes an output element stores its fp32
+ * partial into that element's slot of every rank's exchange buffer (plain 8-byte peer stores, each with its own
+ * validity mark) and adds the ranks' partials from its own buffer in rank order as they arrive (bounded waits ->
+ * PARE_ERR_TIMEOUT in the buffer's status word, read with pare_peer_status).  y is the complete sum on every rank,
+ * identical bits everywhere, rounded once; there is no separate all-reduce launch.  No counterpart in the reference
+ * (single GPU).  buffers / buffer_bytes / rank / world as for pare_peer_allreduce (the buffers' data area is split
+ * between the two calls, so both may be used on the same buffers); M * N * 8 bytes must fit a slot:
+ * (buffer_bytes - 4096) / 2 / (2 * world).  Every rank makes the same sequence of calls; a bias given on several
+ * ranks is added once per rank that gives it (give it on one).  PARE_ERR_UNSUPPORTED for shapes the streaming
+ * kernels do not take (K % 256, group % 128): run the plain call and pare_peer_allreduce then. */
+int pare_w4a16_forward_prepared_allreduce(const void* prepared, int x_dtype,
+                                          const uint8_t* packed, const float* scale, const float* zero, const void* meta_h2,
+                                          const void* bias, void* y, int64_t ldy, int M, int N, int K, int group_size,
+                                          void* workspace, size_t workspace_bytes,
+                                          int rank, int world, void* const* buffers, size_t buffer_bytes, void* stream);
+int pare_w4a16_forward_produced_allreduce(int producer, const void* a, const void* b, const void* c, void* resid_out,
+                                          int64_t lda, float eps, int x_dtype,
+                                          const uint8_t* packed, const float* scale, const float* zero, const void* meta_h2,
+                                          const void* bias, void* y, int64_t ldy, int M, int N, int K, int group_size,
+                                          void* workspace, size_t workspace_bytes,
+                                          int rank, int world, void* const* buffers, size_t buffer_bytes, void* stream);
 
 #ifdef __cplusplus
 }

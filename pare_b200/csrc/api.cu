@@ -1,4 +1,5 @@
 // extern "C" surface of libpare_b200: argument checks and dispatch only.
+#include "peer.cuh"
 #include "prep.cuh"
 
 namespace pare {
@@ -15,7 +16,8 @@ size_t gemv_workspace_bytes(int M, int N, int K, int G);
 int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale,
                  const float* zero, const void* meta_h2, const int32_t* col_perm, const float* input_scale,
                  const void* bias, void* y, int64_t ldy, int M, int N, int K, int G, void* workspace,
-                 size_t workspace_bytes, cudaStream_t stream, const void* prepared, const ProducerArgs* prod);
+                 size_t workspace_bytes, cudaStream_t stream, const void* prepared, const ProducerArgs* prod,
+                 const PeerCtx* peer = nullptr);
 int gemv_prepare(const void* x, int x_dtype, int64_t ldx, const int32_t* col_perm, const float* input_scale, int M, int K,
                  void* prepared, cudaStream_t stream);
 bool gemv_persist_supported(int M, int N, int K, int G, bool producer = false);
@@ -139,6 +141,83 @@ int pare_w4a16_forward_produced(int producer, const void* a, const void* b, cons
   if (rc != PARE_OK) return rc;
   return pare::gemv_forward(nullptr, x_dtype, K, packed, scale, zero, meta_h2, nullptr, nullptr, bias, y, ldy, M, N, K,
                             group_size, workspace, workspace_bytes, s, prepared, nullptr);
+}
+
+namespace {
+// exchange buffers of a tensor-parallel group -> the kernels' view of them
+int make_peer_ctx(int rank, int world, void* const* buffers, size_t buffer_bytes, pare::PeerCtx* pc) {
+  PARE_REQUIRE(buffers && world >= 2 && world <= pare::kPeerMaxRanks && rank >= 0 && rank < world, PARE_ERR_SHAPE);
+  PARE_REQUIRE(buffer_bytes >= pare::kPeerHeaderBytes + 2 * 4096, PARE_ERR_WORKSPACE);
+  *pc = pare::PeerCtx{};
+  for (int q = 0; q < world; ++q) {
+    PARE_REQUIRE(buffers[q] != nullptr, PARE_ERR_SHAPE);
+    pc->buf[q] = reinterpret_cast<unsigned char*>(buffers[q]);
+  }
+  pc->rank = rank;
+  pc->world = world;
+  pc->data_off = pare::peer_fused_offset(buffer_bytes);
+  pc->slot_bytes = ((buffer_bytes - pc->data_off) / (2 * (size_t)world)) & ~(size_t)255;
+  PARE_REQUIRE(pc->slot_bytes > 0, PARE_ERR_WORKSPACE);
+  return PARE_OK;
+}
+}  // namespace
+
+int pare_w4a16_forward_prepared_allreduce(const void* prepared, int x_dtype, const uint8_t* packed, const float* scale,
+                                          const float* zero, const void* meta_h2, const void* bias, void* y, int64_t ldy,
+                                          int M, int N, int K, int group_size, void* workspace, size_t workspace_bytes,
+                                          int rank, int world, void* const* buffers, size_t buffer_bytes, void* stream) {
+  PARE_REQUIRE(M > 0 && N > 0 && K > 0 && group_size > 0, PARE_ERR_SHAPE);
+  PARE_REQUIRE((K % 2) == 0 && (K % group_size) == 0 && ldy >= N, PARE_ERR_SHAPE);
+  PARE_REQUIRE(M <= 16, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE(x_dtype == PARE_F16 || x_dtype == PARE_BF16, PARE_ERR_DTYPE);
+  PARE_REQUIRE(prepared && packed && y && (meta_h2 || (scale && zero)), PARE_ERR_SHAPE);
+  pare::PeerCtx pc;
+  const int rc = make_peer_ctx(rank, world, buffers, buffer_bytes, &pc);
+  if (rc != PARE_OK) return rc;
+  return pare::gemv_forward(nullptr, x_dtype, K, packed, scale, zero, meta_h2, nullptr, nullptr, bias, y, ldy, M, N, K,
+                            group_size, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream), prepared, nullptr, &pc);
+}
+
+int pare_w4a16_forward_produced_allreduce(int producer, const void* a, const void* b, const void* c, void* resid_out,
+                                          int64_t lda, float eps, int x_dtype, const uint8_t* packed, const float* scale,
+                                          const float* zero, const void* meta_h2, const void* bias, void* y, int64_t ldy,
+                                          int M, int N, int K, int group_size, void* workspace, size_t workspace_bytes,
+                                          int rank, int world, void* const* buffers, size_t buffer_bytes, void* stream) {
+  PARE_REQUIRE(M > 0 && M <= 16 && N > 0 && K > 0 && group_size > 0, PARE_ERR_SHAPE);
+  PARE_REQUIRE((K % 256) == 0 && (group_size % 128) == 0 && (K % group_size) == 0 && ldy >= N, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE(x_dtype == PARE_F16 || x_dtype == PARE_BF16, PARE_ERR_DTYPE);
+  PARE_REQUIRE(a && packed && y && (meta_h2 || (scale && zero)), PARE_ERR_SHAPE);
+  PARE_REQUIRE(pare::aligned16(a) && lda % 8 == 0, PARE_ERR_ALIGN);
+  if (producer == PARE_PRODUCER_RMSNORM) {
+    PARE_REQUIRE(c != nullptr && lda >= K && resid_out != a, PARE_ERR_SHAPE);
+    PARE_REQUIRE(pare::aligned16(c) && (b == nullptr || pare::aligned16(b)) && (resid_out == nullptr || pare::aligned16(resid_out)),
+                 PARE_ERR_ALIGN);
+  } else if (producer == PARE_PRODUCER_SILU_MUL) {
+    PARE_REQUIRE(lda >= 2 * (int64_t)K, PARE_ERR_SHAPE);
+  } else {
+    return PARE_ERR_UNSUPPORTED;
+  }
+  pare::PeerCtx pc;
+  int rc = make_peer_ctx(rank, world, buffers, buffer_bytes, &pc);
+  if (rc != PARE_OK) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const pare::ProducerArgs prod{producer, a, b, c, resid_out, lda, eps};
+  rc = pare::gemv_forward(nullptr, x_dtype, K, packed, scale, zero, meta_h2, nullptr, nullptr, bias, y, ldy, M, N, K,
+                          group_size, workspace, workspace_bytes, s, nullptr, &prod, &pc);
+  if (rc != PARE_ERR_UNSUPPORTED) return rc;
+  // no fused staging for this shape: stand-alone glue kernel into the workspace's prepared-activation area, then the
+  // prepared forward with the exchange in its epilogue
+  PARE_REQUIRE(workspace && workspace_bytes >= pare_w4a16_workspace_bytes(M, N, K, group_size), PARE_ERR_WORKSPACE);
+  void* prepared = reinterpret_cast<unsigned char*>(workspace) + pare::gemv::kCounterBytes;
+  if (producer == PARE_PRODUCER_RMSNORM) {
+    PARE_REQUIRE(lda == K, PARE_ERR_UNSUPPORTED);
+    rc = pare_rmsnorm_residual(a, b, c, resid_out, nullptr, prepared, M, K, eps, x_dtype, stream);
+  } else {
+    rc = pare_silu_mul(a, nullptr, prepared, M, K, lda, x_dtype, stream);
+  }
+  if (rc != PARE_OK) return rc;
+  return pare::gemv_forward(nullptr, x_dtype, K, packed, scale, zero, meta_h2, nullptr, nullptr, bias, y, ldy, M, N, K,
+                            group_size, workspace, workspace_bytes, s, prepared, nullptr, &pc);
 }
 
 }  // extern "C"

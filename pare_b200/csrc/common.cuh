@@ -38,17 +38,27 @@ inline int sm_count() {
   return cached[dev];
 }
 
-// cudaFuncSetAttribute(max dynamic shared memory) once per (kernel, device), thread-safe.
-template <typename Kern>
-inline bool ensure_smem_attr(Kern kern, int bytes) {
+// cudaFuncSetAttribute(max dynamic shared memory) once per (kernel, device), thread-safe.  Keyed by the kernel's
+// address: instantiations of one kernel template share a function-pointer type, so a static per type would not do.
+inline bool ensure_smem_attr(const void* kern, int bytes) {
   static std::mutex mu;
-  static bool done[64] = {};
+  static const void* seen[256][2] = {};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return false;
+  const void* tag = reinterpret_cast<const void*>(static_cast<uintptr_t>(dev) + 1);
   std::lock_guard<std::mutex> lock(mu);
-  if (!done[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
-    done[dev] = true;
+  int free_slot = -1;
+  for (int i = 0; i < 256; ++i) {
+    if (seen[i][0] == kern && seen[i][1] == tag) return true;
+    if (seen[i][0] == nullptr) {
+      free_slot = i;
+      break;
+    }
+  }
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  if (free_slot >= 0) {
+    seen[free_slot][0] = kern;
+    seen[free_slot][1] = tag;
   }
   return true;
 }

@@ -3,6 +3,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "peer.cuh"
 
 namespace pare {
 namespace gemv {
@@ -49,6 +50,8 @@ struct GemvParams {
   void* resid_out;      // rmsnorm: x + delta is stored here by the first CTA (may be NULL; must not alias x)
   int64_t lda;
   float eps;
+  // row-parallel layer of a tensor-parallel model: the ranks' partial outputs are added inside the epilogue (peer.cuh)
+  PeerCtx peer;
 };
 
 // ---- mbarrier / bulk-copy primitives -----------------------------------------------------

@@ -5,35 +5,52 @@
 // (pare/kv_cache.py:183-186).  This kernel reads the packed cache directly and never
 // materialises K or V.  Dequantization is folded into the operands that are small:
 //     S[h][t] = sum_c (q[h][c] * ks[g][c]) * code_k[t][c]  +  sum_c q[h][c] * kz[g][c]
-//     O[h][c] = sum_t (p[h][t] * vs[t]) * (code_v[t][c] - 8)  +  sum_t p[h][t] * (vz[t] + 8 vs[t])
-// so the 4-bit codes go to the warp-level MMA unit as exact integer-valued fp16 (OR-ed into
-// the mantissa of 1024.0 and the offset subtracted again, see common.cuh; logits are
-// exponentiated, so nothing large is left to cancel in the accumulator) and the
-// per-channel / per-token scales multiply the
-// query row (once per 32-token group) and the probabilities instead of every cache element.
-// The up to 8 query heads that share a KV head sit in the 8 MMA columns, so the cache is read
-// once for all of them.
+//     O[h][c] = sum_t (p[h][t] * vs[t]) * code_v[t][c]     +  sum_t p[h][t] * vz[t]
+// so the codes go to the warp-level MMA unit as integer-valued fp16 (OR-ed into the mantissa of
+// 1024.0, see common.cuh) and the per-channel / per-token scales multiply the query row (once per
+// token group) and the probabilities instead of every cache element.  The up to 8 query heads that
+// share a KV head sit in the 8 MMA columns, so the cache is read once for all of them.
 //
-// Grid: (splits, kv heads, batch).  Each split owns a chunk of compressed tokens (split-KV
-// for long contexts) or up to 64 tokens of the full-precision residual window.  A CTA first
-// puts everything it will read into shared memory with a handful of bulk async copies on one
-// mbarrier (codes, scales and zeros of a chunk are contiguous in the cache layout), so the
-// phases that follow never wait on global memory: (A) scores of its chunk, (B) softmax
-// statistics and scaled probabilities in operand order (warp-shuffle reductions), (C) P.V with
-// the V codes as the MMA A operand.  Partial (max, sum, O) go to a workspace; the CTA that
-// arrives last at the per-(batch, head) counter merges them in split order and resets the counter.
+// Grid: (splits, kv heads, batch).  A split is either a run of up to `nb` blocks of 128 compressed
+// tokens or up to 64 tokens of the full-precision residual window.
 //
-// Launched with programmatic stream serialization: the compressed cache of this step is
-// immutable, so its copies are issued before griddepcontrol.wait and overlap the tail of the
-// kernel that produces q; the residual window and q are read after the wait.  The newest
-// token can be handed in separately (new_k / new_v, e.g. straight out of the q|k|v projection):
-// the CTA that owns the last window position attends to it and stores it into the window.
+// A compressed split is a software pipeline over its blocks, with no CTA-wide barrier inside:
+//   * a ring of stages is kept full by one lane of the last value warp: the six pieces of a block (key
+//     codes, key scales, key zeros, value codes, value scales, value zeros) are contiguous in the cache
+//     layout and arrive by six bulk async copies on one mbarrier; a slot is refilled as soon as all eight
+//     warps have released it.  The compressed cache is immutable during a decode step, so the first
+//     copies start before griddepcontrol.wait and overlap the kernel that produces q.
+//   * four score warps, one per 32 tokens of the block: scaled-query operand for the token group
+//     (registers), scores by MMA, block maximum (one named barrier among the four warps), running
+//     maximum / sum, and the probabilities times the value scale written to a two-stage shared
+//     buffer in the operand order of the next MMA (online softmax: the rescale factor of the block
+//     goes with it);
+//   * four value warps, 32 channels each: O = O * alpha + codes_v^T . P per block, accumulators in
+//     registers for the whole split.
+// Codes enter the MMA as exact small integers (the mantissa offset is removed per element: attention outputs
+// and logits are small differences of large sums, so an offset left in the accumulator costs the digits
+// that matter); value codes are centred (c - 8) so that the products are half as large.
+// Partial (max, sum, O) of a split go to a workspace; the CTA that arrives last at the per-(batch,
+// head) counter merges them in split order and resets the counter.
 //
-// The merged output can also be written as prepared activations of the next W4A16 linear
-// (operand order + per-step sums, see prep.cuh): head h is exactly one 128-column step.
+// The residual window, q and the newest token are read after the dependency wait.  The newest token
+// can be handed in separately (new_k / new_v, e.g. straight out of the q|k|v projection): the CTA
+// that owns the last window position attends to it and stores it into the window.  The merged
+// output can also be written as prepared activations of the next W4A16 linear (operand order +
+// per-step sums, see prep.cuh): head h is exactly one 128-column step.
+//
+// Every mbarrier wait is bounded: on expiry the thread records PARE_ERR_TIMEOUT in the workspace
+// status word and never waits again; the CTA still reaches every named barrier and returns.
+
+#include <cstdlib>
+#include <type_traits>
 
 #include "gemv_common.cuh"
 #include "prep.cuh"
+
+#ifndef PARE_ATTN_MODE
+#define PARE_ATTN_MODE 3   // bit 0: two-term scaled query, bit 1: two-term probabilities (see the kernel template)
+#endif
 
 namespace pare {
 namespace {
@@ -42,25 +59,52 @@ using gemv::bulk_load;
 using gemv::kStatusIndex;
 using gemv::mbar_expect_tx;
 using gemv::mbar_init;
-using gemv::mbar_wait;
+using gemv::mbar_test;
 using gemv::smem_u32;
 
-constexpr int kAttnWarps = 8;
-constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr int kScoreWarps = 4;
+constexpr int kValueWarps = 4;
+constexpr int kComputeThreads = (kScoreWarps + kValueWarps) * 32;   // 256
+constexpr int kAttnThreads = kComputeThreads;
+constexpr int kAttnWarps = 8;            // the residual branch and the merge use all warps alike
 constexpr int kD = 128;
 constexpr int kHeads = 8;
-constexpr int kMaxVG = 4;        // value scale / zero groups per token at most (32 channels each)
-// bytes of shared memory in front of q: mbarrier, flag, statistics [2 + vg][8]
-__host__ __device__ constexpr int attn_header(int vg) { return vg == 1 ? 128 : 256; }
-constexpr int kMaxChunk = 512;
+constexpr int kMaxVG = 4;                // value scale / zero groups per token at most (32 channels each)
+constexpr int kBlk = 128;                // compressed tokens per pipeline block
+constexpr int kMaxStages = 4;
+constexpr int kMaxNb = 16;               // blocks per compressed split the planner chooses at most
+constexpr int kMaxSplits = 250;          // splits per (batch, head) the merge takes
 constexpr int kResChunk = 64;            // residual tokens per split
 constexpr int kResPitch = 320;           // bytes per staged residual row (256 + 64: conflict-free 16-byte reads down a column)
 constexpr int kMaxResidual = 512;
-constexpr size_t kCounterInts = gemv::kCounterInts;
+constexpr int kPHead = 320;              // bytes per head row of a probability operand buffer (256 + 64)
 constexpr size_t kCounterBytes = gemv::kCounterBytes;
-constexpr size_t kAttnSmemCap = 200 * 1024;
 constexpr float kNegBig = -1e30f;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
 constexpr int kQS = 132;   // floats per staged query row: channel c at (c>>3 & 3)*32 + (c>>5)*8 + (c&7), rows 16 bytes off a bank period
+constexpr uint32_t kSpin = 1u << 22;
+
+// ---- shared-memory map (bytes) ----
+constexpr int kOffBars = 0;       // data_full[4] data_empty[4] p_full[2] p_empty[2] res_bar
+constexpr int kOffLast = 104;
+constexpr int kOffStM = 128;      // [8]
+constexpr int kOffStL = 160;      // [8]
+constexpr int kOffAlpha = 320;    // [2][8]
+constexpr int kOffGmax = 384;     // [2][4][8]
+constexpr int kOffFin = 640;      // [4 score warps][8 heads][1 + kMaxVG]: sum, constant term per value group
+constexpr int kFinStride = 1 + kMaxVG;
+constexpr int kOffQ = 2048;       // [8][kQS] fp32
+constexpr int kOffP = kOffQ + kHeads * kQS * 4;            // 6272
+__host__ __device__ constexpr int p_stage_bytes(int vg) { return vg * 2 * kHeads * kPHead; }   // per stage: [vg][hi, lo][8][kPHead]
+__host__ __device__ constexpr int ring_offset(int vg) { return kOffP + 2 * p_stage_bytes(vg); }
+constexpr size_t kAttnSmemBudget = 112 * 1024;   // two CTAs per SM
+
+// bytes of one pipeline stage (a block of 128 compressed tokens)
+__host__ __device__ inline int stage_bytes(int group, int bits, int vg) {
+  return kBlk * (kD * bits / 8) + 2 * (kBlk / group) * kD * 4 + kD * (kBlk * bits / 8) + 2 * kBlk * 4 * vg;
+}
+
 // Rotary position embedding of eight consecutive channels c8 .. c8+7 of a head (pairing i <-> i + D/2): own = the
 // channels themselves, other = their partners, cs = cos | sin of the position.  Separately rounded products and
 // sum (no fused multiply-add), then rounded to T: what an fp32 restatement computes.
@@ -108,10 +152,9 @@ struct AttnParams {
   float4* prep_tab;
   float sm_scale;
   int B, Hq, H, rep, group, cap, n_comp;
-  int vg;        // value scale / zero groups per token (1: one per token; 4: one per 32 channels)
-  int chunk, n_csplit, n_split;
-  int s_stride;  // floats per score row
-  int p_stride;  // bytes per probability row
+  int nb;              // blocks of 128 compressed tokens per compressed split
+  int stages;          // pipeline stages in shared memory
+  int n_csplit, n_split;
   float* part_o;
   float* part_ml;
   int* counters;
@@ -120,14 +163,6 @@ struct AttnParams {
 __device__ __forceinline__ uint32_t h2_bits(float lo, float hi) {
   const __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-// (a, b) -> hi = fp16 pair, lo = fp16 pair of the rounding residuals
-__device__ __forceinline__ void split_h2(float a, float b, uint32_t& hi, uint32_t& lo) {
-  const __half2 h = __floats2half2_rn(a, b);
-  const __half2 l = __floats2half2_rn(a - __low2float(h), b - __high2float(h));
-  hi = *reinterpret_cast<const uint32_t*>(&h);
-  lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
 template <typename T>
@@ -141,9 +176,20 @@ __device__ __forceinline__ uint32_t pair_to_h2<__nv_bfloat16>(uint32_t raw) {
 
 __device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// bytes of the operand stage of a compressed split
-__host__ __device__ inline int stage_bytes(int chunk, int group, int bits, int vg) {
-  return chunk * (kD * bits / 8) + 2 * (chunk / group) * kD * 4 + (chunk / 128) * kD * (128 * bits / 8) + 2 * chunk * 4 * vg;
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void named_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// Bounded wait; `dead` is sticky per thread: after one expiry nothing waits any more.
+__device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, int* status, bool& dead) {
+  if (dead) return;
+#pragma unroll 1
+  for (uint32_t i = 0; i < kSpin; ++i)
+    if (mbar_test(bar, parity)) return;
+  dead = true;
+  atomicExch(status, PARE_ERR_TIMEOUT);
 }
 
 // codes - CENTER of one word as exact fp16 pairs: four pairs (c_k, c_k+4) at 4 bits, eight pairs (c_j, c_j+8) at 2 bits
@@ -153,14 +199,32 @@ __device__ __forceinline__ void unpack_exact(uint32_t w, uint32_t (&p)[BITS == 4
   else unpack_codes2_exact<CENTER>(w, p);
 }
 
-template <typename T, int BITS, int VG>
-__global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const AttnParams p) {
+// byte offset, inside a head row of a probability buffer, of token tl (0..127) of the block: the operand order of the
+// value MMA ([4 code words of a lane][4 lanes of a quad: the token's 32-token range, XOR-ed with the head pair so that
+// neither the scattered stores nor the 16-byte loads meet bank conflicts][8 halves in pair order])
+template <int BITS>
+__device__ __forceinline__ int p_offset(int tl, int head) {
+  const int chunk = ((tl >> 5) ^ (head >> 1)) & 3;
+  if constexpr (BITS == 4) {
+    const int pos = tl & 7;
+    return ((tl >> 3) & 3) * 64 + chunk * 16 + ((((pos & 3) << 1) | (pos >> 2)) * 2);
+  } else {
+    const int e = tl & 15, j = e & 7;
+    return ((((tl >> 4) & 1) * 2 + (j >> 2)) * 64) + chunk * 16 + (((j & 3) * 2 + (e >> 3)) * 2);
+  }
+}
+
+// MODE bit 0: the scaled query q * k_scale as a two-term fp16 expansion (hi + rounding residual); bit 1: the same for the
+// probabilities times the value scale.  Single terms are the faster, less accurate choice.
+template <typename T, int BITS, int VG, int MODE>
+__global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
+  constexpr bool K2 = (MODE & 1) != 0, P2 = (MODE & 2) != 0;
   constexpr int NW = BITS == 4 ? 4 : 2;          // code words of the 32 channels / tokens a lane owns
   constexpr int PW = BITS == 4 ? 4 : 8;          // fp16 pairs per word
   constexpr int LB = 4 * BITS;                   // bytes of those 32 codes
   constexpr int KROW = kD * BITS / 8;            // bytes of a token's key codes
-  constexpr int VROW = 128 * BITS / 8;           // bytes of a channel's value codes in a 128-token block
+  constexpr int VROW = kBlk * BITS / 8;          // bytes of a channel's value codes in a 128-token block
   constexpr int VCENTER = BITS == 4 ? 8 : 2;     // value codes are centred (halves the magnitude of the products)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
@@ -168,59 +232,72 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
   const size_t bh = (size_t)b * p.H + h;
   const bool is_res = (split >= p.n_csplit);
 
-  // header: mbarrier, flags, statistics | q fp32 | scores | probabilities (hi, lo) | operand stage
-  uint64_t* bar_p = reinterpret_cast<uint64_t*>(smem);
-  int* s_last = reinterpret_cast<int*>(smem + 8);
-  float* st_m = reinterpret_cast<float*>(smem + 16);                // [8]
-  float* st_l = st_m + kHeads;
-  float* st_c = st_l + kHeads;                                      // [vg][8]
-  float* qf = reinterpret_cast<float*>(smem + attn_header(VG));         // [8][kQS], channels in q_pos order
-  float* S = qf + kHeads * kQS;                                     // [8][s_stride]
-  // per value group: [8][p_stride] fp16 hi parts, then [8][p_stride] fp16 lo parts
-  unsigned char* P = reinterpret_cast<unsigned char*>(S + kHeads * p.s_stride);
-  const int pgs = 2 * kHeads * p.p_stride;           // bytes per value group
-  unsigned char* stage = P + VG * pgs;             // 128-byte aligned by construction of the strides
-  const uint32_t bar = smem_u32(bar_p);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
+  const uint32_t data_full = smem_u32(bars), data_empty = smem_u32(bars + 4), p_full = smem_u32(bars + 8),
+                 p_empty = smem_u32(bars + 10), res_bar = smem_u32(bars + 12);
+  int* s_last = reinterpret_cast<int*>(smem + kOffLast);
+  float* st_m = reinterpret_cast<float*>(smem + kOffStM);
+  float* st_l = reinterpret_cast<float*>(smem + kOffStL);
+  float* alpha_s = reinterpret_cast<float*>(smem + kOffAlpha);  // [2][8]
+  float* gmax_s = reinterpret_cast<float*>(smem + kOffGmax);    // [2][4][8]
+  float* fin_s = reinterpret_cast<float*>(smem + kOffFin);      // [4][8][kFinStride]
+  float* qf = reinterpret_cast<float*>(smem + kOffQ);           // [8][kQS], channels in q_pos order
+  unsigned char* Pring = smem + kOffP;
+  unsigned char* stage = smem + ring_offset(VG);
   int* status = p.counters + kStatusIndex;
+  bool dead = false;
 
-  int valid;           // tokens this CTA attends to
-  int chunk_start = 0;
+  const int G = p.group;
+  const int sbytes = stage_bytes(G, BITS, VG);
+  // pieces of a stage
+  const int off_ks = kBlk * KROW, off_kz = off_ks + (kBlk / G) * kD * 4, off_vc = off_kz + (kBlk / G) * kD * 4;
+  const int off_vs = off_vc + kD * VROW, off_vz = off_vs + kBlk * 4 * VG;
+
   if (threadIdx.x == 0) {
-    mbar_init(bar, 1);
+    for (int i = 0; i < kMaxStages; ++i) {
+      mbar_init(data_full + i * 8, 1);
+      mbar_init(data_empty + i * 8, kAttnWarps);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(p_full + i * 8, kScoreWarps);
+      mbar_init(p_empty + i * 8, kValueWarps);
+    }
+    mbar_init(res_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   pdl_launch_dependents();
+  __syncthreads();   // the barriers are initialised for everybody
 
-  // operand stage of a compressed split
-  const int ngr_full = p.chunk / p.group;
-  unsigned char* kc_s = stage;
-  float* ks_s = reinterpret_cast<float*>(kc_s + p.chunk * KROW);
-  float* kz_s = ks_s + ngr_full * kD;
-  unsigned char* vc_s = reinterpret_cast<unsigned char*>(kz_s + ngr_full * kD);
-  float* vs_s = reinterpret_cast<float*>(vc_s + (p.chunk / 128) * kD * VROW);
-  float* vz_s = vs_s + p.chunk * VG;               // [token][vg] both
+  // blocks of this compressed split
+  const int nblk_total = (p.n_comp + kBlk - 1) / kBlk;
+  const int blk0 = split * p.nb;
+  const int nblk = is_res ? 0 : min(p.nb, nblk_total - blk0);
 
-  if (!is_res) {
-    chunk_start = split * p.chunk;
-    valid = min(p.chunk, p.n_comp - chunk_start);
-    if (threadIdx.x == 0) {
-      // the compressed cache does not change during a decode step: fetch before the dependency wait
-      const int ngroups = valid / p.group, nblk = (valid + 127) >> 7;
-      const size_t grow = bh * (p.cap / p.group) + chunk_start / p.group;
-      mbar_expect_tx(bar, valid * KROW + 2 * ngroups * kD * 4 + nblk * kD * VROW + 2 * valid * 4 * VG);
-      bulk_load(smem_u32(kc_s), p.k_codes + (bh * p.cap + chunk_start) * (size_t)KROW, valid * KROW, bar);
-      bulk_load(smem_u32(ks_s), p.k_scale + grow * kD, ngroups * kD * 4, bar);
-      bulk_load(smem_u32(kz_s), p.k_zero + grow * kD, ngroups * kD * 4, bar);
-      bulk_load(smem_u32(vc_s), p.v_codes + (bh * (p.cap / 128) + (chunk_start >> 7)) * (size_t)(kD * VROW), nblk * kD * VROW, bar);
-      bulk_load(smem_u32(vs_s), p.v_scale + (bh * p.cap + chunk_start) * VG, valid * 4 * VG, bar);
-      bulk_load(smem_u32(vz_s), p.v_zero + (bh * p.cap + chunk_start) * VG, valid * 4 * VG, bar);
-    }
-  }
-  __syncthreads();   // the barrier is initialised for everybody
+  // one block of the compressed cache into its ring slot (six bulk copies on the slot's barrier); issued by one thread
+  auto issue_block = [&](int i) {
+    const int slot = i % p.stages;
+    const int t0 = (blk0 + i) * kBlk;
+    const int valid = min(kBlk, p.n_comp - t0), ngroups = valid / G;
+    const size_t grow = bh * (p.cap / G) + t0 / G;
+    const uint32_t dst = smem_u32(stage + slot * sbytes), bar = data_full + slot * 8;
+    mbar_expect_tx(bar, valid * KROW + 2 * ngroups * kD * 4 + kD * VROW + 2 * valid * 4 * VG);
+    bulk_load(dst, p.k_codes + (bh * p.cap + t0) * (size_t)KROW, valid * KROW, bar);
+    bulk_load(dst + off_ks, p.k_scale + grow * kD, ngroups * kD * 4, bar);
+    bulk_load(dst + off_kz, p.k_zero + grow * kD, ngroups * kD * 4, bar);
+    bulk_load(dst + off_vc, p.v_codes + (bh * (p.cap / kBlk) + (t0 >> 7)) * (size_t)(kD * VROW), kD * VROW, bar);
+    bulk_load(dst + off_vs, p.v_scale + (bh * p.cap + t0) * VG, valid * 4 * VG, bar);
+    bulk_load(dst + off_vz, p.v_zero + (bh * p.cap + t0) * VG, valid * 4 * VG, bar);
+  };
+  // the compressed cache does not change during a decode step, so the first stages are fetched before the dependency wait
+  if (warp == kAttnWarps - 1 && lane == 0)
+    for (int i = 0; i < nblk && i < p.stages; ++i) issue_block(i);
+
   pdl_wait();   // q, the newest token and the residual window may come from the previous kernels
 
   unsigned char* rk_s = stage;
   unsigned char* rv_s = stage + kResChunk * kResPitch;
+  int valid = 0;           // tokens a residual split attends to
+  int chunk_start = 0;
   if (is_res) {
     chunk_start = (split - p.n_csplit) * kResChunk;
     valid = min(kResChunk, p.n_res - chunk_start);
@@ -230,11 +307,11 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
     const bool has_new = p.new_k != nullptr && chunk_start + valid == p.n_res;
     const int ncopy = has_new ? valid - 1 : valid;
     if (warp == 0) {
-      if (lane == 0) mbar_expect_tx(bar, ncopy * 2 * kD * (int)sizeof(T));
+      if (lane == 0) mbar_expect_tx(res_bar, ncopy * 2 * kD * (int)sizeof(T));
       __syncwarp();
       for (int i = lane; i < ncopy; i += 32) {
-        bulk_load(smem_u32(rk_s + i * kResPitch), rk + (int64_t)(chunk_start + i) * p.r_st, kD * sizeof(T), bar);
-        bulk_load(smem_u32(rv_s + i * kResPitch), rv + (int64_t)(chunk_start + i) * p.r_st, kD * sizeof(T), bar);
+        bulk_load(smem_u32(rk_s + i * kResPitch), rk + (int64_t)(chunk_start + i) * p.r_st, kD * sizeof(T), res_bar);
+        bulk_load(smem_u32(rv_s + i * kResPitch), rv + (int64_t)(chunk_start + i) * p.r_st, kD * sizeof(T), res_bar);
       }
     } else if (warp == 1 && has_new) {
       const bool is_v = lane >= 16;
@@ -250,7 +327,7 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
   // ---- query rows of this KV head as fp32 (rows >= rep are zero) ----
   {
     const T* qg = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_sb + (int64_t)h * p.rep * p.q_sh;
-    for (int i = threadIdx.x; i < kHeads * (kD / 8); i += kAttnThreads) {
+    for (int i = threadIdx.x; i < kHeads * (kD / 8); i += kComputeThreads) {
       const int hh = i >> 4, c8 = (i & 15) * 8;
       float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
       if (hh < p.rep) {
@@ -276,214 +353,369 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       *reinterpret_cast<float4*>(qf + hh * kQS + q_pos(c8) + 4) = hi4;
     }
   }
-  __syncthreads();
-  mbar_wait(bar, 0, status);   // bounded; a timeout is reported through the status word
-
-  float o_acc[4] = {0.f, 0.f, 0.f, 0.f};   // phase C result, layout depends on the branch
+  named_sync(1, kComputeThreads);
 
   if (!is_res) {
-    const int G = p.group;
-    const int ngroups = valid / G;
-
-    // ================= phase A: scores =================
-    // one (group, 16-token tile) item per warp when that occupies no more than the eight warps (short chunks:
-    // the per-group operand preparation is repeated, the serial tile loop is cut); else one group per warp
-    const int tpg = G / 16;
-    const bool split_tiles = ngroups * tpg <= kAttnWarps;
-    const int n_items = split_tiles ? ngroups * tpg : ngroups;
-    for (int item = warp; item < n_items; item += kAttnWarps) {
-      const int gl = split_tiles ? item / tpg : item;
-      const int tile_lo = split_tiles ? item - gl * tpg : 0, tile_hi = split_tiles ? tile_lo + 1 : tpg;
-      const unsigned char* krow = kc_s + (gl * G) * KROW + tig * LB;
-      const float* ks = ks_s + gl * kD + tig * 8;   // rows in kmeta_pos order: channels 8u .. 8u+7 of this lane at u * 32 + tig * 8
-      const float* kz = kz_s + gl * kD + tig * 8;
+    const float scale2 = p.sm_scale * kLog2e;   // scores in base-2 units: p = exp2(s2 - m2)
+    if (warp < kScoreWarps) {
+      // ================= score warps: tokens [32 warp, 32 warp + 32) of every block =================
+      // this lane's query row (head gid, channels 32 tig .. + 31 in runs of eight) stays in shared memory and is read
+      // once per token group
       const float* qrow = qf + gid * kQS + tig * 8;
-      // q * scale as a two-term fp16 expansion (hi + lo, ~22 bits): a single fp16 rounding of
-      // this operand would move the logits by more than the reference's own fp16 cast of K^.
-      // xh / xl[w * PW + j]: the operand pair that meets pair j of code word w.
-      uint32_t xh[16], xl[16];
-      float bias = 0.f;
+      // where this lane's four (tile, row half) tokens go in a probability row, per head of its pair
+      int poff[2][2][2];
 #pragma unroll
-      for (int h2 = 0; h2 < 2; ++h2) {   // sixteen channels (two runs of eight) at a time
-        float pr[2][8];
+      for (int tile = 0; tile < 2; ++tile)
 #pragma unroll
-        for (int u2 = 0; u2 < 2; ++u2) {
-          const int u = h2 * 2 + u2;
-          const float4 s0 = *reinterpret_cast<const float4*>(ks + u * 32);
-          const float4 s1 = *reinterpret_cast<const float4*>(ks + u * 32 + 4);
-          const float4 z0 = *reinterpret_cast<const float4*>(kz + u * 32);
-          const float4 z1 = *reinterpret_cast<const float4*>(kz + u * 32 + 4);
-          const float4 q0 = *reinterpret_cast<const float4*>(qrow + u * 32);
-          const float4 q1 = *reinterpret_cast<const float4*>(qrow + u * 32 + 4);
-          bias = fmaf(q0.x, z0.x, bias); bias = fmaf(q0.y, z0.y, bias); bias = fmaf(q0.z, z0.z, bias); bias = fmaf(q0.w, z0.w, bias);
-          bias = fmaf(q1.x, z1.x, bias); bias = fmaf(q1.y, z1.y, bias); bias = fmaf(q1.z, z1.z, bias); bias = fmaf(q1.w, z1.w, bias);
-          pr[u2][0] = q0.x * s0.x; pr[u2][1] = q0.y * s0.y; pr[u2][2] = q0.z * s0.z; pr[u2][3] = q0.w * s0.w;
-          pr[u2][4] = q1.x * s1.x; pr[u2][5] = q1.y * s1.y; pr[u2][6] = q1.z * s1.z; pr[u2][7] = q1.w * s1.w;
-        }
-        if constexpr (BITS == 4) {   // a word is one run of eight channels: pairs (c_k, c_k+4)
+        for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
-          for (int u2 = 0; u2 < 2; ++u2)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) split_h2(pr[u2][k], pr[u2][k + 4], xh[(h2 * 2 + u2) * 4 + k], xl[(h2 * 2 + u2) * 4 + k]);
-        } else {                      // a word is both runs: pairs (c_j, c_j+8)
-#pragma unroll
-          for (int j = 0; j < 8; ++j) split_h2(pr[0][j], pr[1][j], xh[h2 * 8 + j], xl[h2 * 8 + j]);
-        }
-      }
-      bias += __shfl_xor_sync(0xffffffffu, bias, 1);
-      bias += __shfl_xor_sync(0xffffffffu, bias, 2);
-      const float c0 = __shfl_sync(0xffffffffu, bias, (tig * 2) * 4);
-      const float c1 = __shfl_sync(0xffffffffu, bias, (tig * 2 + 1) * 4);
+          for (int e = 0; e < 2; ++e) {
+            const int tl = 32 * warp + 16 * tile + gid + 8 * hf, head = 2 * tig + e;
+            poff[tile][hf][e] = head * kPHead + p_offset<BITS>(tl, head);
+          }
 
-      for (int tile = tile_lo; tile < tile_hi; ++tile) {
-        uint32_t wa[NW], wb[NW];
-        if constexpr (BITS == 4) {
-          const uint4 wa4 = *reinterpret_cast<const uint4*>(krow + (tile * 16 + gid) * KROW);
-          const uint4 wb4 = *reinterpret_cast<const uint4*>(krow + (tile * 16 + gid + 8) * KROW);
-          wa[0] = wa4.x; wa[1] = wa4.y; wa[2] = wa4.z; wa[3] = wa4.w;
-          wb[0] = wb4.x; wb[1] = wb4.y; wb[2] = wb4.z; wb[3] = wb4.w;
+      float m_run[2] = {kNegBig, kNegBig}, l_run[2] = {0.f, 0.f};
+      float z_run[VG][2];   // sum of p * (value zero + centre * value scale): the constant term of the output
+#pragma unroll
+      for (int g = 0; g < VG; ++g) z_run[g][0] = z_run[g][1] = 0.f;
+
+      for (int i = 0; i < nblk; ++i) {
+        const int slot = i % p.stages, ps = i & 1;
+        const unsigned char* st = stage + slot * sbytes;
+        const int t0 = (blk0 + i) * kBlk;
+        const int bvalid = min(kBlk, p.n_comp - t0);
+        const int wvalid = max(0, min(32, bvalid - 32 * warp));   // 0, 16 or 32 tokens of this warp (16 only when G == 16)
+        wait_bar(data_full + slot * 8, (i / p.stages) & 1, status, dead);
+
+        float s[2][4];
+        uint32_t xh[16], xl[K2 ? 16 : 1];
+        float c0 = 0.f, c1 = 0.f;
+        // ---- scaled query of a token group: x = q * k_scale as fp16 operand pairs (two-term: value + rounding
+        // residual, ~22 bits), and the constant sum_c q k_zero of the group for this lane's two heads ----
+        auto prep = [&](int gl) {
+          const float* ks = reinterpret_cast<const float*>(st + off_ks) + gl * kD + tig * 8;   // rows in kmeta_pos order
+          const float* kz = reinterpret_cast<const float*>(st + off_kz) + gl * kD + tig * 8;
+          float bias = 0.f;
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {   // sixteen channels (two runs of eight) at a time
+            float pr[2][8];
+#pragma unroll
+            for (int u2 = 0; u2 < 2; ++u2) {
+              const int u = h2 * 2 + u2;
+              const float4 s0 = *reinterpret_cast<const float4*>(ks + u * 32);
+              const float4 s1 = *reinterpret_cast<const float4*>(ks + u * 32 + 4);
+              const float4 z0 = *reinterpret_cast<const float4*>(kz + u * 32);
+              const float4 z1 = *reinterpret_cast<const float4*>(kz + u * 32 + 4);
+              const float4 q0 = *reinterpret_cast<const float4*>(qrow + u * 32);
+              const float4 q1 = *reinterpret_cast<const float4*>(qrow + u * 32 + 4);
+              const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+              const float zv[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+              const float qv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                pr[u2][e] = qv[e] * sv[e];
+                bias = fmaf(qv[e], zv[e], bias);
+              }
+            }
+            auto put = [&](int idx, float a, float bb) {
+              const __half2 hv = __floats2half2_rn(a, bb);
+              xh[idx] = *reinterpret_cast<const uint32_t*>(&hv);
+              if constexpr (K2) {
+                const float2 hf = __half22float2(hv);
+                const __half2 lv = __floats2half2_rn(a - hf.x, bb - hf.y);
+                xl[idx] = *reinterpret_cast<const uint32_t*>(&lv);
+              }
+            };
+            if constexpr (BITS == 4) {   // a word is one run of eight channels: pairs (c_k, c_k+4)
+#pragma unroll
+              for (int u2 = 0; u2 < 2; ++u2)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) put((h2 * 2 + u2) * 4 + k, pr[u2][k], pr[u2][k + 4]);
+            } else {                      // a word is both runs: pairs (c_j, c_j+8)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) put(h2 * 8 + j, pr[0][j], pr[1][j]);
+            }
+          }
+          bias += __shfl_xor_sync(0xffffffffu, bias, 1);
+          bias += __shfl_xor_sync(0xffffffffu, bias, 2);
+          c0 = __shfl_sync(0xffffffffu, bias, (tig * 2) * 4);
+          c1 = __shfl_sync(0xffffffffu, bias, (tig * 2 + 1) * 4);
+        };
+        // ---- scores of NT tiles of 16 tokens that share the operand: their MMA chains are independent and interleave ----
+        auto run_tiles = [&](auto nt_tag, int tile0) {
+          constexpr int NT = decltype(nt_tag)::value;
+          uint32_t wa[NT][NW], wb[NT][NW];
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            const unsigned char* krow = st + (32 * warp + 16 * (tile0 + t) + gid) * KROW + tig * LB;
+            if constexpr (BITS == 4) {
+              const uint4 wa4 = *reinterpret_cast<const uint4*>(krow);
+              const uint4 wb4 = *reinterpret_cast<const uint4*>(krow + 8 * KROW);
+              wa[t][0] = wa4.x; wa[t][1] = wa4.y; wa[t][2] = wa4.z; wa[t][3] = wa4.w;
+              wb[t][0] = wb4.x; wb[t][1] = wb4.y; wb[t][2] = wb4.z; wb[t][3] = wb4.w;
+            } else {
+              const uint2 wa2 = *reinterpret_cast<const uint2*>(krow);
+              const uint2 wb2 = *reinterpret_cast<const uint2*>(krow + 8 * KROW);
+              wa[t][0] = wa2.x; wa[t][1] = wa2.y;
+              wb[t][0] = wb2.x; wb[t][1] = wb2.y;
+            }
+          }
+          float d0[NT][4], d1[NT][4];
+#pragma unroll
+          for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) d0[t][e] = d1[t][e] = 0.f;
+#pragma unroll
+          for (int w = 0; w < NW; ++w) {
+            uint32_t pa[NT][PW], pb[NT][PW];
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+              unpack_exact<BITS, 0>(wa[t][w], pa[t]);
+              unpack_exact<BITS, 0>(wb[t][w], pb[t]);
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < PW / 4; ++q4) {
+              const int x0 = w * PW + q4 * 4;
+#pragma unroll
+              for (int t = 0; t < NT; ++t) {
+                mma16816<__half>(d0[t], pa[t][q4 * 4], pb[t][q4 * 4], pa[t][q4 * 4 + 1], pb[t][q4 * 4 + 1], xh[x0], xh[x0 + 1]);
+                mma16816<__half>(d1[t], pa[t][q4 * 4 + 2], pb[t][q4 * 4 + 2], pa[t][q4 * 4 + 3], pb[t][q4 * 4 + 3], xh[x0 + 2], xh[x0 + 3]);
+              }
+              if constexpr (K2) {
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                  mma16816<__half>(d0[t], pa[t][q4 * 4], pb[t][q4 * 4], pa[t][q4 * 4 + 1], pb[t][q4 * 4 + 1], xl[x0], xl[x0 + 1]);
+                  mma16816<__half>(d1[t], pa[t][q4 * 4 + 2], pb[t][q4 * 4 + 2], pa[t][q4 * 4 + 3], pb[t][q4 * 4 + 3], xl[x0 + 2], xl[x0 + 3]);
+                }
+              }
+            }
+          }
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            s[tile0 + t][0] = (d0[t][0] + d1[t][0] + c0) * scale2;   // token gid,     head 2 tig
+            s[tile0 + t][1] = (d0[t][1] + d1[t][1] + c1) * scale2;   // token gid,     head 2 tig + 1
+            s[tile0 + t][2] = (d0[t][2] + d1[t][2] + c0) * scale2;   // token gid + 8, head 2 tig
+            s[tile0 + t][3] = (d0[t][3] + d1[t][3] + c1) * scale2;   // token gid + 8, head 2 tig + 1
+          }
+        };
+#pragma unroll
+        for (int t = 0; t < 2; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = kNegBig;
+        if (G >= 32) {
+          if (wvalid > 0) {   // both tiles lie in one token group
+            prep((32 * warp) / G);
+            run_tiles(std::integral_constant<int, 2>{}, 0);
+          }
         } else {
-          const uint2 wa2 = *reinterpret_cast<const uint2*>(krow + (tile * 16 + gid) * KROW);
-          const uint2 wb2 = *reinterpret_cast<const uint2*>(krow + (tile * 16 + gid + 8) * KROW);
-          wa[0] = wa2.x; wa[1] = wa2.y;
-          wb[0] = wb2.x; wb[1] = wb2.y;
-        }
-        float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-          uint32_t pa[PW], pb[PW];
-          unpack_exact<BITS, 0>(wa[w], pa);
-          unpack_exact<BITS, 0>(wb[w], pb);
-#pragma unroll
-          for (int q4 = 0; q4 < PW / 4; ++q4) {
-            const int x0 = w * PW + q4 * 4;
-            mma16816<__half>(d0, pa[q4 * 4], pb[q4 * 4], pa[q4 * 4 + 1], pb[q4 * 4 + 1], xh[x0], xh[x0 + 1]);
-            mma16816<__half>(d1, pa[q4 * 4 + 2], pb[q4 * 4 + 2], pa[q4 * 4 + 3], pb[q4 * 4 + 3], xh[x0 + 2], xh[x0 + 3]);
-            mma16816<__half>(d0, pa[q4 * 4], pb[q4 * 4], pa[q4 * 4 + 1], pb[q4 * 4 + 1], xl[x0], xl[x0 + 1]);
-            mma16816<__half>(d1, pa[q4 * 4 + 2], pb[q4 * 4 + 2], pa[q4 * 4 + 3], pb[q4 * 4 + 3], xl[x0 + 2], xl[x0 + 3]);
+          for (int tile = 0; tile * 16 < wvalid; ++tile) {
+            prep((32 * warp + 16 * tile) / G);
+            if (tile == 0) run_tiles(std::integral_constant<int, 1>{}, 0);
+            else run_tiles(std::integral_constant<int, 1>{}, 1);
           }
         }
-        const int tl = gl * G + tile * 16 + gid;
-        float* s0 = S + (tig * 2) * p.s_stride + tl;
-        float* s1 = S + (tig * 2 + 1) * p.s_stride + tl;
-        s0[0] = (d0[0] + d1[0] + c0) * p.sm_scale;
-        s1[0] = (d0[1] + d1[1] + c1) * p.sm_scale;
-        s0[8] = (d0[2] + d1[2] + c0) * p.sm_scale;
-        s1[8] = (d0[3] + d1[3] + c1) * p.sm_scale;
-      }
-    }
-    __syncthreads();
 
-    // ================= phase B: softmax statistics, scaled probabilities =================
-    const int nblk = (valid + 127) >> 7;
-    if (warp < p.rep) {
-      const float* srow = S + warp * p.s_stride;
-      float m = kNegBig;
-      for (int t = lane; t < valid; t += 32) m = fmaxf(m, srow[t]);
-      m = warp_max(m);
-      float l = 0.f, z[VG] = {};
-      unsigned char* prow = P + warp * p.p_stride;
-      for (int t = lane; t < nblk * 128; t += 32) {
-        float e = 0.f;
-        if (t < valid) {
-          e = __expf(srow[t] - m);
-          l += e;
+        // ---- block maximum per head: this warp's 32 tokens, then the four warps through shared memory ----
+        float mx0 = fmaxf(fmaxf(s[0][0], s[0][2]), fmaxf(s[1][0], s[1][2]));
+        float mx1 = fmaxf(fmaxf(s[0][1], s[0][3]), fmaxf(s[1][1], s[1][3]));
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
         }
-        // operand layout of a 128-token block: [4 operand quads][lane quad 0..3] chunks of 8 halves = four pairs, in the
-        // order the pairs of the value code words come out of the unpack (4 bits: (t_k, t_k+4) per 8 tokens; 2 bits:
-        // (t_j, t_j+8) per 16 tokens)
-        const int tl = t & 127;
-        int off;
-        if constexpr (BITS == 4) {
-          const int pos = tl & 7;
-          off = (t >> 7) * 256 + ((tl >> 3) & 3) * 64 + (tl >> 5) * 16 + ((((pos & 3) << 1) | (pos >> 2)) * 2);
-        } else {
-          const int e = tl & 15, j = e & 7;
-          off = (t >> 7) * 256 + ((((tl >> 4) & 1) * 2 + (j >> 2)) * 64) + (tl >> 5) * 16 + (((j & 3) * 2 + (e >> 3)) * 2);
+        float* gm = gmax_s + ps * (kScoreWarps * kHeads);
+        if (gid == 0) *reinterpret_cast<float2*>(gm + warp * kHeads + 2 * tig) = make_float2(mx0, mx1);
+        named_sync(2, kScoreWarps * 32);
+        float alpha[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float mb = kNegBig;
+#pragma unroll
+          for (int w = 0; w < kScoreWarps; ++w) mb = fmaxf(mb, gm[w * kHeads + 2 * tig + e]);
+          const float m_new = fmaxf(m_run[e], mb);
+          alpha[e] = exp2f(m_run[e] - m_new);
+          m_run[e] = m_new;
+          l_run[e] *= alpha[e];
+#pragma unroll
+          for (int g = 0; g < VG; ++g) z_run[g][e] *= alpha[e];
         }
+
+        // ---- probabilities times the value scale into the operand buffer of the value warps ----
+        wait_bar(p_empty + ps * 8, ((i >> 1) & 1) ^ 1, status, dead);
+        if (warp == 0 && gid == 0) *reinterpret_cast<float2*>(alpha_s + ps * kHeads + 2 * tig) = make_float2(alpha[0], alpha[1]);
+        unsigned char* pst = Pring + ps * p_stage_bytes(VG);
+        const float* vs = reinterpret_cast<const float*>(st + off_vs);
+        const float* vz = reinterpret_cast<const float*>(st + off_vz);
+#pragma unroll
+        for (int tile = 0; tile < 2; ++tile)
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            const int tl = 32 * warp + 16 * tile + gid + 8 * hf;
+            const bool live = tl < bvalid;
+            float pe[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              pe[e] = live ? exp2f(s[tile][hf * 2 + e] - m_run[e]) : 0.f;
+              l_run[e] += pe[e];
+            }
+#pragma unroll
+            for (int g = 0; g < VG; ++g) {
+              const float sc = live ? vs[tl * VG + g] : 0.f;
+              const float zc = live ? fmaf((float)VCENTER, sc, vz[tl * VG + g]) : 0.f;   // the value codes are centred
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const float pv = pe[e] * sc;
+                z_run[g][e] = fmaf(pe[e], zc, z_run[g][e]);
+                const __half hv = __float2half_rn(pv);
+                unsigned char* dst = pst + g * (2 * kHeads * kPHead) + poff[tile][hf][e];
+                *reinterpret_cast<__half*>(dst) = hv;
+                if constexpr (P2) *reinterpret_cast<__half*>(dst + kHeads * kPHead) = __float2half_rn(pv - __half2float(hv));
+              }
+            }
+          }
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(p_full + ps * 8);
+          mbar_arrive(data_empty + slot * 8);
+        }
+      }
+
+      // ---- statistics of the split: sum and the constant term per head (and value group), over this warp's tokens ----
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float lsum = l_run[e];
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+        float cs[VG];
 #pragma unroll
         for (int g = 0; g < VG; ++g) {
-          {
-            float pv = 0.f;
-            if (t < valid) {
-              const float sc = vs_s[t * VG + g];
-              z[g] = fmaf(e, fmaf((float)VCENTER, sc, vz_s[t * VG + g]), z[g]);   // value codes are centred in phase C
-              pv = e * sc;
-            }
-            // two-term fp16 expansion of p * scale (hi + residual): keeps P.V at fp32-level accuracy
-            const __half hv = __float2half_rn(pv);
-            *reinterpret_cast<__half*>(prow + g * pgs + off) = hv;
-            *reinterpret_cast<__half*>(prow + g * pgs + kHeads * p.p_stride + off) = __float2half_rn(pv - __half2float(hv));
+          float c = z_run[g][e];
+#pragma unroll
+          for (int o = 4; o < 32; o <<= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+          cs[g] = c;
+        }
+        if (gid == 0) {
+          float* f = fin_s + (warp * kHeads + 2 * tig + e) * kFinStride;
+          f[0] = lsum;
+#pragma unroll
+          for (int g = 0; g < VG; ++g) f[1 + g] = cs[g];
+          if (warp == 0) st_m[2 * tig + e] = m_run[e] * kLn2;
+        }
+      }
+      named_sync(1, kComputeThreads);
+      if (warp == 0 && lane < kHeads) {
+        float l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kScoreWarps; ++w) l += fin_s[(w * kHeads + lane) * kFinStride];
+        st_l[lane] = l;
+      }
+    } else {
+      // ================= value warps: channels [32 v, 32 v + 32), two MMA row tiles of 16 =================
+      const int v = warp - kScoreWarps;
+      float oacc[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[mt][e] = 0.f;
+      const int pg = VG == 1 ? 0 : v;   // 32 channels = one value group
+      const int pchunk = ((tig ^ (gid >> 1)) & 3) * 16;
+
+      for (int i = 0; i < nblk; ++i) {
+        const int slot = i % p.stages, ps = i & 1;
+        const unsigned char* st = stage + slot * sbytes;
+        wait_bar(data_full + slot * 8, (i / p.stages) & 1, status, dead);
+        uint32_t wa[2][NW], wb[2][NW];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          const unsigned char* vrow = st + off_vc + (32 * v + 16 * mt + gid) * VROW + tig * LB;
+          if constexpr (BITS == 4) {
+            const uint4 va = *reinterpret_cast<const uint4*>(vrow);
+            const uint4 vb = *reinterpret_cast<const uint4*>(vrow + 8 * VROW);
+            wa[mt][0] = va.x; wa[mt][1] = va.y; wa[mt][2] = va.z; wa[mt][3] = va.w;
+            wb[mt][0] = vb.x; wb[mt][1] = vb.y; wb[mt][2] = vb.z; wb[mt][3] = vb.w;
+          } else {
+            const uint2 va = *reinterpret_cast<const uint2*>(vrow);
+            const uint2 vb = *reinterpret_cast<const uint2*>(vrow + 8 * VROW);
+            wa[mt][0] = va.x; wa[mt][1] = va.y;
+            wb[mt][0] = vb.x; wb[mt][1] = vb.y;
           }
         }
-      }
-      l = warp_sum(l);
+        wait_bar(p_full + ps * 8, (i >> 1) & 1, status, dead);
+        const float2 al = *reinterpret_cast<const float2*>(alpha_s + ps * kHeads + 2 * tig);
+        const unsigned char* ph = Pring + ps * p_stage_bytes(VG) + pg * (2 * kHeads * kPHead) + gid * kPHead + pchunk;
+        // independent accumulator chains: (row tile, pair half, term)
+        float o0[2][4], o1[2][4], o0l[2][4], o1l[2][4];
 #pragma unroll
-      for (int g = 0; g < VG; ++g) z[g] = warp_sum(z[g]);
-      if (lane == 0) {
-        st_m[warp] = m;
-        st_l[warp] = l;
+        for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-        for (int g = 0; g < VG; ++g)
-          st_c[g * kHeads + warp] = z[g];
-      }
-    }
-    __syncthreads();
-
-    // ================= phase C: O^T[c][h] = sum_t code_v[t][c] * P'[t][h] =================
-    {
-      const int row = warp * 16 + gid;  // channel
-      const unsigned char* Pg = P + ((warp * 16 * VG) / kD) * pgs;   // probabilities scaled for this warp's channel group
-      const unsigned char* vbase = vc_s + row * VROW + tig * LB;
-      float o0[4] = {0.f, 0.f, 0.f, 0.f}, o1[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int blk = 0; blk < nblk; ++blk) {
-        uint32_t wa[NW], wb[NW];
-        if constexpr (BITS == 4) {
-          const uint4 va = *reinterpret_cast<const uint4*>(vbase + blk * (kD * VROW));
-          const uint4 vb = *reinterpret_cast<const uint4*>(vbase + blk * (kD * VROW) + 8 * VROW);
-          wa[0] = va.x; wa[1] = va.y; wa[2] = va.z; wa[3] = va.w;
-          wb[0] = vb.x; wb[1] = vb.y; wb[2] = vb.z; wb[3] = vb.w;
-        } else {
-          const uint2 va = *reinterpret_cast<const uint2*>(vbase + blk * (kD * VROW));
-          const uint2 vb = *reinterpret_cast<const uint2*>(vbase + blk * (kD * VROW) + 8 * VROW);
-          wa[0] = va.x; wa[1] = va.y;
-          wb[0] = vb.x; wb[1] = vb.y;
-        }
+          for (int e = 0; e < 4; ++e) o0[mt][e] = o1[mt][e] = o0l[mt][e] = o1l[mt][e] = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
-          uint32_t pa[PW], pb[PW];
-          unpack_exact<BITS, VCENTER>(wa[w], pa);
-          unpack_exact<BITS, VCENTER>(wb[w], pb);
+          uint32_t pa[2][PW], pb[2][PW];
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            unpack_exact<BITS, VCENTER>(wa[mt][w], pa[mt]);
+            unpack_exact<BITS, VCENTER>(wb[mt][w], pb[mt]);
+          }
 #pragma unroll
           for (int q4 = 0; q4 < PW / 4; ++q4) {
-            const int i = w * (PW / 4) + q4;   // operand quad
-            uint4 pf = make_uint4(0u, 0u, 0u, 0u), pl = make_uint4(0u, 0u, 0u, 0u);
-            if (gid < p.rep) {
-              pf = *reinterpret_cast<const uint4*>(Pg + gid * p.p_stride + blk * 256 + i * 64 + tig * 16);
-              pl = *reinterpret_cast<const uint4*>(Pg + kHeads * p.p_stride + gid * p.p_stride + blk * 256 + i * 64 + tig * 16);
+            const int ci = w * (PW / 4) + q4;   // operand quad
+            const uint4 pf = *reinterpret_cast<const uint4*>(ph + ci * 64);
+            uint4 pl = make_uint4(0u, 0u, 0u, 0u);
+            if constexpr (P2) pl = *reinterpret_cast<const uint4*>(ph + kHeads * kPHead + ci * 64);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+              mma16816<__half>(o0[mt], pa[mt][q4 * 4], pb[mt][q4 * 4], pa[mt][q4 * 4 + 1], pb[mt][q4 * 4 + 1], pf.x, pf.y);
+              mma16816<__half>(o1[mt], pa[mt][q4 * 4 + 2], pb[mt][q4 * 4 + 2], pa[mt][q4 * 4 + 3], pb[mt][q4 * 4 + 3], pf.z, pf.w);
+              if constexpr (P2) {
+                mma16816<__half>(o0l[mt], pa[mt][q4 * 4], pb[mt][q4 * 4], pa[mt][q4 * 4 + 1], pb[mt][q4 * 4 + 1], pl.x, pl.y);
+                mma16816<__half>(o1l[mt], pa[mt][q4 * 4 + 2], pb[mt][q4 * 4 + 2], pa[mt][q4 * 4 + 3], pb[mt][q4 * 4 + 3], pl.z, pl.w);
+              }
             }
-            mma16816<__half>(o0, pa[q4 * 4], pb[q4 * 4], pa[q4 * 4 + 1], pb[q4 * 4 + 1], pf.x, pf.y);
-            mma16816<__half>(o1, pa[q4 * 4 + 2], pb[q4 * 4 + 2], pa[q4 * 4 + 3], pb[q4 * 4 + 3], pf.z, pf.w);
-            mma16816<__half>(o0, pa[q4 * 4], pb[q4 * 4], pa[q4 * 4 + 1], pb[q4 * 4 + 1], pl.x, pl.y);
-            mma16816<__half>(o1, pa[q4 * 4 + 2], pb[q4 * 4 + 2], pa[q4 * 4 + 3], pb[q4 * 4 + 3], pl.z, pl.w);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(p_empty + ps * 8);
+          mbar_arrive(data_empty + slot * 8);
+          if (v == kValueWarps - 1 && i + p.stages < nblk) {   // refill the slot once all eight warps have released it
+            wait_bar(data_empty + slot * 8, (i / p.stages) & 1, status, dead);
+            issue_block(i + p.stages);
+          }
+        }
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          oacc[mt][0] = fmaf(oacc[mt][0], al.x, (o0[mt][0] + o1[mt][0]) + (o0l[mt][0] + o1l[mt][0]));
+          oacc[mt][1] = fmaf(oacc[mt][1], al.y, (o0[mt][1] + o1[mt][1]) + (o0l[mt][1] + o1l[mt][1]));
+          oacc[mt][2] = fmaf(oacc[mt][2], al.x, (o0[mt][2] + o1[mt][2]) + (o0l[mt][2] + o1l[mt][2]));
+          oacc[mt][3] = fmaf(oacc[mt][3], al.y, (o0[mt][3] + o1[mt][3]) + (o0l[mt][3] + o1l[mt][3]));
+        }
+      }
+
+      named_sync(1, kComputeThreads);   // the score warps' statistics are in shared memory
+      // partial O of the split: lane holds channels (row, row + 8) x heads (2 tig, 2 tig + 1) of each row tile
+      float* po = p.part_o + (bh * p.n_split + split) * (size_t)(kHeads * kD);
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int hh = 2 * tig + e;
+        float corr = 0.f;
+#pragma unroll
+        for (int w = 0; w < kScoreWarps; ++w) corr += fin_s[(w * kHeads + hh) * kFinStride + 1 + pg];
+        if (hh < p.rep) {
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            const int c = 32 * v + 16 * mt + gid;
+            __stcg(po + hh * kD + c, oacc[mt][e] + corr);
+            __stcg(po + hh * kD + c + 8, oacc[mt][2 + e] + corr);
           }
         }
       }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) o_acc[i] = o0[i] + o1[i];
     }
-    // write partial O: lane holds channels (row, row+8) x heads (tig*2, tig*2+1)
-    {
-      float* po = p.part_o + (bh * p.n_split + split) * (size_t)(kHeads * kD);
-      const int row = warp * 16 + gid;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int hh = tig * 2 + (i & 1), c = row + 8 * (i >> 1);
-        if (hh < p.rep) __stcg(po + hh * kD + c, o_acc[i] + st_c[((warp * 16 * VG) / kD) * kHeads + hh]);
-      }
-    }
+    named_sync(1, kComputeThreads);   // st_m / st_l are complete
   } else {
     // ================= residual window: dense fp16/bf16 tokens from the stage =================
+    float* S = reinterpret_cast<float*>(Pring);                 // [8][s_stride] scores
+    constexpr int s_stride = kResChunk + 4;
+    float* red = reinterpret_cast<float*>(Pring + 4096);        // [8][128] fp32
+    wait_bar(res_bar, 0, status, dead);
     for (int tile = warp; tile * 16 < valid; tile += kAttnWarps) {
       const int tA = min(tile * 16 + gid, valid - 1), tB = min(tile * 16 + gid + 8, valid - 1);
       float d0[4] = {0.f, 0.f, 0.f, 0.f};
@@ -500,16 +732,16 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
                          h2_bits(q1.x, q1.y), h2_bits(q1.z, q1.w));
       }
       const int tl = tile * 16 + gid;
-      float* s0 = S + (tig * 2) * p.s_stride + tl;
-      float* s1 = S + (tig * 2 + 1) * p.s_stride + tl;
+      float* s0 = S + (tig * 2) * s_stride + tl;
+      float* s1 = S + (tig * 2 + 1) * s_stride + tl;
       s0[0] = d0[0] * p.sm_scale;
       s1[0] = d0[1] * p.sm_scale;
       s0[8] = d0[2] * p.sm_scale;
       s1[8] = d0[3] * p.sm_scale;
     }
-    __syncthreads();
+    named_sync(1, kComputeThreads);
     if (warp < p.rep) {
-      float* srow = S + warp * p.s_stride;
+      float* srow = S + warp * s_stride;
       float m = kNegBig;
       for (int t = lane; t < valid; t += 32) m = fmaxf(m, srow[t]);
       m = warp_max(m);
@@ -523,10 +755,9 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       if (lane == 0) {
         st_m[warp] = m;
         st_l[warp] = l;
-        st_c[warp] = 0.f;
       }
     }
-    __syncthreads();
+    named_sync(1, kComputeThreads);
     // P.V on the CUDA cores: thread = (channel, token half); 8 heads per thread
     {
       const int c = threadIdx.x & 127, half = threadIdx.x >> 7;
@@ -536,16 +767,15 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
 #pragma unroll
       for (int hh = 0; hh < kHeads; ++hh) acc[hh] = 0.f;
       for (int t = tb; t < te; ++t) {
-        const float v = to_float<T>(*reinterpret_cast<const T*>(rv_s + t * kResPitch + c * 2));
+        const float vv = to_float<T>(*reinterpret_cast<const T*>(rv_s + t * kResPitch + c * 2));
 #pragma unroll
-        for (int hh = 0; hh < kHeads; ++hh) acc[hh] = fmaf(S[hh * p.s_stride + t], v, acc[hh]);
+        for (int hh = 0; hh < kHeads; ++hh) acc[hh] = fmaf(S[hh * s_stride + t], vv, acc[hh]);
       }
-      float* red = reinterpret_cast<float*>(P);  // [8][128], reused
       if (half) {
 #pragma unroll
         for (int hh = 0; hh < kHeads; ++hh) red[hh * kD + c] = acc[hh];
       }
-      __syncthreads();
+      named_sync(1, kComputeThreads);
       if (!half) {
         float* po = p.part_o + (bh * p.n_split + split) * (size_t)(kHeads * kD);
         for (int hh = 0; hh < p.rep; ++hh) __stcg(po + hh * kD + c, acc[hh] + red[hh * kD + c]);
@@ -561,9 +791,9 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
 
   // ================= merge of the splits by the last CTA of this (batch, head) =================
   __threadfence();
-  __syncthreads();
+  named_sync(1, kComputeThreads);
   if (threadIdx.x == 0) *s_last = (atomicAdd(p.counters + bh, 1) == p.n_split - 1);
-  __syncthreads();
+  named_sync(1, kComputeThreads);
   if (!*s_last) return;
   __threadfence();
   const float* pm = p.part_ml + bh * p.n_split * (size_t)(kHeads * 2);
@@ -573,7 +803,7 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
   // thread = (split group, head, 8 channels): the groups take contiguous ranges of splits; their partial sums
   // meet in shared memory and are added in group order
   const int rep_pad = p.rep <= 1 ? 1 : (p.rep <= 2 ? 2 : (p.rep <= 4 ? 4 : 8));
-  const int pairs = 16 * rep_pad, n_sg = kAttnThreads / pairs;
+  const int pairs = 16 * rep_pad, n_sg = kComputeThreads / pairs;
   const int pair = threadIdx.x % pairs, sg = threadIdx.x / pairs;
   const int mh = pair >> 4, mc = pair & 15;
   const bool head_ok = mh < p.rep;
@@ -592,14 +822,14 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       pa1[k] = __ldcg(reinterpret_cast<const float4*>(psrc + (size_t)sp * (kHeads * kD) + 4));
     }
   }
-  float* w_s = reinterpret_cast<float*>(stage);   // [n_split][8]: max, then weight (the operand stage is free by now)
+  float* w_s = reinterpret_cast<float*>(stage);   // [n_split][8]: max, then weight (the operand stages are free by now)
   float* l_s = w_s + p.n_split * kHeads;          // [n_split][8]: sum
-  for (int i = threadIdx.x; i < p.n_split * kHeads; i += kAttnThreads) {
+  for (int i = threadIdx.x; i < p.n_split * kHeads; i += kComputeThreads) {
     const int hh = i & 7;
     w_s[i] = hh < p.rep ? __ldcg(pm + i * 2) : kNegBig;
     l_s[i] = hh < p.rep ? __ldcg(pm + i * 2 + 1) : 0.f;
   }
-  __syncthreads();
+  named_sync(1, kComputeThreads);
   if (warp < p.rep) {   // one warp per head: weights of the splits and their sum
     const int hh = warp;
     float M = kNegBig;
@@ -614,7 +844,7 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
     L = warp_sum(L);
     if (lane == 0) st_l[hh] = L;
   }
-  __syncthreads();
+  named_sync(1, kComputeThreads);
   {
     const int hh = mh, c = mc;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -640,7 +870,7 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
       *reinterpret_cast<float4*>(red + (sg * pairs + pair) * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
       *reinterpret_cast<float4*>(red + (sg * pairs + pair) * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
-    __syncthreads();
+    named_sync(1, kComputeThreads);
     const bool active = head_ok && sg == 0;
     if (active) {
       for (int g2 = 1; g2 < n_sg; ++g2) {
@@ -676,40 +906,54 @@ __global__ void __launch_bounds__(kAttnThreads) kivi_decode_attn_kernel(const At
   if (threadIdx.x == 0) p.counters[bh] = 0;
 }
 
-int pick_chunk(int B, int H, int n_comp, int group) {
-  int chunk;
-  {
-    // 256 tokens per CTA: every warp has a 32-token group to score, three CTAs stay resident per SM (what overlaps
-    // one CTA's copies with another's arithmetic once the grid is larger than the machine), and the merge of
-    // a 4096-token context reads each split's partial output in one round trip
-    chunk = n_comp <= 128 ? 128 : 256;
-    // a grid that does not even fill the machine is all latency: longer chunks mean fewer splits to merge
-    // (measured at batch 1, 4096 tokens: 11.6 us with 512-token chunks, 12.9 us with 256)
-    if ((long long)B * H * ((n_comp + 255) / 256) <= sm_count() && n_comp > 256) chunk = 512;
-    while (chunk < kMaxChunk && (n_comp + chunk - 1) / chunk > 96) chunk += 128;   // bound the merge
-  }
-  if (chunk % group) chunk = (chunk + group - 1) / group * group;
-  return chunk;
-}
-
 struct AttnPlan {
-  int chunk, n_csplit, n_rsplit, n_split, s_stride, p_stride;
+  int nb, n_csplit, n_rsplit, n_split, stages;
   size_t smem;
 };
 
+// Blocks per compressed split: enough CTAs for two per SM, few enough splits for the merge, and as little of a
+// nearly empty last wave as the choice allows (cost in block times: a CTA's fixed part counts as two blocks).
 AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group, int bits, int vg) {
-  AttnPlan a;
-  a.chunk = pick_chunk(B, H, n_comp, group);
-  a.n_csplit = (n_comp + a.chunk - 1) / a.chunk;
+  AttnPlan a{};
+  const int nblk = (n_comp + kBlk - 1) / kBlk;
   a.n_rsplit = (n_res + kResChunk - 1) / kResChunk;
+  const long long slots = 2LL * sm_count();
+  int nb_min = (nblk + (kMaxSplits - a.n_rsplit) - 1) / (kMaxSplits - a.n_rsplit);
+  if (nb_min < 1) nb_min = 1;
+  int nb_max = nblk < kMaxNb ? nblk : kMaxNb;
+  if (nb_max < nb_min) nb_max = nb_min;
+  int best = nb_min;
+  double best_cost = 1e30;
+  for (int nb = nb_min; nb <= nb_max; ++nb) {
+    const long long cs = (nblk + nb - 1) / nb;
+    const double ctas = (double)B * H * (cs + a.n_rsplit * 2.0 / (nb + 2.0));
+    const double waves = ctas <= (double)slots ? 1.0 : (double)((long long)((ctas + slots - 1) / slots));
+    const double cost = waves * (nb + 2.0) + 0.02 * cs;   // a slight preference for fewer splits to merge
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = nb;
+    }
+  }
+#ifdef PARE_EXPERIMENT
+  if (const char* env = getenv("PARE_ATTN_NB")) {
+    const int v = atoi(env);
+    if (v >= nb_min) best = v;
+  }
+#endif
+  a.nb = best;
+  a.n_csplit = nblk ? (nblk + a.nb - 1) / a.nb : 0;
   a.n_split = a.n_csplit + a.n_rsplit;
-  const int span = a.chunk > 128 ? a.chunk : 128;
-  a.s_stride = span + 4;
-  a.p_stride = (span / 128) * 256 + 64;
-  if (a.p_stride < 512) a.p_stride = 512;   // the residual branch reuses the buffer for an [8][128] fp32 reduction
-  const int st = stage_bytes(a.chunk, group, bits, vg), rs = 2 * kResChunk * kResPitch;
-  a.smem = attn_header(vg) + (size_t)kHeads * kQS * sizeof(float) + (size_t)kHeads * a.s_stride * sizeof(float) +
-           2 * (size_t)kHeads * a.p_stride * vg + (size_t)(st > rs ? st : rs);
+  const int sb = stage_bytes(group, bits, vg);
+  const size_t fixed = ring_offset(vg);
+  int stages = (int)((kAttnSmemBudget - fixed) / sb);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages > a.nb) stages = a.nb;
+  if (stages < 2) stages = 2;
+  a.stages = stages;
+  size_t ring = (size_t)stages * sb;
+  const size_t need_other = 2 * kResChunk * kResPitch;   // the residual stage; the merge scratch (24 KB) is smaller
+  if (ring < need_other) ring = need_other;
+  a.smem = fixed + ring;
   return a;
 }
 
@@ -720,8 +964,9 @@ extern "C" {
 
 size_t pare_kivi_attn_workspace_bytes(int B, int H, int n_comp, int n_res) {
   if (B <= 0 || H <= 0 || n_comp < 0 || n_res < 0) return 0;
-  // smallest chunk any plan uses -> upper bound on the split count
-  const size_t n_split = (size_t)(n_comp + 127) / 128 + (size_t)(n_res + pare::kResChunk - 1) / pare::kResChunk + 1;
+  // one block per split is the finest plan -> upper bound on the split count
+  size_t n_split = (size_t)(n_comp + 127) / 128 + (size_t)(n_res + pare::kResChunk - 1) / pare::kResChunk + 1;
+  if (n_split > (size_t)pare::kMaxSplits + 1) n_split = pare::kMaxSplits + 1;
   return pare::kCounterBytes + (size_t)B * H * n_split * (pare::kHeads * pare::kD + pare::kHeads * 2) * sizeof(float);
 }
 
@@ -765,8 +1010,11 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
                  PARE_ERR_ALIGN);
 
   const AttnPlan plan = make_attn_plan(B, H, n_comp, n_res, group, bits, vg);
-  PARE_REQUIRE(plan.chunk % 128 == 0 && plan.chunk % group == 0 && plan.chunk <= kMaxChunk, PARE_ERR_UNSUPPORTED);
-  PARE_REQUIRE(plan.smem <= kAttnSmemCap && (size_t)plan.n_split * 2 * kHeads * sizeof(float) <= 16384, PARE_ERR_UNSUPPORTED);
+  // The merge takes kMaxSplits splits per (batch, head); a split runs as many blocks of 128 compressed tokens as that
+  // bound needs, so the context itself is not limited here (beyond kMaxNb blocks per split the planner only stops
+  // balancing waves).
+  PARE_REQUIRE(plan.n_split <= kMaxSplits, PARE_ERR_UNSUPPORTED);
+  PARE_REQUIRE(plan.smem <= kAttnSmemBudget, PARE_ERR_UNSUPPORTED);
 
   AttnParams p{};
   p.q = q; p.q_sb = q_stride_b; p.q_sh = q_stride_h;
@@ -783,9 +1031,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
   }
   p.sm_scale = softmax_scale;
   p.B = B; p.Hq = Hq; p.H = H; p.rep = Hq / H; p.group = group; p.cap = cap; p.n_comp = n_comp;
-  p.vg = vg;
-  p.chunk = plan.chunk; p.n_csplit = plan.n_csplit; p.n_split = plan.n_split;
-  p.s_stride = plan.s_stride; p.p_stride = plan.p_stride;
+  p.nb = plan.nb; p.stages = plan.stages; p.n_csplit = plan.n_csplit; p.n_split = plan.n_split;
   const size_t need = kCounterBytes + (size_t)B * H * p.n_split * (kHeads * kD + kHeads * 2) * sizeof(float);
   PARE_REQUIRE(workspace && workspace_bytes >= need, PARE_ERR_WORKSPACE);
   p.counters = reinterpret_cast<int*>(workspace);
@@ -793,7 +1039,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
   p.part_ml = p.part_o + (size_t)B * H * p.n_split * kHeads * kD;
 
   auto launch = [&](auto kern) -> int {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAttnSmemCap) != cudaSuccess) return PARE_ERR_CUDA;
+    if (!ensure_smem_attr(reinterpret_cast<const void*>(kern), (int)kAttnSmemBudget)) return PARE_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.n_split, H, B);
     cfg.blockDim = dim3(kAttnThreads, 1, 1);
@@ -806,12 +1052,13 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess ? PARE_OK : PARE_ERR_CUDA;
   };
+  constexpr int kMode = PARE_ATTN_MODE;
   if (vg == 1) {
-    if (bits == 4) return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 4, 1>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 4, 1>);
-    return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 2, 1>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 2, 1>);
+    if (bits == 4) return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 4, 1, kMode>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 4, 1, kMode>);
+    return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 2, 1, kMode>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 2, 1, kMode>);
   }
-  if (bits == 4) return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 4, kMaxVG>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 4, kMaxVG>);
-  return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 2, kMaxVG>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 2, kMaxVG>);
+  if (bits == 4) return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 4, kMaxVG, kMode>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 4, kMaxVG, kMode>);
+  return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 2, kMaxVG, kMode>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 2, kMaxVG, kMode>);
 }
 
 }  // extern "C"

@@ -10,7 +10,8 @@
 // ranks).  One kernel launch per all-reduce, one NVLink store latency end to end.
 //
 // Exchange buffer of a rank (allocated by pare_peer_buffer_create, mapped into the peers with
-// CUDA IPC):  [0, 4096): header -- epoch[kMaxCtas] ints, status word; [4096, ...): data[2][world][slot].
+// CUDA IPC):  [0, 4096): header -- epoch[kMaxCtas] ints, status word; the first half of what follows:
+// data[2][world][slot] (the second half serves the exchange fused into the linears' epilogues, peer.cuh).
 // Slots are double-buffered by the parity of an epoch that the kernel itself advances, so a captured CUDA
 // graph can be replayed.  Every call launches all kMaxCtas CTAs (those without units only advance their
 // epoch word), so every CTA's word equals the number of calls made so far whatever the calls' shapes were:
@@ -21,6 +22,7 @@
 // whatever it has (the host reads the word with pare_peer_status).
 
 #include "common.cuh"
+#include "peer.cuh"
 
 namespace pare {
 namespace {
@@ -165,8 +167,9 @@ int pare_peer_allreduce(const void* x, int64_t ldx, void* y, int64_t ldy, int ro
     PARE_REQUIRE(buffers[q] != nullptr, PARE_ERR_SHAPE);
     p.buf[q] = reinterpret_cast<unsigned char*>(buffers[q]);
   }
-  PARE_REQUIRE(buffer_bytes > kHeaderBytes, PARE_ERR_WORKSPACE);
-  p.slot_bytes = ((buffer_bytes - kHeaderBytes) / (2 * (size_t)world)) & ~(size_t)255;
+  PARE_REQUIRE(buffer_bytes > kHeaderBytes + 2 * 4096, PARE_ERR_WORKSPACE);
+  // this call's half of the data area (the other half belongs to the exchange fused into the linears, peer.cuh)
+  p.slot_bytes = ((peer_fused_offset(buffer_bytes) - kHeaderBytes) / (2 * (size_t)world)) & ~(size_t)255;
   const size_t units = (size_t)rows * cols / 4;
   PARE_REQUIRE(units * 16 <= p.slot_bytes, PARE_ERR_WORKSPACE);
   p.x = x; p.y = y; p.ldx = ldx; p.ldy = ldy; p.rows = rows; p.cols = cols; p.rank = rank; p.world = world;

@@ -519,7 +519,8 @@ bool gemm_supported(int M, int K, int G, const float* scale, const float* zero) 
 
 size_t gemm_workspace_bytes(int M, int N, int K) {
   const GemmPlan g = gemm_plan(M, N, K);
-  return kCounterBytes + ((size_t)g.mpad * K * 2 + 255) / 256 * 256 + (size_t)16 * M * N * sizeof(float);
+  // the same formula as gemm_forward's own check: partial sums only when the plan splits K, and only its splits
+  return kCounterBytes + ((size_t)g.mpad * K * 2 + 255) / 256 * 256 + (g.splits > 1 ? (size_t)g.splits * M * N * sizeof(float) : 0);
 }
 
 int gemm_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale, const float* zero,

@@ -289,6 +289,9 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
   T* yg = reinterpret_cast<T*>(p.y);
   const T* bias = reinterpret_cast<const T*>(p.bias);
   float* part = p.splits > 1 ? p.partial + (size_t)blockIdx.y * p.M * p.N : nullptr;
+  const bool peer = peer_on(p.peer);
+  const uint32_t pe = peer ? peer_epoch(p.peer) : 0u;   // after the dependency wait above
+  bool peer_timeout = false;
   if (threadIdx.x < 32 * MB * RB) {   // one warp per (row block, column block)
     const int rb = (threadIdx.x >> 5) / MB, mb = (threadIdx.x >> 5) % MB;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -300,23 +303,42 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
       acc.z += v.z;
       acc.w += v.w;
     }
-    const float out[4] = {acc.x, acc.y, acc.z, acc.w};
+    float out[4] = {acc.x, acc.y, acc.z, acc.w};
+    if (peer && !part) {   // the ranks' partial outputs meet here: send all four, then collect them
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int n = row0 + rb * 16 + gid + 8 * (i >> 1);
-      const int m = mb * 8 + tig * 2 + (i & 1);
-      if (n < p.N && m < p.M) {
-        if (part) {
-          __stcg(part + (size_t)m * p.N + n, out[i]);
-        } else {
-          float v = out[i];
-          if (bias) v += to_float<T>(bias[n]);
-          yg[(size_t)m * p.ldy + n] = from_float<T>(v);
+      for (int i = 0; i < 4; ++i) {
+        const int n = row0 + rb * 16 + gid + 8 * (i >> 1), m = mb * 8 + tig * 2 + (i & 1);
+        if (n < p.N && m < p.M) peer_send(p.peer, pe, (size_t)m * p.N + n, out[i] + (bias ? to_float<T>(bias[n]) : 0.f));
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int n = row0 + rb * 16 + gid + 8 * (i >> 1), m = mb * 8 + tig * 2 + (i & 1);
+        if (n < p.N && m < p.M) yg[(size_t)m * p.ldy + n] = from_float<T>(peer_recv(p.peer, pe, (size_t)m * p.N + n, peer_timeout));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int n = row0 + rb * 16 + gid + 8 * (i >> 1);
+        const int m = mb * 8 + tig * 2 + (i & 1);
+        if (n < p.N && m < p.M) {
+          if (part) {
+            __stcg(part + (size_t)m * p.N + n, out[i]);
+          } else {
+            float v = out[i];
+            if (bias) v += to_float<T>(bias[n]);
+            yg[(size_t)m * p.ldy + n] = from_float<T>(v);
+          }
         }
       }
     }
   }
-  if (p.splits == 1) return;
+  if (p.splits == 1) {
+    if (peer) {   // one exchanging unit per row tile
+      const int any_timeout = __syncthreads_or(peer_timeout);
+      if (threadIdx.x == 0) peer_unit_done(p.peer, pe, gridDim.x, any_timeout != 0);
+    }
+    return;
+  }
 
   // ---- K spans several CTAs: the last one to arrive adds the partial sums in split order ----
   __threadfence();
@@ -332,7 +354,16 @@ __global__ void __launch_bounds__(WARPS * 32) w4a16_gemv_kernel(const GemvParams
     float v = 0.f;
     for (int s = 0; s < p.splits; ++s) v += __ldcg(p.partial + ((size_t)s * p.M + m) * p.N + n);
     if (bias) v += to_float<T>(bias[n]);
-    yg[(size_t)m * p.ldy + n] = from_float<T>(v);
+    if (peer) peer_send(p.peer, pe, (size_t)m * p.N + n, v);
+    else yg[(size_t)m * p.ldy + n] = from_float<T>(v);
+  }
+  if (peer) {
+    for (int idx = threadIdx.x; idx < tile_rows * p.M; idx += THREADS) {
+      const int m = idx / tile_rows, n = row0 + (idx - m * tile_rows);
+      yg[(size_t)m * p.ldy + n] = from_float<T>(peer_recv(p.peer, pe, (size_t)m * p.N + n, peer_timeout));
+    }
+    const int any_timeout = __syncthreads_or(peer_timeout);
+    if (threadIdx.x == 0) peer_unit_done(p.peer, pe, gridDim.x, any_timeout != 0);
   }
   if (threadIdx.x == 0) p.counters[blockIdx.x] = 0;  // leave the workspace ready for the next call
 }
@@ -529,7 +560,8 @@ size_t gemv_workspace_bytes(int M, int N, int K, int G) {
 int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale,
                  const float* zero, const void* meta_h2, const int32_t* col_perm, const float* input_scale,
                  const void* bias, void* y, int64_t ldy, int M, int N, int K, int G, void* workspace,
-                 size_t workspace_bytes, cudaStream_t stream, const void* prepared, const ProducerArgs* prod) {
+                 size_t workspace_bytes, cudaStream_t stream, const void* prepared, const ProducerArgs* prod,
+                 const PeerCtx* peer) {
   GemvParams p{};
   p.x = x;
   p.ldx = ldx;
@@ -555,6 +587,11 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
     PARE_REQUIRE(pl.fast && col_perm == nullptr && input_scale == nullptr && prepared == nullptr && M <= 4, PARE_ERR_UNSUPPORTED);
     p.producer = prod->kind;
     p.pa = prod->a; p.pb = prod->b; p.pc = prod->c; p.resid_out = prod->resid_out; p.lda = prod->lda; p.eps = prod->eps;
+  }
+  if (peer) {   // the ranks' partial outputs are added in the epilogue: streaming kernels only, one fp32 unit per output
+    PARE_REQUIRE(pl.fast, PARE_ERR_UNSUPPORTED);
+    PARE_REQUIRE((size_t)M * N * 8 <= peer->slot_bytes, PARE_ERR_WORKSPACE);
+    p.peer = *peer;
   }
   if (!pl.fast) {
     return x_dtype == PARE_F16 ? launch_generic<__half>(p, packed, G, stream)

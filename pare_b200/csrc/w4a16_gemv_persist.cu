@@ -188,6 +188,11 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
     const int n_epi = nred >= 2 ? 2 : 1;
     const int ew = warp - kCW - 1;
     if (ew >= n_epi) return;
+    // tensor-parallel row-parallel layer: the ranks' partial outputs are exchanged and added right here (peer.cuh),
+    // while the consumer warps stream on
+    const bool peer = peer_on(p.peer);
+    const uint32_t pe = peer ? peer_epoch(p.peer) : 0u;
+    bool peer_timeout = false;
     for (int i = ew; i < n_items; i += n_epi) {
       const Item it = item_of(pl, bl, i);
       const int par = i % nred, rph = (i / nred) & 1;
@@ -240,7 +245,18 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
       // contributions that meet in this row tile: one per K slice, P per slice for a left-over tile
       const int contrib = pl.n_slices * (it.tile >= pl.n_full ? pl.P : 1);
       const int row0 = it.tile * R;
-      if (contrib == 1) {
+      if (contrib == 1 && peer) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          const int n = row0 + row_of(k), m = m_of(k);
+          if (k < nvals && m < p.M) peer_send(p.peer, pe, (size_t)m * p.N + n, out[k] + (bias ? to_float<T>(bias[n]) : 0.f));
+        }
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          const int n = row0 + row_of(k), m = m_of(k);
+          if (k < nvals && m < p.M) yg[(size_t)m * p.ldy + n] = from_float<T>(peer_recv(p.peer, pe, (size_t)m * p.N + n, peer_timeout));
+        }
+      } else if (contrib == 1) {
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
           const int n = row0 + row_of(k), m = m_of(k);
@@ -295,13 +311,26 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
 #pragma unroll
                   for (int c = 0; c < C; ++c) v[mi] += t[mi][c];
               }
+              if (peer) {
 #pragma unroll
-              for (int mi = 0; mi < MI; ++mi) {
-                const int m = m0 + mi;
-                if (m < p.M && lane < R) {
-                  float r = v[mi];
-                  if (bias) r += to_float<T>(bias[n]);
-                  yg[(size_t)m * p.ldy + n] = from_float<T>(r);
+                for (int mi = 0; mi < MI; ++mi) {
+                  const int m = m0 + mi;
+                  if (m < p.M && lane < R) peer_send(p.peer, pe, (size_t)m * p.N + n, v[mi] + (bias ? to_float<T>(bias[n]) : 0.f));
+                }
+#pragma unroll
+                for (int mi = 0; mi < MI; ++mi) {
+                  const int m = m0 + mi;
+                  if (m < p.M && lane < R) yg[(size_t)m * p.ldy + n] = from_float<T>(peer_recv(p.peer, pe, (size_t)m * p.N + n, peer_timeout));
+                }
+              } else {
+#pragma unroll
+                for (int mi = 0; mi < MI; ++mi) {
+                  const int m = m0 + mi;
+                  if (m < p.M && lane < R) {
+                    float r = v[mi];
+                    if (bias) r += to_float<T>(bias[n]);
+                    yg[(size_t)m * p.ldy + n] = from_float<T>(r);
+                  }
                 }
               }
             }
@@ -314,6 +343,10 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
           if (lane == 0) p.counters[it.tile] = 0;
         }
       }
+    }
+    if (peer) {   // one exchanging unit per epilogue warp that runs
+      const bool any_timeout = __any_sync(0xffffffffu, peer_timeout);
+      if (lane == 0) peer_unit_done(p.peer, pe, gridDim.x * n_epi, any_timeout);
     }
     return;
   }

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "peer.cuh"
 
 namespace pare {
 struct ProducerArgs {
@@ -24,7 +25,8 @@ size_t gemv_workspace_bytes(int M, int N, int K, int G);
 int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed, const float* scale,
                  const float* zero, const void* meta_h2, const int32_t* col_perm, const float* input_scale,
                  const void* bias, void* y, int64_t ldy, int M, int N, int K, int G, void* workspace,
-                 size_t workspace_bytes, cudaStream_t stream, const void* prepared, const ProducerArgs* prod);
+                 size_t workspace_bytes, cudaStream_t stream, const void* prepared, const ProducerArgs* prod,
+                 const PeerCtx* peer = nullptr);
 }  // namespace pare
 
 namespace {

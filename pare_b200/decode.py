@@ -5,12 +5,15 @@ This is the measurement vehicle for "decode tok/s": every transformer block is
 rmsnorm(+residual) -> fused gate|up linear -> SwiGLU -> down linear``, with random-init INT4
 weights of the requested shape.  The linears are ordinary :class:`QuantizedLinear` modules
 (``use_kernel=True``) and the cache an ordinary :class:`QuantizedKVCache`, i.e. the public API
-a user of the reference would call; rotary embeddings, the token embedding and the LM head are
-left out (they are not part of the path this package replaces).
+a user of the reference would call; q and the new key get their rotary embedding inside the
+attention launch; the token embedding and the LM head are left out (they are not part of the
+path this package replaces).
 
-Tensor parallelism (one process per GPU): q|k|v and gate|up are split by output rows (whole
-heads / FFN columns per rank), o and down by input columns, the KV cache by KV head; the two
-row-parallel outputs of a block are summed with one NCCL all-reduce each.
+Tensor parallelism (one process per GPU): ONE model is built from the seeds and every rank keeps
+its slice of it -- q|k|v and gate|up split by output rows (whole heads / FFN columns per rank),
+o and down by input columns in whole groups, the KV cache by KV head.  The two row-parallel
+outputs of a block are summed over the ranks by the one-launch peer all-reduce over NVLink
+(``pare_peer_allreduce``), NCCL for tensors too large for its exchange buffers.
 """
 
 from __future__ import annotations
@@ -58,17 +61,49 @@ def synthetic_linear(out_features: int, in_features: int, *, seed: int, device, 
     return layer
 
 
+def _take_rows(layer: QuantizedLinear, ranges: list[tuple[int, int]]) -> QuantizedLinear:
+    """The output rows ``[a, b)`` of every range, concatenated (a column-parallel shard of a fused projection)."""
+    idx = torch.cat([torch.arange(a, b, device=layer.packed_weight.device) for a, b in ranges])
+    shard = QuantizedLinear.from_tensors(layer.packed_weight[idx].contiguous(), None, layer.scale[idx].contiguous(),
+                                         layer.zero[idx].contiguous(), layer.config, None, layer.in_features, idx.numel())
+    shard.use_kernel = True
+    return shard
+
+
+def _take_cols(layer: QuantizedLinear, a: int, b: int) -> QuantizedLinear:
+    """The input columns ``[a, b)`` in whole groups (a row-parallel shard)."""
+    g = layer.config.group_size
+    assert a % g == 0 and b % g == 0
+    shard = QuantizedLinear.from_tensors(layer.packed_weight[:, a // 2:b // 2].contiguous(), None,
+                                         layer.scale[:, a // g:b // g].contiguous(), layer.zero[:, a // g:b // g].contiguous(),
+                                         layer.config, None, b - a, layer.out_features)
+    shard.use_kernel = True
+    return shard
+
+
 class DecodeBlock(nn.Module):
+    """One block's four fused projections.  With ``tp_world > 1`` the FULL layers are generated from the seeds (the same
+    on every rank) and this rank keeps its slice: its query / key / value heads of q|k|v, its FFN columns of gate|up,
+    the matching input columns of o and down."""
+
     def __init__(self, hidden: int, ffn: int, hq: int, hkv: int, d: int, *, seed: int, device, dtype,
-                 tp_world: int = 1) -> None:
+                 tp_world: int = 1, tp_rank: int = 0) -> None:
         super().__init__()
         assert hq % tp_world == 0 and hkv % tp_world == 0 and ffn % (tp_world * 128) == 0
         self.hq, self.hkv, self.d, self.ffn = hq // tp_world, hkv // tp_world, d, ffn // tp_world
         self.hidden = hidden
-        self.qkv = synthetic_linear((self.hq + 2 * self.hkv) * d, hidden, seed=seed * 7 + 0, device=device)
-        self.o = synthetic_linear(hidden, self.hq * d, seed=seed * 7 + 3, device=device)
-        self.gate_up = synthetic_linear(2 * self.ffn, hidden, seed=seed * 7 + 4, device=device)
-        self.down = synthetic_linear(hidden, self.ffn, seed=seed * 7 + 6, device=device)
+        qkv = synthetic_linear((hq + 2 * hkv) * d, hidden, seed=seed * 7 + 0, device=device)
+        o = synthetic_linear(hidden, hq * d, seed=seed * 7 + 3, device=device)
+        gate_up = synthetic_linear(2 * ffn, hidden, seed=seed * 7 + 4, device=device)
+        down = synthetic_linear(hidden, ffn, seed=seed * 7 + 6, device=device)
+        if tp_world > 1:
+            r, nq, nkv, nf = tp_rank, self.hq * d, self.hkv * d, self.ffn
+            qkv = _take_rows(qkv, [(r * nq, (r + 1) * nq), (hq * d + r * nkv, hq * d + (r + 1) * nkv),
+                                   ((hq + hkv) * d + r * nkv, (hq + hkv) * d + (r + 1) * nkv)])
+            o = _take_cols(o, r * nq, (r + 1) * nq)
+            gate_up = _take_rows(gate_up, [(r * nf, (r + 1) * nf), (ffn + r * nf, ffn + (r + 1) * nf)])
+            down = _take_cols(down, r * nf, (r + 1) * nf)
+        self.qkv, self.o, self.gate_up, self.down = qkv, o, gate_up, down
         self.register_buffer("norm1", torch.ones(hidden, device=device, dtype=dtype))
         self.register_buffer("norm2", torch.ones(hidden, device=device, dtype=dtype))
 
@@ -79,15 +114,20 @@ class DecodeStack(nn.Module):
     def __init__(self, shape: str | tuple, *, device="cuda", dtype=torch.bfloat16, n_layers: int | None = None,
                  kv_config: KVCacheConfig | None = None, max_seq_len: int = 8192, tp_world: int = 1,
                  process_group=None, seed: int = 0, peer_all_reduce: bool = True,
-                 rope_theta: float | None = 500000.0) -> None:
+                 rope_theta: float | None = 500000.0, tp_rank: int | None = None) -> None:
         super().__init__()
         hidden, ffn, hq, hkv, d, layers = SHAPES[shape] if isinstance(shape, str) else shape
         self.hidden, self.d = hidden, d
+        self.hkv_total = hkv
         self.n_layers = n_layers or layers
         self.dtype, self.device = dtype, torch.device(device)
         self.tp_world, self.group = tp_world, process_group
+        if tp_rank is None:
+            tp_rank = torch.distributed.get_rank(process_group) if tp_world > 1 else 0
+        self.tp_rank = tp_rank
         self.blocks = nn.ModuleList(
-            DecodeBlock(hidden, ffn, hq, hkv, d, seed=seed + i, device=self.device, dtype=dtype, tp_world=tp_world)
+            DecodeBlock(hidden, ffn, hq, hkv, d, seed=seed + i, device=self.device, dtype=dtype, tp_world=tp_world,
+                        tp_rank=tp_rank)
             for i in range(self.n_layers))
         self.cache = QuantizedKVCache(self.n_layers, kv_config or KVCacheConfig(), max_seq_len=max_seq_len)
         self._code = _lib.dtype_code(dtype)
@@ -140,16 +180,24 @@ class DecodeStack(nn.Module):
     @torch.no_grad()
     def prefill_cache(self, batch: int, context: int, seed: int = 1) -> None:
         """Fill every layer's cache with ``context`` synthetic tokens: N(0,1) with 1 % of the channels
-        (same channels for all tokens) scaled by 10, the stand-in for real K/V statistics."""
+        (same channels for all tokens) scaled by 10, the stand-in for real K/V statistics.  Under tensor
+        parallelism the tokens of ALL KV heads are generated (the same on every rank, one head at a time) and this
+        rank keeps its heads."""
         g = torch.Generator(device=self.device).manual_seed(seed)
         blk = self.blocks[0]
+        mine = range(self.tp_rank * blk.hkv, (self.tp_rank + 1) * blk.hkv)
         for layer in range(self.n_layers):
-            k = torch.randn(batch, blk.hkv, context, self.d, device=self.device, generator=g)
-            v = torch.randn(batch, blk.hkv, context, self.d, device=self.device, generator=g)
             out_ch = torch.randperm(self.d, device=self.device, generator=g)[: max(1, self.d // 100)]
-            k[..., out_ch] *= 10.0
+            ks, vs = [], []
+            for head in range(self.hkv_total):
+                k = torch.randn(batch, 1, context, self.d, device=self.device, generator=g)
+                v = torch.randn(batch, 1, context, self.d, device=self.device, generator=g)
+                if head in mine:
+                    k[..., out_ch] *= 10.0
+                    ks.append(k.to(self.dtype))
+                    vs.append(v.to(self.dtype))
             self.cache.reset(layer)
-            self.cache._append(layer, k.to(self.dtype), v.to(self.dtype))
+            self.cache._append(layer, torch.cat(ks, dim=1), torch.cat(vs, dim=1))
 
     # ---- the prompt -----------------------------------------------------------------------
     @torch.no_grad()
@@ -182,7 +230,8 @@ class DecodeStack(nn.Module):
     def forward(self, x: Tensor) -> Tensor:
         """``x [M, hidden]``: hidden state of the newest token of each of M sequences → same shape.
 
-        For M <= 16 a block is five launches: q|k|v linear (normalises the residual stream itself),
+        For M <= 16 a block is five launches, at any tensor-parallel degree (the sums over the ranks after the o and
+        down linears are added inside those kernels): q|k|v linear (normalises the residual stream itself),
         attention (appends the new K / V token, hands its output over as prepared activations), o linear,
         gate|up linear (adds the attention branch to the residual stream and normalises it itself), down
         linear (applies the SwiGLU gate itself).  Larger M takes plain tensors and stand-alone glue kernels.
@@ -209,10 +258,17 @@ class DecodeStack(nn.Module):
             v = qkv[:, (hq + hkv) * d:].unflatten(1, (hkv, 1, d))
             if fused:
                 self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d), prepared_out=p_attn, rope=rope)
-                o = self._all_reduce(blk.o.forward_prepared(p_attn))
+                # tensor parallel: the sums of the two row-parallel layers over the ranks are added inside their kernels
+                peer = self.peer_reduce if (self.tp_world > 1 and self.peer_reduce is not None
+                                            and m * self.hidden <= self.peer_reduce.max_fused_elements()) else None
+                o = blk.o.forward_prepared(p_attn, peer=peer)
+                if peer is None:
+                    o = self._all_reduce(o)
                 gate_up = blk.gate_up.forward_rmsnorm(resid, o, blk.norm2, resid_out=spare)
                 resid, spare = spare, resid
-                delta = self._all_reduce(blk.down.forward_silu_mul(gate_up))
+                delta = blk.down.forward_silu_mul(gate_up, peer=peer)
+                if peer is None:
+                    delta = self._all_reduce(delta)
             else:
                 attn = self.cache.attend(i, q, k, v, scale=1.0 / math.sqrt(d), rope=rope)
                 o = self._all_reduce(blk.o(attn.reshape(m, hq * d)))

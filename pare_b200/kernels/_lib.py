@@ -58,6 +58,11 @@ SIGNATURES: dict[str, tuple] = {
     "pare_peer_buffer_destroy": (_i, [_vp]),
     "pare_peer_status": (_i, [_vp, _vp]),
     "pare_peer_allreduce": (_i, [_vp, _i64, _vp, _i64, _i, _i, _i, _i, _i, C.POINTER(C.c_void_p), _sz, _vp]),
+    "pare_w4a16_forward_prepared_allreduce": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                                                   _i, _i, _i, _i, _vp, _sz, _i, _i, C.POINTER(C.c_void_p), _sz, _vp]),
+    "pare_w4a16_forward_produced_allreduce": (_i, [_i, _vp, _vp, _vp, _vp, _i64, C.c_float, _i,
+                                                   _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                                                   _i, _i, _i, _i, _vp, _sz, _i, _i, C.POINTER(C.c_void_p), _sz, _vp]),
     "pare_w4a16_static_scratch_bytes": (_sz, []),
     "pare_w4a16_forward_static": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                        _i, _i, _i, _i, _vp]),

@@ -138,8 +138,10 @@ def prepare(x: Tensor, *, col_perm: Tensor | None = None, input_scale: Tensor | 
 
 def w4a16_forward_prepared(prep: PreparedActivations, packed_weight: Tensor, scale: Tensor | None, zero: Tensor | None,
                            group_size: int, *, bias: Tensor | None = None, meta_h2: Tensor | None = None,
-                           out: Tensor | None = None) -> Tensor:
-    """:func:`w4a16_forward` for activations that already are in operand order."""
+                           out: Tensor | None = None, peer=None) -> Tensor:
+    """:func:`w4a16_forward` for activations that already are in operand order.  ``peer`` (a
+    :class:`pare_b200.parallel.PeerAllReduce`): the layer is a row-parallel shard and the result is the sum over the
+    ranks, added inside the kernel's epilogue."""
     n, k_half = packed_weight.shape
     assert prep.k == 2 * k_half and packed_weight.dtype == torch.uint8 and packed_weight.is_contiguous()
     m, k = prep.rows, prep.k
@@ -149,6 +151,14 @@ def w4a16_forward_prepared(prep: PreparedActivations, packed_weight: Tensor, sca
     y = out if out is not None else torch.empty(m, n, device=dev, dtype=prep.dtype)
     L = _lib.lib()
     ws = _lib.workspace(dev, L.pare_w4a16_workspace_bytes(m, n, k, group_size))
+    if peer is not None:
+        status = L.pare_w4a16_forward_prepared_allreduce(
+            prep.data_ptr(), _lib.dtype_code(prep.dtype), packed_weight.data_ptr(),
+            _lib.ptr(scale), _lib.ptr(zero), _lib.ptr(meta_h2), _lib.ptr(bias),
+            y.data_ptr(), y.stride(0), m, n, k, group_size, ws.data_ptr(), ws.numel(),
+            peer.rank, peer.world, peer._ptrs, peer.buffer_bytes, _lib.current_stream(dev))
+        _lib.check(status, "pare_w4a16_forward_prepared_allreduce")
+        return y
     status = L.pare_w4a16_forward_prepared(
         prep.data_ptr(), _lib.dtype_code(prep.dtype), packed_weight.data_ptr(),
         _lib.ptr(scale), _lib.ptr(zero), _lib.ptr(meta_h2), _lib.ptr(bias),
@@ -160,7 +170,7 @@ def w4a16_forward_prepared(prep: PreparedActivations, packed_weight: Tensor, sca
 def w4a16_forward_produced(producer: int, a: Tensor, packed_weight: Tensor, scale: Tensor | None, zero: Tensor | None,
                            group_size: int, *, delta: Tensor | None = None, norm_weight: Tensor | None = None,
                            resid_out: Tensor | None = None, eps: float = 1e-5, bias: Tensor | None = None,
-                           meta_h2: Tensor | None = None, out: Tensor | None = None) -> Tensor:
+                           meta_h2: Tensor | None = None, out: Tensor | None = None, peer=None) -> Tensor:
     """The linear with its activations computed inside the streaming kernel (M <= 16).
 
     ``producer = _lib.PRODUCER_RMSNORM``: ``x = rmsnorm(a + delta) * norm_weight`` (``a [M, K]``; ``a + delta`` is
@@ -183,6 +193,14 @@ def w4a16_forward_produced(producer: int, a: Tensor, packed_weight: Tensor, scal
     y = out if out is not None else torch.empty(m, n, device=a.device, dtype=a.dtype)
     L = _lib.lib()
     ws = _lib.workspace(a.device, L.pare_w4a16_workspace_bytes(m, n, k, group_size))
+    if peer is not None:   # row-parallel shard: the sum over the ranks is added inside the kernel
+        status = L.pare_w4a16_forward_produced_allreduce(
+            producer, a.data_ptr(), _lib.ptr(delta), _lib.ptr(norm_weight), _lib.ptr(resid_out), a.stride(0), float(eps),
+            _lib.dtype_code(a.dtype), packed_weight.data_ptr(), _lib.ptr(scale), _lib.ptr(zero), _lib.ptr(meta_h2), _lib.ptr(bias),
+            y.data_ptr(), y.stride(0), m, n, k, group_size, ws.data_ptr(), ws.numel(),
+            peer.rank, peer.world, peer._ptrs, peer.buffer_bytes, _lib.current_stream(a.device))
+        _lib.check(status, "pare_w4a16_forward_produced_allreduce")
+        return y
     status = L.pare_w4a16_forward_produced(
         producer, a.data_ptr(), _lib.ptr(delta), _lib.ptr(norm_weight), _lib.ptr(resid_out), a.stride(0), float(eps),
         _lib.dtype_code(a.dtype), packed_weight.data_ptr(), _lib.ptr(scale), _lib.ptr(zero), _lib.ptr(meta_h2), _lib.ptr(bias),

@@ -181,9 +181,11 @@ class QuantizedLinear(nn.Module):
                 and self.g_idx is None and self.input_scale is None and rows <= 16
                 and self.in_features % 256 == 0 and self._kernel_group_size() % 128 == 0)
 
-    def forward_prepared(self, prep) -> Tensor:
+    def forward_prepared(self, prep, peer=None) -> Tensor:
         """Forward for activations handed over as :class:`PreparedActivations` (decode, rows <= 16):
-        the producing kernel wrote them in operand order, so no preparation launch is needed."""
+        the producing kernel wrote them in operand order, so no preparation launch is needed.  ``peer`` (a
+        ``PeerAllReduce``): this layer is a row-parallel shard; the result is the sum over the ranks, added inside
+        the kernel."""
         from pare_b200.kernels.matmul_int4 import w4a16_forward_prepared
 
         if not self.supports_prepared(prep.rows):
@@ -194,7 +196,7 @@ class QuantizedLinear(nn.Module):
         return w4a16_forward_prepared(
             prep, self._packed_weight_kernel,
             None if use_h2 else self._scale_kernel, None if use_h2 else self._zero_kernel,
-            self._kernel_group_size(), bias=self.bias, meta_h2=self._meta_h2_kernel if use_h2 else None)
+            self._kernel_group_size(), bias=self.bias, meta_h2=self._meta_h2_kernel if use_h2 else None, peer=peer)
 
     def _forward_produced(self, producer: int, a: Tensor, **kw) -> Tensor:
         from pare_b200.kernels.matmul_int4 import w4a16_forward_produced
@@ -217,11 +219,12 @@ class QuantizedLinear(nn.Module):
 
         return self._forward_produced(_lib.PRODUCER_RMSNORM, x, delta=delta, norm_weight=norm_weight, resid_out=resid_out, eps=eps)
 
-    def forward_silu_mul(self, gate_up: Tensor) -> Tensor:
-        """``self(silu(gate) * up)`` for a fused ``gate_up [rows <= 16, 2 * in_features]`` in one launch."""
+    def forward_silu_mul(self, gate_up: Tensor, peer=None) -> Tensor:
+        """``self(silu(gate) * up)`` for a fused ``gate_up [rows <= 16, 2 * in_features]`` in one launch; with ``peer`` (a
+        ``PeerAllReduce``) summed over the ranks inside the kernel (this layer being a row-parallel shard)."""
         from pare_b200.kernels import _lib
 
-        return self._forward_produced(_lib.PRODUCER_SILU_MUL, gate_up)
+        return self._forward_produced(_lib.PRODUCER_SILU_MUL, gate_up, peer=peer)
 
     # -- alternate constructors ----------------------------------------------
     @classmethod

@@ -100,7 +100,7 @@ class PeerAllReduce:
     sequence of calls.  Capturable in a CUDA graph.  2 <= world <= 8, one process per GPU on one node.
     """
 
-    def __init__(self, group=None, max_bytes: int = 256 << 10) -> None:
+    def __init__(self, group=None, max_bytes: int = 512 << 10) -> None:
         import ctypes as C
 
         import torch.distributed as dist
@@ -113,8 +113,10 @@ class PeerAllReduce:
         self.rank = dist.get_rank(group)
         if not 2 <= self.world <= 8:
             raise ValueError("PeerAllReduce serves 2..8 ranks")
-        # every 8 bytes of data travel with 8 bytes of validity marks
-        self.buffer_bytes = 4096 + 2 * self.world * ((2 * max_bytes + 255) // 256 * 256)
+        # every 8 bytes of data travel with 8 bytes of validity marks; the data area is split in two halves, one for the
+        # stand-alone all-reduce, one for the exchange fused into the row-parallel linears (fp32 partials: 8 bytes per
+        # element, i.e. max_bytes / 2 elements of a 16-bit tensor per call)
+        self.buffer_bytes = 4096 + 2 * (2 * self.world * ((2 * max_bytes + 255) // 256 * 256))
         L = _lib.lib()
         own = C.c_void_p()
         handle = C.create_string_buffer(64)
@@ -136,7 +138,12 @@ class PeerAllReduce:
         dist.barrier(group=group)   # nobody stores into a buffer that is not mapped everywhere yet
 
     def max_elements(self) -> int:
-        return ((self.buffer_bytes - 4096) // (2 * self.world) // 256 * 256) // 4
+        """Elements of a tensor the stand-alone all-reduce takes."""
+        return ((self.buffer_bytes - 4096) // 2 // (2 * self.world) // 256 * 256) // 4
+
+    def max_fused_elements(self) -> int:
+        """Output elements (rows x out_features) of a row-parallel linear whose sum is added inside the kernel."""
+        return ((self.buffer_bytes - 4096) // 2 // (2 * self.world) // 256 * 256) // 8
 
     def __call__(self, x, out=None):
         assert x.is_cuda and x.dim() == 2 and x.stride(1) == 1

@@ -4,7 +4,9 @@ Two child processes, one per GPU, NCCL only for the handle exchange.  Checks: th
 sum of the ranks' inputs rounded once to the tensor dtype (bit-exact: rank-order fp32 addition), identical
 on both ranks, over many back-to-back calls (double-buffered slots), over a queue of calls of different shapes
 with no host synchronisation between them while one rank launches late, eagerly and from a replayed CUDA
-graph, and the status word stays clean.
+graph, and the status word stays clean.  Then the same sum added INSIDE the row-parallel linears (tile and
+persistent streaming kernels, prepared and SwiGLU-producing forwards) against the unsharded layer, identical
+bits on both ranks, and a 2-block tensor-parallel decode stack against the unsharded stack.
 """
 
 import os
@@ -69,6 +71,53 @@ dist.all_gather(xs, x)
 once = sum(t.float() for t in xs).half()
 ok &= bool(torch.equal(out, (once.float() * world).half()))
 ok &= ar.status(x.device) == 0
+# ---- the sum over the ranks added INSIDE the row-parallel linears (no all-reduce launch) ----
+from pare_b200.decode import synthetic_linear, _take_cols, DecodeStack
+from pare_b200.kernels.matmul_int4 import prepare
+import numpy as np
+def rel(y, ref):
+    ref = ref.float(); e = (y.float() - ref).abs() / torch.maximum(ref.abs(), 1e-2 * ref.abs().max())
+    return float(e.max()), float(e.mean())
+for (n, k), ms in (((4096, 4096), (1, 4)), ((4096, 14336), (1, 3)), ((1024, 2048), (2,))):   # tile kernel, persistent kernel (K slices), small
+    full = synthetic_linear(n, k, seed=n + k, device="cuda")
+    shard = _take_cols(full, rank * k // world, (rank + 1) * k // world)
+    for m in ms:
+        g = torch.Generator(device="cuda").manual_seed(m)
+        x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+        xs = x[:, rank * k // world:(rank + 1) * k // world].contiguous()
+        ys = [shard.forward_prepared(prepare(xs), peer=ar) for _ in range(4)]        # back to back, no host sync
+        gu = torch.randn(m, 2 * k, device="cuda", generator=g).to(torch.bfloat16)    # SwiGLU producer + exchange
+        kk = k // world
+        gus = torch.cat([gu[:, rank * kk:(rank + 1) * kk], gu[:, k + rank * kk:k + (rank + 1) * kk]], dim=1).contiguous()
+        y2 = shard.forward_silu_mul(gus, peer=ar)
+        torch.cuda.synchronize()
+        ref = full(x)
+        mx, mean = rel(ys[0], ref)
+        ok &= mx <= 1e-2 and mean <= 2.5e-3
+        ok &= all(bool(torch.equal(ys[0], y)) for y in ys[1:])
+        act = (torch.nn.functional.silu(gu[:, :k].float()) * gu[:, k:].float()).to(torch.bfloat16)
+        mx, mean = rel(y2, full(act))
+        ok &= mx <= 1e-2 and mean <= 2.5e-3
+        both = [torch.empty_like(ys[0]) for _ in range(world)]
+        dist.all_gather(both, ys[0])
+        ok &= all(bool(torch.equal(both[0], b)) for b in both)                        # identical bits on every rank
+ok &= ar.status(torch.device("cuda", rank)) == 0
+# a 2-block tensor-parallel decode step (5 launches per block) against the unsharded stack on the same GPU
+shape = (1024, 2048, 8, 2, 128, 2)
+tp = DecodeStack(shape, dtype=torch.float16, max_seq_len=512, seed=3, tp_world=world)
+tp.prefill_cache(2, 224)
+xh = torch.randn(2, 1024, generator=torch.Generator().manual_seed(5)).half().cuda()
+for _ in range(3):
+    yt = tp(xh)
+one = DecodeStack(shape, dtype=torch.float16, max_seq_len=512, seed=3, tp_world=1, tp_rank=0)
+one.prefill_cache(2, 224)
+for _ in range(3):
+    yo = one(xh)
+mx, mean = rel(yt, yo)
+print("tp stack vs unsharded", rank, mx, mean, flush=True)
+ok &= mx <= 3e-2 and mean <= 3e-3
+ok &= tp.peer_reduce.status(torch.device("cuda", rank)) == 0
+dist.barrier(); tp.peer_reduce.close()
 flag = torch.tensor([1 if ok else 0], device="cuda")
 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
 ar.close()

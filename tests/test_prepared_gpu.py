@@ -259,14 +259,14 @@ def test_decode_stack_prefill_equals_token_by_token(cuda_lib):
 
 @pytest.mark.parametrize("m", [1, 3])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_decode_stack_step_against_fp32_restatement(m, dtype, cuda_lib):
-    """Two blocks of a small Llama-shaped stack, one decode step, against an fp32 restatement of the block written
-    here from the oracle's pieces (not against the stack's other route): RMSNorm -> q|k|v linear -> rotary embedding of
-    q and the new key -> KIVI cache update -> attention over the cache -> o linear -> residual add -> RMSNorm ->
-    gate|up linear -> SwiGLU -> down linear -> residual add.  Catches wiring errors both routes of the stack would
-    share (residual ping-pong, head slicing, rotary position).  The restatement keeps fp32 between the stages where
-    the kernels round to the activation dtype (eleven hand-overs in two blocks), hence max <= 3e-2, mean <= 3e-3
-    for fp16 and 1e-1 / 1.2e-2 for bf16 (8 significant bits per hand-over)."""
+def test_decode_stack_step_against_restatement(m, dtype, cuda_lib):
+    """Two blocks of a small Llama-shaped stack, one decode step, against a restatement of the block written here
+    from the oracle's pieces (not against the stack's other route): RMSNorm -> q|k|v linear -> rotary embedding of q
+    and the new key -> KIVI cache update -> attention over the cache -> o linear -> residual add -> RMSNorm -> gate|up
+    linear -> SwiGLU -> down linear -> residual add.  Catches wiring errors both routes of the stack would share
+    (residual ping-pong, head slicing, rotary position).  Every stage is computed in fp32 from the previous stage's
+    result rounded to the activation dtype, which is where the kernels round too; what is left is the kernels' own
+    error, eleven stages deep: max <= 3e-2, mean <= 2e-3 for fp16, 1.5e-1 / 1e-2 for bf16 (8 significant bits)."""
     from oracle import kivi as ok
     shape = (1024, 2048, 8, 2, 128, 2)
     hidden, ffn, hq, hkv, d, layers = shape
@@ -291,29 +291,35 @@ def test_decode_stack_step_against_fp32_restatement(m, dtype, cuda_lib):
 
     rows = stack.rope.cpu().numpy()
     pos = ctx
+    r = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dtype).float().numpy()   # round to the dtype
 
     def rms(h, w):
-        return h / np.sqrt((h * h).mean(-1, keepdims=True) + 1e-5) * w
+        return r(h / np.sqrt((h * h).mean(-1, keepdims=True) + 1e-5) * w)
 
     def lin(layer, a):
         n = layer.out_features
-        return ow.linear(a, layer.packed_weight.cpu().numpy(), layer.scale.cpu().numpy().reshape(n, -1),
-                         layer.zero.cpu().numpy().reshape(n, -1))
+        return r(ow.linear(a, layer.packed_weight.cpu().numpy(), layer.scale.cpu().numpy().reshape(n, -1),
+                           layer.zero.cpu().numpy().reshape(n, -1)))
 
     h = x.float().numpy()
+    delta = None
     for i, blk in enumerate(stack.blocks):
+        if delta is not None:
+            h = r(h + delta)
         qkv = lin(blk.qkv, rms(h, blk.norm1.float().cpu().numpy()))
         q = qkv[:, : hq * d].reshape(m, hq, 1, d)
         k1 = qkv[:, hq * d:(hq + hkv) * d].reshape(m, hkv, 1, d)
         v1 = qkv[:, (hq + hkv) * d:].reshape(m, hkv, 1, d)
-        q, k1 = ok.apply_rope(q, rows[pos]), ok.apply_rope(k1, rows[pos])
-        fk, fv = caches[i].update(k1.astype(np.float32), v1.astype(np.float32))
-        attn = ok.decode_attention(q.astype(np.float32), fk, fv).reshape(m, hq * d)
-        h = h + lin(blk.o, attn)
+        q, k1 = r(ok.apply_rope(q, rows[pos])), r(ok.apply_rope(k1, rows[pos]))
+        fk, fv = caches[i].update(k1, v1)
+        attn = r(ok.decode_attention(q, fk, fv).reshape(m, hq * d))
+        h = r(h + lin(blk.o, attn))
         gu = lin(blk.gate_up, rms(h, blk.norm2.float().cpu().numpy()))
         gate, up = gu[:, :ffn], gu[:, ffn:]
-        h = h + lin(blk.down, gate / (1 + np.exp(-gate)) * up)
-    mx, mean = ow.rel_err(y, h)
-    bars = (3e-2, 3e-3) if dtype == torch.float16 else (1e-1, 1.2e-2)
+        delta = lin(blk.down, r(gate / (1 + np.exp(-gate)) * up))
+    want = r(h + delta)
+    mx, mean = ow.rel_err(y, want)
+    print("stack vs restatement", dtype, m, mx, mean)
+    bars = (3e-2, 2e-3) if dtype == torch.float16 else (1.5e-1, 1e-2)
     assert mx <= bars[0] and mean <= bars[1], (mx, mean)
     assert stack.cache.seq_len(0) == stack.cache.seq_len(1) == ctx + 1

@@ -85,6 +85,10 @@ def test_awq_export_equals_reference_exporter_bits(golden):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_reference_checkpoint_runs_on_the_kernels(dtype, golden, cuda_lib):
+    """The layers rebuilt from the reference-written file, on the CUDA path, against the oracle on the file's own
+    tensors (bars of tests/parity.py: 1 row runs the streaming kernel, 64 rows the tensor-core kernel); the oracle
+    itself reproduces the outputs the reference's model gave on the same fp16 inputs."""
+    from parity import check_linear, oracle_pair
     io = golden("ref_ckpt_io.npz")
     model = pare_b200.load_quantized(MLP(), GOLDEN / "ref_ckpt", use_kernel=True).cuda()
     assert model.up_proj.use_kernel and model.down_proj.use_kernel
@@ -92,43 +96,46 @@ def test_reference_checkpoint_runs_on_the_kernels(dtype, golden, cuda_lib):
         for m in ("1", "64"):
             x = torch.from_numpy(io["x" + m]).cuda().to(dtype)
             up = model.up_proj(x)
-            assert hasattr(model.up_proj, "_packed_weight_kernel") and up.dtype == dtype
-            if dtype == torch.float16:   # same inputs as the reference saw
-                _bars(up.float().cpu().numpy(), io["up" + m])
-                _bars(model(x).float().cpu().numpy(), io["y" + m])
-            else:                        # bf16 rounds the input: compare with the eager branch on the same input
-                model.up_proj.use_kernel = False
-                ref = model.up_proj(x.float()).float().cpu().numpy()
-                model.up_proj.use_kernel = True
-                mx, mean = rel_err(up.float().cpu().numpy(), ref)
-                assert mx <= 1e-2 and mean <= 2.5e-3, (mx, mean)
+            assert hasattr(model.up_proj, "_packed_weight_kernel") and up.dtype == dtype and up.shape == (int(m), 768)
+            check_linear(up, model.up_proj, x, dtype)
+            h = torch.relu(up)
+            check_linear(model.down_proj(h), model.down_proj, h, dtype)
+            if dtype == torch.float16:
+                ref32, _ = oracle_pair(model.up_proj, x, dtype)
+                b16 = model.up_proj.bias.detach().half().float().cpu().numpy() - model.up_proj.bias.detach().float().cpu().numpy()
+                assert np.allclose(ref32 - b16, io["up" + m], rtol=0, atol=3e-5)     # oracle == the reference's own run
+                mx, mean = rel_err(model(x).float().cpu().numpy(), io["y" + m])       # whole model, end to end
+                assert mx <= 5e-2 and mean <= 2e-3, (mx, mean)                        # two layers, weights cast at 64 rows
 
 
 @pytest.mark.gpu
 def test_reference_checkpoint_tensor_parallel_slices_on_the_kernels(golden, cuda_lib):
-    """Both ranks' slices of the reference-written file, each through the kernels on this GPU: column shards
-    concatenate, row shards add up to the reference's outputs."""
+    """Both ranks' slices of the reference-written file, each through the kernels on this GPU: the column shards'
+    outputs concatenate to the unsharded layer's, the row shards' partial sums add up to it."""
+    from parity import check_linear
     io = golden("ref_ckpt_io.npz")
     plan = {"up_proj": "column", "down_proj": "row"}
+    whole = pare_b200.load_quantized(MLP(), GOLDEN / "ref_ckpt", use_kernel=True).cuda()
+    shards = [pare_b200.load_quantized(MLP(), GOLDEN / "ref_ckpt", use_kernel=True, tp_plan=plan, tp_rank=r, tp_world=2).cuda()
+              for r in range(2)]
     with torch.no_grad():
         for m in ("1", "64"):
             x = torch.from_numpy(io["x" + m]).cuda()
-            total = None
-            ups = []
-            for rank in range(2):
-                shard = pare_b200.load_quantized(MLP(), GOLDEN / "ref_ckpt", use_kernel=True, tp_plan=plan, tp_rank=rank,
-                                                 tp_world=2).cuda()
-                assert shard.up_proj.out_features == 384 and shard.down_proj.in_features == 384
-                up = shard.up_proj(x)
-                ups.append(up)
-                part = shard.down_proj(torch.relu(up)).float()
-                total = part if total is None else total + part
-            _bars(torch.cat(ups, dim=1).float().cpu().numpy(), io["up" + m])
-            _bars(total.cpu().numpy(), io["y" + m])
+            ups = [s.up_proj(x) for s in shards]
+            assert ups[0].shape == (int(m), 384)
+            up = torch.cat(ups, dim=1)
+            assert torch.equal(up, whole.up_proj(x))                 # output rows are independent: same bits
+            h = torch.relu(up)
+            parts = [s.down_proj(h[:, r * 384:(r + 1) * 384].contiguous()).float() for r, s in enumerate(shards)]
+            total = (parts[0] + parts[1]).half()
+            # rank 0 carries the bias; the sum of the two partial products is the unsharded product up to rounding.
+            # Each partial is itself rounded to fp16 at its own (larger) magnitude before the sum: max <= 2e-2 here.
+            check_linear(total, whole.down_proj, h, torch.float16, max_rel=2e-2)
 
 
 @pytest.mark.gpu
 def test_awq_gemm_import_runs_on_the_kernels(golden, cuda_lib):
+    from parity import check_linear
     g = golden("awq_gemm_layer.npz")
     layer = from_awq_gemm(*(torch.from_numpy(g[k]) for k in ("qweight", "qzeros", "scales", "bias")), group_size=128).cuda()
     layer.use_kernel = True
@@ -137,6 +144,6 @@ def test_awq_gemm_import_runs_on_the_kernels(golden, cuda_lib):
         for m in (1, 4, 16, 64):
             y = layer(x[:m])
             assert y.dtype == torch.float16 and y.shape == (m, 256)
-            _bars(y.float().cpu().numpy(), _awq_oracle(g, g["x"][:m]))
-            mx, mean = rel_err(y.float().cpu().numpy(), g["y"][:m])      # fp16 scales of the format: widened max
-            assert mx <= 5e-2 and mean <= 1e-3, (mx, mean)
+            check_linear(y, layer, x[:m], torch.float16)                  # on what the AutoAWQ tensors hold
+            mx, mean = rel_err(y.float().cpu().numpy(), g["y"][:m])      # the reference layer's fp32-scale outputs:
+            assert mx <= 5e-2 and mean <= 1.5e-3, (mx, mean)              # fp16 scales of the format, widened max
