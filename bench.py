@@ -681,7 +681,9 @@ def run_ours(args) -> None:
         "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
         "e2e": {"value": args.batch * steps / sec_e2e, "unit": UNIT,
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
-        "gpu_launches": (LAUNCHES_PER_BLOCK + (2 if world > 1 and stack.peer_reduce is not None else 0)) * args.layers * steps,
+        # under tensor parallelism the sums over the ranks are added inside the o and down kernels: still 5 launches a block
+        "gpu_launches": (LAUNCHES_PER_BLOCK + (0 if world == 1 or (stack.peer_reduce is not None and
+                         args.batch * hidden <= stack.peer_reduce.max_fused_elements()) else 2)) * args.layers * steps,
         "clocks": clocks,
     }
     # bytes one step must move: all linears (algorithmic) + the cache

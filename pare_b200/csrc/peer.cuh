@@ -43,7 +43,7 @@ struct PeerCtx {
   size_t slot_bytes;   // bytes per (parity, rank) slot
 };
 
-__device__ __forceinline__ bool peer_on(const PeerCtx& pc) { return pc.buf[0] != nullptr; }
+__host__ __device__ __forceinline__ bool peer_on(const PeerCtx& pc) { return pc.buf[0] != nullptr; }
 
 // epoch of this call (read after the dependency wait: the previous call has advanced the word by then)
 __device__ __forceinline__ uint32_t peer_epoch(const PeerCtx& pc) {

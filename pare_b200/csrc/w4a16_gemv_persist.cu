@@ -59,6 +59,7 @@ struct StreamPlan {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void named_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -109,7 +110,9 @@ __device__ __forceinline__ Item item_of(const StreamPlan& pl, int bl, int i) {
 
 // SPW = 128-column steps per consumer warp and slice, RB = 16-row blocks per tile, MB = blocks of 8
 // activation rows (M <= 8 MB).
-template <typename T, bool META16, int SPW, int RB, int MB, bool PROD>
+// PEER: the layer is a row-parallel shard of a tensor-parallel model and the epilogue warps add the ranks' partial
+// outputs (peer.cuh).  A template parameter so that the single-GPU instantiations carry none of that code.
+template <typename T, bool META16, int SPW, int RB, int MB, bool PROD, bool PEER>
 __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const GemvParams p, const StreamPlan pl) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int R = 16 * RB;   // rows per tile
@@ -169,6 +172,18 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
         const int r = it.tile * R + lane;
         bulk_load(ring_u32 + (slot * R + lane) * pitch + lo * 64,
                   p.packed + (size_t)r * (p.K >> 1) + (size_t)(s0 + lo) * 64, bytes, full0 + slot * 8);
+        // the item's scale / zero rows towards this SM's L1: the consumer warps read them (row-strided, one line per
+        // row and array) when they reach the item, two or three items from now
+        const size_t ridx = (size_t)r * p.ngroups + s0 + lo;
+        if (META16) {
+          prefetch_l1(p.meta_h2 + ridx);
+          prefetch_l1(p.meta_h2 + ridx + (hi - lo) - 1);
+        } else {
+          prefetch_l1(p.scale + ridx);
+          prefetch_l1(p.scale + ridx + (hi - lo) - 1);
+          prefetch_l1(p.zero + ridx);
+          prefetch_l1(p.zero + ridx + (hi - lo) - 1);
+        }
       }
       if (++slot == depth) { slot = 0; ph ^= 1; }
     }
@@ -190,7 +205,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemv_persist_kernel(const G
     if (ew >= n_epi) return;
     // tensor-parallel row-parallel layer: the ranks' partial outputs are exchanged and added right here (peer.cuh),
     // while the consumer warps stream on
-    const bool peer = peer_on(p.peer);
+    const bool peer = PEER && peer_on(p.peer);
     const uint32_t pe = peer ? peer_epoch(p.peer) : 0u;
     bool peer_timeout = false;
     for (int i = ew; i < n_items; i += n_epi) {
@@ -610,9 +625,17 @@ int gemv_persist_launch(const gemv::GemvParams& p, int x_dtype, cudaStream_t str
   auto pick = [&](auto t_tag, auto m16_tag) -> int {
     using TT = typename decltype(t_tag)::type;
     constexpr bool M16 = decltype(m16_tag)::value;
-    if (p.producer) return pl.rows == 32 ? launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 2, 1, true>) : PARE_ERR_UNSUPPORTED;
-    return pl.rows == 32 ? launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 2, 1, false>)
-                         : launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 1, 2, false>);
+    if (peer_on(p.peer)) {   // row-parallel shard: fp32 metadata only
+      if constexpr (M16) return PARE_ERR_UNSUPPORTED;
+      else {
+        if (p.producer) return pl.rows == 32 ? launch(w4a16_gemv_persist_kernel<TT, false, kStepsPW, 2, 1, true, true>) : PARE_ERR_UNSUPPORTED;
+        return pl.rows == 32 ? launch(w4a16_gemv_persist_kernel<TT, false, kStepsPW, 2, 1, false, true>)
+                             : launch(w4a16_gemv_persist_kernel<TT, false, kStepsPW, 1, 2, false, true>);
+      }
+    }
+    if (p.producer) return pl.rows == 32 ? launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 2, 1, true, false>) : PARE_ERR_UNSUPPORTED;
+    return pl.rows == 32 ? launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 2, 1, false, false>)
+                         : launch(w4a16_gemv_persist_kernel<TT, M16, kStepsPW, 1, 2, false, false>);
   };
   const bool m16 = p.meta_h2 != nullptr;
   if (x_dtype == PARE_F16) return m16 ? pick(TypeTag<__half>{}, std::true_type{}) : pick(TypeTag<__half>{}, std::false_type{});
