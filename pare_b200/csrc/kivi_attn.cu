@@ -62,9 +62,7 @@ using gemv::mbar_init;
 using gemv::mbar_test;
 using gemv::smem_u32;
 
-constexpr int kScoreWarps = 4;
-constexpr int kValueWarps = 4;
-constexpr int kComputeThreads = (kScoreWarps + kValueWarps) * 32;   // 256
+constexpr int kComputeThreads = 256;     // two teams of four warps
 constexpr int kAttnThreads = kComputeThreads;
 constexpr int kAttnWarps = 8;            // the residual branch and the merge use all warps alike
 constexpr int kD = 128;
@@ -72,7 +70,7 @@ constexpr int kHeads = 8;
 constexpr int kMaxVG = 4;                // value scale / zero groups per token at most (32 channels each)
 constexpr int kBlk = 128;                // compressed tokens per pipeline block
 constexpr int kMaxStages = 4;
-constexpr int kMaxNb = 16;               // blocks per compressed split the planner chooses at most
+constexpr int kMaxNb = 64;               // blocks per compressed split the planner chooses at most
 constexpr int kMaxSplits = 250;          // splits per (batch, head) the merge takes
 constexpr int kResChunk = 64;            // residual tokens per split
 constexpr int kResPitch = 320;           // bytes per staged residual row (256 + 64: conflict-free 16-byte reads down a column)
@@ -86,13 +84,13 @@ constexpr int kQS = 132;   // floats per staged query row: channel c at (c>>3 & 
 constexpr uint32_t kSpin = 1u << 22;
 
 // ---- shared-memory map (bytes) ----
-constexpr int kOffBars = 0;       // data_full[4] data_empty[4] p_full[2] p_empty[2] res_bar
+constexpr int kOffBars = 0;       // data_full[4] data_empty[4]
 constexpr int kOffLast = 104;
 constexpr int kOffStM = 128;      // [8]
 constexpr int kOffStL = 160;      // [8]
 constexpr int kOffAlpha = 320;    // [2][8]
 constexpr int kOffGmax = 384;     // [2][4][8]
-constexpr int kOffFin = 640;      // [4 score warps][8 heads][1 + kMaxVG]: sum, constant term per value group
+constexpr int kOffFin = 640;      // [8 warps][8 heads][1 + kMaxVG]: sum, constant term per value group
 constexpr int kFinStride = 1 + kMaxVG;
 constexpr int kOffQ = 2048;       // [8][kQS] fp32
 constexpr int kOffP = kOffQ + kHeads * kQS * 4;            // 6272
@@ -192,11 +190,60 @@ __device__ __forceinline__ void wait_bar(uint32_t bar, uint32_t parity, int* sta
   atomicExch(status, PARE_ERR_TIMEOUT);
 }
 
-// codes - CENTER of one word as exact fp16 pairs: four pairs (c_k, c_k+4) at 4 bits, eight pairs (c_j, c_j+8) at 2 bits
-template <int BITS, int CENTER>
-__device__ __forceinline__ void unpack_exact(uint32_t w, uint32_t (&p)[BITS == 4 ? 4 : 8]) {
-  if constexpr (BITS == 4) unpack_codes_exact<CENTER>(w, p);
-  else unpack_codes2_exact<CENTER>(w, p);
+// ---- codes as fp16 subnormals ----
+// A code field that lies inside the ten mantissa bits of an fp16 whose exponent bits are zero IS the number
+// code * 2^(b - 24) (b = the field's lowest bit): masking alone yields an exact tensor-core operand, with no
+// offset to remove.  A 4-bit word gives the pairs (c_k, c_k+4) at b = 0 (k even) or 4 (k odd); a 2-bit word the
+// pairs (c_j, c_j+8) at b = 2j (j <= 4) or 2(j - 5) after one shift.  The other operand of position e = k or j is
+// pre-multiplied by code_factor(e) = 2^(S - b), so every product carries the same 2^(S - 24) = 1 / kCodeOut.
+template <int BITS>
+__host__ __device__ constexpr float code_factor(int e) {
+  if (BITS == 4) return (e & 1) ? 0.0625f : 1.f;
+  const int b = (e & 7) <= 4 ? 2 * (e & 7) : 2 * ((e & 7) - 5);
+  return 4.f / (float)(1 << b);
+}
+template <int BITS>
+constexpr float kCodeOut = BITS == 4 ? 16777216.f : 4194304.f;
+
+// The value side keeps offset-free CENTRED codes instead (code - kVCentre, one more half2 operation per pair): its
+// other operand, the probabilities, is all positive, so with uncentred codes the tensor-core sum and the fp32 zero
+// term would be two large numbers that cancel, and the accumulation error of the former showed up a hundredfold in
+// the output (1e-2 instead of 5e-4 against the fp32 restatement at 32768 tokens).  The key side's other operand has
+// random signs and no such cancellation.
+template <int BITS>
+constexpr int kVCentre = BITS == 4 ? 8 : 2;
+template <int BITS>
+__device__ __forceinline__ void unpack_centred(uint32_t w, uint32_t (&p)[BITS == 4 ? 4 : 8]) {
+  if constexpr (BITS == 4) unpack_codes_exact<kVCentre<BITS>>(w, p);
+  else unpack_codes2_exact<kVCentre<BITS>>(w, p);
+}
+
+template <int BITS>
+__device__ __forceinline__ void unpack_sub(uint32_t w, uint32_t (&p)[BITS == 4 ? 4 : 8]) {
+  if constexpr (BITS == 4) {
+    const uint32_t t = w >> 8;
+    p[0] = w & 0x000f000fu; p[1] = w & 0x00f000f0u; p[2] = t & 0x000f000fu; p[3] = t & 0x00f000f0u;
+  } else {
+    const uint32_t t = w >> 10;
+#pragma unroll
+    for (int j = 0; j < 5; ++j) p[j] = w & (0x00030003u << (2 * j));
+#pragma unroll
+    for (int j = 5; j < 8; ++j) p[j] = t & (0x00030003u << (2 * (j - 5)));
+  }
+}
+
+// two independent fp32 operations per instruction
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 x, y;\n\tmov.b64 x, {%2, %3};\n\tmov.b64 y, {%4, %5};\n\tmul.rn.f32x2 x, x, y;\n\tmov.b64 {%0, %1}, x;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 x, y, z;\n\tmov.b64 x, {%2, %3};\n\tmov.b64 y, {%4, %5};\n\tmov.b64 z, {%6, %7};\n\tfma.rn.f32x2 x, x, y, z;\n\tmov.b64 {%0, %1}, x;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
 }
 
 // byte offset, inside a head row of a probability buffer, of token tl (0..127) of the block: the operand order of the
@@ -225,7 +272,6 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
   constexpr int LB = 4 * BITS;                   // bytes of those 32 codes
   constexpr int KROW = kD * BITS / 8;            // bytes of a token's key codes
   constexpr int VROW = kBlk * BITS / 8;          // bytes of a channel's value codes in a 128-token block
-  constexpr int VCENTER = BITS == 4 ? 8 : 2;     // value codes are centred (halves the magnitude of the products)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -233,8 +279,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
   const bool is_res = (split >= p.n_csplit);
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
-  const uint32_t data_full = smem_u32(bars), data_empty = smem_u32(bars + 4), p_full = smem_u32(bars + 8),
-                 p_empty = smem_u32(bars + 10), res_bar = smem_u32(bars + 12);
+  const uint32_t data_full = smem_u32(bars), data_empty = smem_u32(bars + 4);
   int* s_last = reinterpret_cast<int*>(smem + kOffLast);
   float* st_m = reinterpret_cast<float*>(smem + kOffStM);
   float* st_l = reinterpret_cast<float*>(smem + kOffStL);
@@ -256,13 +301,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(data_full + i * 8, 1);
-      mbar_init(data_empty + i * 8, kAttnWarps);
+      mbar_init(data_empty + i * 8, 4);   // the four warps of the team that owns the block
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(p_full + i * 8, kScoreWarps);
-      mbar_init(p_empty + i * 8, kValueWarps);
-    }
-    mbar_init(res_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   pdl_launch_dependents();
@@ -274,11 +314,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
   const int nblk = is_res ? 0 : min(p.nb, nblk_total - blk0);
 
   // one block of the compressed cache into its ring slot (six bulk copies on the slot's barrier); issued by one thread
-  auto issue_block = [&](int i) {
-    const int slot = i % p.stages;
+  const int lg = 31 - __clz(G);   // G is a power of two
+  auto issue_block = [&](int i, int slot) {
     const int t0 = (blk0 + i) * kBlk;
-    const int valid = min(kBlk, p.n_comp - t0), ngroups = valid / G;
-    const size_t grow = bh * (p.cap / G) + t0 / G;
+    const int valid = min(kBlk, p.n_comp - t0), ngroups = valid >> lg;
+    const size_t grow = bh * (size_t)(p.cap >> lg) + (t0 >> lg);
     const uint32_t dst = smem_u32(stage + slot * sbytes), bar = data_full + slot * 8;
     mbar_expect_tx(bar, valid * KROW + 2 * ngroups * kD * 4 + kD * VROW + 2 * valid * 4 * VG);
     bulk_load(dst, p.k_codes + (bh * p.cap + t0) * (size_t)KROW, valid * KROW, bar);
@@ -290,7 +330,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
   };
   // the compressed cache does not change during a decode step, so the first stages are fetched before the dependency wait
   if (warp == kAttnWarps - 1 && lane == 0)
-    for (int i = 0; i < nblk && i < p.stages; ++i) issue_block(i);
+    for (int i = 0; i < nblk && i < p.stages; ++i) issue_block(i, i);
 
   pdl_wait();   // q, the newest token and the residual window may come from the previous kernels
 
@@ -298,6 +338,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
   unsigned char* rv_s = stage + kResChunk * kResPitch;
   int valid = 0;           // tokens a residual split attends to
   int chunk_start = 0;
+  constexpr int kResLoads = kResChunk * 32 / kComputeThreads;   // 16-byte pieces of the window per thread
+  uint4 res_regs[kResLoads];
+  int res_total = 0;
   if (is_res) {
     chunk_start = (split - p.n_csplit) * kResChunk;
     valid = min(kResChunk, p.n_res - chunk_start);
@@ -306,14 +349,22 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
     // the newest token, if handed in separately, is the last window position
     const bool has_new = p.new_k != nullptr && chunk_start + valid == p.n_res;
     const int ncopy = has_new ? valid - 1 : valid;
-    if (warp == 0) {
-      if (lane == 0) mbar_expect_tx(res_bar, ncopy * 2 * kD * (int)sizeof(T));
-      __syncwarp();
-      for (int i = lane; i < ncopy; i += 32) {
-        bulk_load(smem_u32(rk_s + i * kResPitch), rk + (int64_t)(chunk_start + i) * p.r_st, kD * sizeof(T), res_bar);
-        bulk_load(smem_u32(rv_s + i * kResPitch), rv + (int64_t)(chunk_start + i) * p.r_st, kD * sizeof(T), res_bar);
+    // the window rows as 16-byte pieces straight into registers (all in flight at once); they are stored to the
+    // padded stage after the query rows below have been staged
+    {
+      const int total = res_total = ncopy * 32;   // 16 pieces of K and 16 of V per token
+#pragma unroll
+      for (int j = 0; j < kResLoads; ++j) {
+        const int idx = threadIdx.x + j * kComputeThreads;
+        res_regs[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (idx < total) {
+          const int row = idx >> 5, part = idx & 31;
+          const T* src = (part < 16 ? rk : rv) + (int64_t)(chunk_start + row) * p.r_st + (part & 15) * 8;
+          res_regs[j] = __ldcg(reinterpret_cast<const uint4*>(src));
+        }
       }
-    } else if (warp == 1 && has_new) {
+    }
+    if (warp == 1 && has_new) {
       const bool is_v = lane >= 16;
       const int part = lane & 15;   // 16 bytes each
       const T* src = reinterpret_cast<const T*>(is_v ? p.new_v : p.new_k) + (int64_t)b * p.n_sb + (int64_t)h * p.n_sh;
@@ -348,46 +399,77 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
         const T* e = reinterpret_cast<const T*>(&raw);
         lo4 = make_float4(to_float<T>(e[0]), to_float<T>(e[1]), to_float<T>(e[2]), to_float<T>(e[3]));
         hi4 = make_float4(to_float<T>(e[4]), to_float<T>(e[5]), to_float<T>(e[6]), to_float<T>(e[7]));
+        if (!is_res) {   // the compressed splits multiply q by the factor of its channel's position in a code word
+          lo4.x *= code_factor<BITS>(0); lo4.y *= code_factor<BITS>(1); lo4.z *= code_factor<BITS>(2); lo4.w *= code_factor<BITS>(3);
+          hi4.x *= code_factor<BITS>(4); hi4.y *= code_factor<BITS>(5); hi4.z *= code_factor<BITS>(6); hi4.w *= code_factor<BITS>(7);
+        }
       }
       *reinterpret_cast<float4*>(qf + hh * kQS + q_pos(c8)) = lo4;
       *reinterpret_cast<float4*>(qf + hh * kQS + q_pos(c8) + 4) = hi4;
     }
   }
+  if (is_res) {
+#pragma unroll
+    for (int j = 0; j < kResLoads; ++j) {
+      const int idx = threadIdx.x + j * kComputeThreads;
+      if (idx < res_total) {
+        const int row = idx >> 5, part = idx & 31;
+        *reinterpret_cast<uint4*>((part < 16 ? rk_s : rv_s) + row * kResPitch + (part & 15) * 16) = res_regs[j];
+      }
+    }
+  }
   named_sync(1, kComputeThreads);
 
   if (!is_res) {
+    // ================= compressed split: two teams of four warps, team t takes blocks t, t + 2, ... =================
+    // Inside a team every warp plays both parts on the team's current block: scores and probabilities of its 32 tokens,
+    // then O += codes_v^T . P for its 32 channels; two named barriers per block order the team's probability buffer.
+    // The teams never wait for each other: while one is in a barrier or a dependency stall the other one issues.
     const float scale2 = p.sm_scale * kLog2e;   // scores in base-2 units: p = exp2(s2 - m2)
-    if (warp < kScoreWarps) {
-      // ================= score warps: tokens [32 warp, 32 warp + 32) of every block =================
-      // this lane's query row (head gid, channels 32 tig .. + 31 in runs of eight) stays in shared memory and is read
-      // once per token group
-      const float* qrow = qf + gid * kQS + tig * 8;
-      // where this lane's four (tile, row half) tokens go in a probability row, per head of its pair
-      int poff[2][2][2];
+    const float scale2o = scale2 * kCodeOut<BITS>;   // the code products carry 1 / kCodeOut
+    const int team = warp >> 2, tw = warp & 3;
+    const int team_bar = 2 + team;
+    const float* qrow = qf + gid * kQS + tig * 8;   // this lane's query row (head gid, channels 32 tig .. + 31 in runs of eight)
+    unsigned char* pst = Pring + team * p_stage_bytes(VG);   // the team's probability buffer
+    float* gm = gmax_s + team * (4 * kHeads);
+    // where this lane's four (tile, row half) tokens go in a probability row, per head of its pair
+    int poff[2][2][2];
 #pragma unroll
-      for (int tile = 0; tile < 2; ++tile)
+    for (int tile = 0; tile < 2; ++tile)
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf)
+      for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int tl = 32 * warp + 16 * tile + gid + 8 * hf, head = 2 * tig + e;
-            poff[tile][hf][e] = head * kPHead + p_offset<BITS>(tl, head);
-          }
+        for (int e = 0; e < 2; ++e) {
+          const int tl = 32 * tw + 16 * tile + gid + 8 * hf, head = 2 * tig + e;
+          poff[tile][hf][e] = head * kPHead + p_offset<BITS>(tl, head);
+        }
+    const int pg = VG == 1 ? 0 : tw;   // value part: channels [32 tw, 32 tw + 32) = one value group
+    const int pchunk = ((tig ^ (gid >> 1)) & 3) * 16;
 
-      float m_run[2] = {kNegBig, kNegBig}, l_run[2] = {0.f, 0.f};
-      float z_run[VG][2];   // sum of p * (value zero + centre * value scale): the constant term of the output
+    float m_run[2] = {kNegBig, kNegBig}, l_run[2] = {0.f, 0.f};
+    float z_run[VG][2];   // sum of p * (value zero + centre * value scale): the constant term of the output
 #pragma unroll
-      for (int g = 0; g < VG; ++g) z_run[g][0] = z_run[g][1] = 0.f;
+    for (int g = 0; g < VG; ++g) z_run[g][0] = z_run[g][1] = 0.f;
+    float oacc[2][4];     // value part: channels (32 tw + 16 mt + gid, + 8) x heads (2 tig, 2 tig + 1)
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oacc[mt][e] = 0.f;
 
-      for (int i = 0; i < nblk; ++i) {
-        const int slot = i % p.stages, ps = i & 1;
-        const unsigned char* st = stage + slot * sbytes;
-        const int t0 = (blk0 + i) * kBlk;
-        const int bvalid = min(kBlk, p.n_comp - t0);
-        const int wvalid = max(0, min(32, bvalid - 32 * warp));   // 0, 16 or 32 tokens of this warp (16 only when G == 16)
-        wait_bar(data_full + slot * 8, (i / p.stages) & 1, status, dead);
+    int slot = team, phase = 0;   // ring position of block i = team, team + 2, ...: slot i mod stages, parity of i / stages
+    if (slot >= p.stages) { slot -= p.stages; phase ^= 1; }
+    for (int i = team; i < nblk; i += 2) {
+      const unsigned char* st = stage + slot * sbytes;
+      const int t0 = (blk0 + i) * kBlk;
+      const int bvalid = min(kBlk, p.n_comp - t0);
+      const int wvalid = max(0, min(32, bvalid - 32 * tw));   // 0, 16 or 32 tokens of this warp (16 only when G == 16)
+      wait_bar(data_full + slot * 8, phase, status, dead);
 
-        float s[2][4];
+      // ---------------- scores of this warp's 32 tokens ----------------
+      float s[2][4];
+      float alpha[2];
+      {
+        const int warp_tok = tw;   // (kept as a name: the lambdas below index tokens by it)
         uint32_t xh[16], xl[K2 ? 16 : 1];
         float c0 = 0.f, c1 = 0.f;
         // ---- scaled query of a token group: x = q * k_scale as fp16 operand pairs (two-term: value + rounding
@@ -395,34 +477,38 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
         auto prep = [&](int gl) {
           const float* ks = reinterpret_cast<const float*>(st + off_ks) + gl * kD + tig * 8;   // rows in kmeta_pos order
           const float* kz = reinterpret_cast<const float*>(st + off_kz) + gl * kD + tig * 8;
-          float bias = 0.f;
+          float2 bacc[4];   // sum of (pre-scaled q) * k_zero per channel position pair (e, e + 1) of a run
+#pragma unroll
+          for (int j = 0; j < 4; ++j) bacc[j] = make_float2(0.f, 0.f);
 #pragma unroll
           for (int h2 = 0; h2 < 2; ++h2) {   // sixteen channels (two runs of eight) at a time
-            float pr[2][8];
+            float pr[2][8], qv[2][8], sv[2][8];
 #pragma unroll
             for (int u2 = 0; u2 < 2; ++u2) {
               const int u = h2 * 2 + u2;
-              const float4 s0 = *reinterpret_cast<const float4*>(ks + u * 32);
-              const float4 s1 = *reinterpret_cast<const float4*>(ks + u * 32 + 4);
-              const float4 z0 = *reinterpret_cast<const float4*>(kz + u * 32);
-              const float4 z1 = *reinterpret_cast<const float4*>(kz + u * 32 + 4);
-              const float4 q0 = *reinterpret_cast<const float4*>(qrow + u * 32);
-              const float4 q1 = *reinterpret_cast<const float4*>(qrow + u * 32 + 4);
-              const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-              const float zv[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
-              const float qv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                pr[u2][e] = qv[e] * sv[e];
-                bias = fmaf(qv[e], zv[e], bias);
+              for (int v4 = 0; v4 < 2; ++v4) {
+                const float4 s4 = *reinterpret_cast<const float4*>(ks + u * 32 + v4 * 4);
+                const float4 z4 = *reinterpret_cast<const float4*>(kz + u * 32 + v4 * 4);
+                const float4 q4 = *reinterpret_cast<const float4*>(qrow + u * 32 + v4 * 4);
+                const float2 p01 = mul2(make_float2(q4.x, q4.y), make_float2(s4.x, s4.y));
+                const float2 p23 = mul2(make_float2(q4.z, q4.w), make_float2(s4.z, s4.w));
+                bacc[v4 * 2] = fma2(make_float2(q4.x, q4.y), make_float2(z4.x, z4.y), bacc[v4 * 2]);
+                bacc[v4 * 2 + 1] = fma2(make_float2(q4.z, q4.w), make_float2(z4.z, z4.w), bacc[v4 * 2 + 1]);
+                pr[u2][v4 * 4] = p01.x; pr[u2][v4 * 4 + 1] = p01.y; pr[u2][v4 * 4 + 2] = p23.x; pr[u2][v4 * 4 + 3] = p23.y;
+                if constexpr (K2) {
+                  qv[u2][v4 * 4] = q4.x; qv[u2][v4 * 4 + 1] = q4.y; qv[u2][v4 * 4 + 2] = q4.z; qv[u2][v4 * 4 + 3] = q4.w;
+                  sv[u2][v4 * 4] = s4.x; sv[u2][v4 * 4 + 1] = s4.y; sv[u2][v4 * 4 + 2] = s4.z; sv[u2][v4 * 4 + 3] = s4.w;
+                }
               }
             }
-            auto put = [&](int idx, float a, float bb) {
-              const __half2 hv = __floats2half2_rn(a, bb);
+            // operand pair (channels ua:ea, ub:eb): the fp16 value and, as the second term, the exact residual of the product
+            auto put = [&](int idx, int ua, int ea, int ub, int eb) {
+              const __half2 hv = __floats2half2_rn(pr[ua][ea], pr[ub][eb]);
               xh[idx] = *reinterpret_cast<const uint32_t*>(&hv);
               if constexpr (K2) {
                 const float2 hf = __half22float2(hv);
-                const __half2 lv = __floats2half2_rn(a - hf.x, bb - hf.y);
+                const __half2 lv = __floats2half2_rn(fmaf(qv[ua][ea], sv[ua][ea], -hf.x), fmaf(qv[ub][eb], sv[ub][eb], -hf.y));
                 xl[idx] = *reinterpret_cast<const uint32_t*>(&lv);
               }
             };
@@ -430,16 +516,23 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
 #pragma unroll
               for (int u2 = 0; u2 < 2; ++u2)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) put((h2 * 2 + u2) * 4 + k, pr[u2][k], pr[u2][k + 4]);
+                for (int k = 0; k < 4; ++k) put((h2 * 2 + u2) * 4 + k, u2, k, u2, k + 4);
             } else {                      // a word is both runs: pairs (c_j, c_j+8)
 #pragma unroll
-              for (int j = 0; j < 8; ++j) put(h2 * 8 + j, pr[0][j], pr[1][j]);
+              for (int j = 0; j < 8; ++j) put(h2 * 8 + j, 0, j, 1, j);
             }
+          }
+          // undo the per-position pre-scaling of q in the constant term
+          float bias = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            bias = fmaf(bacc[j].x, 1.f / code_factor<BITS>(2 * j), bias);
+            bias = fmaf(bacc[j].y, 1.f / code_factor<BITS>(2 * j + 1), bias);
           }
           bias += __shfl_xor_sync(0xffffffffu, bias, 1);
           bias += __shfl_xor_sync(0xffffffffu, bias, 2);
-          c0 = __shfl_sync(0xffffffffu, bias, (tig * 2) * 4);
-          c1 = __shfl_sync(0xffffffffu, bias, (tig * 2 + 1) * 4);
+          c0 = __shfl_sync(0xffffffffu, bias, (tig * 2) * 4) * scale2;
+          c1 = __shfl_sync(0xffffffffu, bias, (tig * 2 + 1) * 4) * scale2;
         };
         // ---- scores of NT tiles of 16 tokens that share the operand: their MMA chains are independent and interleave ----
         auto run_tiles = [&](auto nt_tag, int tile0) {
@@ -447,7 +540,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
           uint32_t wa[NT][NW], wb[NT][NW];
 #pragma unroll
           for (int t = 0; t < NT; ++t) {
-            const unsigned char* krow = st + (32 * warp + 16 * (tile0 + t) + gid) * KROW + tig * LB;
+            const unsigned char* krow = st + (32 * warp_tok + 16 * (tile0 + t) + gid) * KROW + tig * LB;
             if constexpr (BITS == 4) {
               const uint4 wa4 = *reinterpret_cast<const uint4*>(krow);
               const uint4 wb4 = *reinterpret_cast<const uint4*>(krow + 8 * KROW);
@@ -470,8 +563,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
             uint32_t pa[NT][PW], pb[NT][PW];
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
-              unpack_exact<BITS, 0>(wa[t][w], pa[t]);
-              unpack_exact<BITS, 0>(wb[t][w], pb[t]);
+              unpack_sub<BITS>(wa[t][w], pa[t]);
+              unpack_sub<BITS>(wb[t][w], pb[t]);
             }
 #pragma unroll
             for (int q4 = 0; q4 < PW / 4; ++q4) {
@@ -492,63 +585,58 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
           }
 #pragma unroll
           for (int t = 0; t < NT; ++t) {
-            s[tile0 + t][0] = (d0[t][0] + d1[t][0] + c0) * scale2;   // token gid,     head 2 tig
-            s[tile0 + t][1] = (d0[t][1] + d1[t][1] + c1) * scale2;   // token gid,     head 2 tig + 1
-            s[tile0 + t][2] = (d0[t][2] + d1[t][2] + c0) * scale2;   // token gid + 8, head 2 tig
-            s[tile0 + t][3] = (d0[t][3] + d1[t][3] + c1) * scale2;   // token gid + 8, head 2 tig + 1
+            s[tile0 + t][0] = fmaf(d0[t][0] + d1[t][0], scale2o, c0);   // token gid,     head 2 tig
+            s[tile0 + t][1] = fmaf(d0[t][1] + d1[t][1], scale2o, c1);   // token gid,     head 2 tig + 1
+            s[tile0 + t][2] = fmaf(d0[t][2] + d1[t][2], scale2o, c0);   // token gid + 8, head 2 tig
+            s[tile0 + t][3] = fmaf(d0[t][3] + d1[t][3], scale2o, c1);   // token gid + 8, head 2 tig + 1
           }
         };
 #pragma unroll
         for (int t = 0; t < 2; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = kNegBig;
         if (G >= 32) {
           if (wvalid > 0) {   // both tiles lie in one token group
-            prep((32 * warp) / G);
+            prep((32 * warp_tok) >> lg);
             run_tiles(std::integral_constant<int, 2>{}, 0);
           }
         } else {
           for (int tile = 0; tile * 16 < wvalid; ++tile) {
-            prep((32 * warp + 16 * tile) / G);
+            prep((32 * warp_tok + 16 * tile) >> lg);
             if (tile == 0) run_tiles(std::integral_constant<int, 1>{}, 0);
             else run_tiles(std::integral_constant<int, 1>{}, 1);
           }
         }
-
-        // ---- block maximum per head: this warp's 32 tokens, then the four warps through shared memory ----
-        float mx0 = fmaxf(fmaxf(s[0][0], s[0][2]), fmaxf(s[1][0], s[1][2]));
-        float mx1 = fmaxf(fmaxf(s[0][1], s[0][3]), fmaxf(s[1][1], s[1][3]));
+      }
+      // ---- block maximum per head: this warp's 32 tokens, then the team's four warps through shared memory ----
+      float mx0 = fmaxf(fmaxf(s[0][0], s[0][2]), fmaxf(s[1][0], s[1][2]));
+      float mx1 = fmaxf(fmaxf(s[0][1], s[0][3]), fmaxf(s[1][1], s[1][3]));
 #pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
-          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
-        }
-        float* gm = gmax_s + ps * (kScoreWarps * kHeads);
-        if (gid == 0) *reinterpret_cast<float2*>(gm + warp * kHeads + 2 * tig) = make_float2(mx0, mx1);
-        named_sync(2, kScoreWarps * 32);
-        float alpha[2];
+      for (int o = 4; o < 32; o <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+      }
+      if (gid == 0) *reinterpret_cast<float2*>(gm + tw * kHeads + 2 * tig) = make_float2(mx0, mx1);
+      named_sync(team_bar, 128);   // the maxima are in; every warp of the team is done with the previous block's probabilities
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          float mb = kNegBig;
+      for (int e = 0; e < 2; ++e) {
+        float mb = kNegBig;
 #pragma unroll
-          for (int w = 0; w < kScoreWarps; ++w) mb = fmaxf(mb, gm[w * kHeads + 2 * tig + e]);
-          const float m_new = fmaxf(m_run[e], mb);
-          alpha[e] = exp2f(m_run[e] - m_new);
-          m_run[e] = m_new;
-          l_run[e] *= alpha[e];
+        for (int w = 0; w < 4; ++w) mb = fmaxf(mb, gm[w * kHeads + 2 * tig + e]);
+        const float m_new = fmaxf(m_run[e], mb);
+        alpha[e] = exp2f(m_run[e] - m_new);
+        m_run[e] = m_new;
+        l_run[e] *= alpha[e];
 #pragma unroll
-          for (int g = 0; g < VG; ++g) z_run[g][e] *= alpha[e];
-        }
-
-        // ---- probabilities times the value scale into the operand buffer of the value warps ----
-        wait_bar(p_empty + ps * 8, ((i >> 1) & 1) ^ 1, status, dead);
-        if (warp == 0 && gid == 0) *reinterpret_cast<float2*>(alpha_s + ps * kHeads + 2 * tig) = make_float2(alpha[0], alpha[1]);
-        unsigned char* pst = Pring + ps * p_stage_bytes(VG);
+        for (int g = 0; g < VG; ++g) z_run[g][e] *= alpha[e];
+      }
+      // ---------------- probabilities times the value scale into the team's operand buffer ----------------
+      {
         const float* vs = reinterpret_cast<const float*>(st + off_vs);
         const float* vz = reinterpret_cast<const float*>(st + off_vz);
 #pragma unroll
         for (int tile = 0; tile < 2; ++tile)
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
-            const int tl = 32 * warp + 16 * tile + gid + 8 * hf;
+            const int tl = 32 * tw + 16 * tile + gid + 8 * hf;
             const bool live = tl < bvalid;
             float pe[2];
 #pragma unroll
@@ -559,7 +647,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
 #pragma unroll
             for (int g = 0; g < VG; ++g) {
               const float sc = live ? vs[tl * VG + g] : 0.f;
-              const float zc = live ? fmaf((float)VCENTER, sc, vz[tl * VG + g]) : 0.f;   // the value codes are centred
+              const float zc = live ? fmaf((float)kVCentre<BITS>, sc, vz[tl * VG + g]) : 0.f;
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
                 const float pv = pe[e] * sc;
@@ -571,61 +659,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
               }
             }
           }
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(p_full + ps * 8);
-          mbar_arrive(data_empty + slot * 8);
-        }
       }
-
-      // ---- statistics of the split: sum and the constant term per head (and value group), over this warp's tokens ----
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float lsum = l_run[e];
-#pragma unroll
-        for (int o = 4; o < 32; o <<= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-        float cs[VG];
-#pragma unroll
-        for (int g = 0; g < VG; ++g) {
-          float c = z_run[g][e];
-#pragma unroll
-          for (int o = 4; o < 32; o <<= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-          cs[g] = c;
-        }
-        if (gid == 0) {
-          float* f = fin_s + (warp * kHeads + 2 * tig + e) * kFinStride;
-          f[0] = lsum;
-#pragma unroll
-          for (int g = 0; g < VG; ++g) f[1 + g] = cs[g];
-          if (warp == 0) st_m[2 * tig + e] = m_run[e] * kLn2;
-        }
-      }
-      named_sync(1, kComputeThreads);
-      if (warp == 0 && lane < kHeads) {
-        float l = 0.f;
-#pragma unroll
-        for (int w = 0; w < kScoreWarps; ++w) l += fin_s[(w * kHeads + lane) * kFinStride];
-        st_l[lane] = l;
-      }
-    } else {
-      // ================= value warps: channels [32 v, 32 v + 32), two MMA row tiles of 16 =================
-      const int v = warp - kScoreWarps;
-      float oacc[2][4];
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) oacc[mt][e] = 0.f;
-      const int pg = VG == 1 ? 0 : v;   // 32 channels = one value group
-      const int pchunk = ((tig ^ (gid >> 1)) & 3) * 16;
-
-      for (int i = 0; i < nblk; ++i) {
-        const int slot = i % p.stages, ps = i & 1;
-        const unsigned char* st = stage + slot * sbytes;
-        wait_bar(data_full + slot * 8, (i / p.stages) & 1, status, dead);
+      named_sync(team_bar, 128);   // the block's probabilities are complete
+      // ---------------- O = O * alpha + codes_v^T . P for this warp's 32 channels ----------------
+      {
         uint32_t wa[2][NW], wb[2][NW];
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) {
-          const unsigned char* vrow = st + off_vc + (32 * v + 16 * mt + gid) * VROW + tig * LB;
+          const unsigned char* vrow = st + off_vc + (32 * tw + 16 * mt + gid) * VROW + tig * LB;
           if constexpr (BITS == 4) {
             const uint4 va = *reinterpret_cast<const uint4*>(vrow);
             const uint4 vb = *reinterpret_cast<const uint4*>(vrow + 8 * VROW);
@@ -638,9 +679,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
             wb[mt][0] = vb.x; wb[mt][1] = vb.y;
           }
         }
-        wait_bar(p_full + ps * 8, (i >> 1) & 1, status, dead);
-        const float2 al = *reinterpret_cast<const float2*>(alpha_s + ps * kHeads + 2 * tig);
-        const unsigned char* ph = Pring + ps * p_stage_bytes(VG) + pg * (2 * kHeads * kPHead) + gid * kPHead + pchunk;
+        const unsigned char* ph = pst + pg * (2 * kHeads * kPHead) + gid * kPHead + pchunk;
         // independent accumulator chains: (row tile, pair half, term)
         float o0[2][4], o1[2][4], o0l[2][4], o1l[2][4];
 #pragma unroll
@@ -652,8 +691,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
           uint32_t pa[2][PW], pb[2][PW];
 #pragma unroll
           for (int mt = 0; mt < 2; ++mt) {
-            unpack_exact<BITS, VCENTER>(wa[mt][w], pa[mt]);
-            unpack_exact<BITS, VCENTER>(wb[mt][w], pb[mt]);
+            unpack_centred<BITS>(wa[mt][w], pa[mt]);
+            unpack_centred<BITS>(wb[mt][w], pb[mt]);
           }
 #pragma unroll
           for (int q4 = 0; q4 < PW / 4; ++q4) {
@@ -674,39 +713,95 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
         }
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(p_empty + ps * 8);
           mbar_arrive(data_empty + slot * 8);
-          if (v == kValueWarps - 1 && i + p.stages < nblk) {   // refill the slot once all eight warps have released it
-            wait_bar(data_empty + slot * 8, (i / p.stages) & 1, status, dead);
-            issue_block(i + p.stages);
+          if (tw == 3 && i + p.stages < nblk) {   // refill the slot once the team's four warps have released it
+            wait_bar(data_empty + slot * 8, phase, status, dead);
+            issue_block(i + p.stages, slot);
           }
         }
+        slot += 2;
+        if (slot >= p.stages) { slot -= p.stages; phase ^= 1; }
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) {
-          oacc[mt][0] = fmaf(oacc[mt][0], al.x, (o0[mt][0] + o1[mt][0]) + (o0l[mt][0] + o1l[mt][0]));
-          oacc[mt][1] = fmaf(oacc[mt][1], al.y, (o0[mt][1] + o1[mt][1]) + (o0l[mt][1] + o1l[mt][1]));
-          oacc[mt][2] = fmaf(oacc[mt][2], al.x, (o0[mt][2] + o1[mt][2]) + (o0l[mt][2] + o1l[mt][2]));
-          oacc[mt][3] = fmaf(oacc[mt][3], al.y, (o0[mt][3] + o1[mt][3]) + (o0l[mt][3] + o1l[mt][3]));
+          oacc[mt][0] = fmaf(oacc[mt][0], alpha[0], (o0[mt][0] + o1[mt][0]) + (o0l[mt][0] + o1l[mt][0]));
+          oacc[mt][1] = fmaf(oacc[mt][1], alpha[1], (o0[mt][1] + o1[mt][1]) + (o0l[mt][1] + o1l[mt][1]));
+          oacc[mt][2] = fmaf(oacc[mt][2], alpha[0], (o0[mt][2] + o1[mt][2]) + (o0l[mt][2] + o1l[mt][2]));
+          oacc[mt][3] = fmaf(oacc[mt][3], alpha[1], (o0[mt][3] + o1[mt][3]) + (o0l[mt][3] + o1l[mt][3]));
         }
       }
+    }
 
-      named_sync(1, kComputeThreads);   // the score warps' statistics are in shared memory
-      // partial O of the split: lane holds channels (row, row + 8) x heads (2 tig, 2 tig + 1) of each row tile
+    // ---------------- the two teams' results become the split's partial (max, sum, O) ----------------
+    float* tm_s = alpha_s;   // [2 teams][8]: running maximum (base-2 units)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float lsum = l_run[e];
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+      float cs[VG];
+#pragma unroll
+      for (int g = 0; g < VG; ++g) {
+        float c = z_run[g][e];
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+        cs[g] = c;
+      }
+      if (gid == 0) {
+        float* f = fin_s + (warp * kHeads + 2 * tig + e) * kFinStride;
+        f[0] = lsum;
+#pragma unroll
+        for (int g = 0; g < VG; ++g) f[1 + g] = cs[g];
+        if (tw == 0) tm_s[team * kHeads + 2 * tig + e] = m_run[e];
+      }
+    }
+    named_sync(1, kComputeThreads);
+    float wt[2], corr[2];   // this team's weight in the split, and its constant term, for heads 2 tig, 2 tig + 1
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int hh = 2 * tig + e;
+      const float M = fmaxf(tm_s[hh], tm_s[kHeads + hh]);
+      wt[e] = exp2f(tm_s[team * kHeads + hh] - M);
+      float c = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) c += fin_s[((team * 4 + w) * kHeads + hh) * kFinStride + 1 + pg];
+      corr[e] = c;
+    }
+    float* obuf = reinterpret_cast<float*>(Pring);   // [8 heads][128 channels] fp32: team 1 -> team 0 (the probability buffers are free)
+    if (team == 1) {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int hh = 2 * tig + e, c = 32 * tw + 16 * mt + gid;
+          obuf[hh * kD + c] = (oacc[mt][e] + corr[e]) * wt[e];
+          obuf[hh * kD + c + 8] = (oacc[mt][2 + e] + corr[e]) * wt[e];
+        }
+    }
+    named_sync(1, kComputeThreads);
+    if (team == 0) {
       float* po = p.part_o + (bh * p.n_split + split) * (size_t)(kHeads * kD);
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int hh = 2 * tig + e;
-        float corr = 0.f;
-#pragma unroll
-        for (int w = 0; w < kScoreWarps; ++w) corr += fin_s[(w * kHeads + hh) * kFinStride + 1 + pg];
         if (hh < p.rep) {
 #pragma unroll
           for (int mt = 0; mt < 2; ++mt) {
-            const int c = 32 * v + 16 * mt + gid;
-            __stcg(po + hh * kD + c, oacc[mt][e] + corr);
-            __stcg(po + hh * kD + c + 8, oacc[mt][2 + e] + corr);
+            const int c = 32 * tw + 16 * mt + gid;
+            __stcg(po + hh * kD + c, (oacc[mt][e] + corr[e]) * wt[e] + obuf[hh * kD + c]);
+            __stcg(po + hh * kD + c + 8, (oacc[mt][2 + e] + corr[e]) * wt[e] + obuf[hh * kD + c + 8]);
           }
         }
+      }
+      if (warp == 0 && lane < kHeads) {
+        const float mA = tm_s[lane], mB = tm_s[kHeads + lane], M = fmaxf(mA, mB);
+        float lA = 0.f, lB = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          lA += fin_s[(w * kHeads + lane) * kFinStride];
+          lB += fin_s[((4 + w) * kHeads + lane) * kFinStride];
+        }
+        st_m[lane] = M * kLn2;
+        st_l[lane] = lA * exp2f(mA - M) + lB * exp2f(mB - M);
       }
     }
     named_sync(1, kComputeThreads);   // st_m / st_l are complete
@@ -715,7 +810,6 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
     float* S = reinterpret_cast<float*>(Pring);                 // [8][s_stride] scores
     constexpr int s_stride = kResChunk + 4;
     float* red = reinterpret_cast<float*>(Pring + 4096);        // [8][128] fp32
-    wait_bar(res_bar, 0, status, dead);
     for (int tile = warp; tile * 16 < valid; tile += kAttnWarps) {
       const int tA = min(tile * 16 + gid, valid - 1), tB = min(tile * 16 + gid + 8, valid - 1);
       float d0[4] = {0.f, 0.f, 0.f, 0.f};
@@ -790,12 +884,16 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
   }
 
   // ================= merge of the splits by the last CTA of this (batch, head) =================
-  __threadfence();
+  // The partials of all threads are ordered before the counter by the barrier and thread 0's release; the last
+  // arriver's acquire, followed by the second barrier, orders every other split's partials before the reads below.
   named_sync(1, kComputeThreads);
-  if (threadIdx.x == 0) *s_last = (atomicAdd(p.counters + bh, 1) == p.n_split - 1);
+  if (threadIdx.x == 0) {
+    int old;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + bh) : "memory");
+    *s_last = (old == p.n_split - 1);
+  }
   named_sync(1, kComputeThreads);
   if (!*s_last) return;
-  __threadfence();
   const float* pm = p.part_ml + bh * p.n_split * (size_t)(kHeads * 2);
   const float* po = p.part_o + bh * p.n_split * (size_t)(kHeads * kD);
   // Everything the merge needs from global memory is requested before anything waits: first the partial outputs
@@ -922,13 +1020,27 @@ AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group, int bits
   if (nb_min < 1) nb_min = 1;
   int nb_max = nblk < kMaxNb ? nblk : kMaxNb;
   if (nb_max < nb_min) nb_max = nb_min;
+  // Makespan model in microseconds.  A compressed split runs its blocks on two teams side by side, so it takes
+  // ceil(nb / 2) block times plus a fixed part (first data, the teams' merge, the partial's store and the counter);
+  // block and fixed times are longer when every SM holds two CTAs.  Residual splits are short and fill the gaps of
+  // the last wave; the merge by the last arriver grows with the number of splits.
   int best = nb_min;
   double best_cost = 1e30;
-  for (int nb = nb_min; nb <= nb_max; ++nb) {
+  const double pairs = (double)B * H;
+  for (int nb = nb_min; nb <= nb_max && nblk > 0; ++nb) {
     const long long cs = (nblk + nb - 1) / nb;
-    const double ctas = (double)B * H * (cs + a.n_rsplit * 2.0 / (nb + 2.0));
-    const double waves = ctas <= (double)slots ? 1.0 : (double)((long long)((ctas + slots - 1) / slots));
-    const double cost = waves * (nb + 2.0) + 0.02 * cs;   // a slight preference for fewer splits to merge
+    const int nb_even = (int)((nblk + cs - 1) / cs);   // blocks of the largest split when the blocks are spread evenly
+    if (nb_even != nb) continue;                        // the same split count with fewer blocks per split comes later
+    const double c_ctas = pairs * cs, r_ctas = pairs * a.n_rsplit;
+    const bool light = c_ctas + r_ctas <= 0.6 * (double)slots;
+    const double t_blk = light ? 2.0 : 3.1, t_fix = light ? 3.0 : 4.5, t_res = light ? 3.0 : 4.0;
+    const double t_cta = t_fix + ((nb + 1) / 2) * t_blk;
+    const double waves = (double)((long long)((c_ctas + slots - 1) / slots));
+    double span = waves * t_cta;
+    const double area = (c_ctas * t_cta + r_ctas * t_res) / (double)slots;
+    if (area > span) span = area;
+    if (span < t_res) span = t_res;
+    const double cost = span + 2.5 + 0.035 * (double)(cs + a.n_rsplit);
     if (cost < best_cost - 1e-9) {
       best_cost = cost;
       best = nb;

@@ -320,6 +320,10 @@ def test_decode_stack_step_against_restatement(m, dtype, cuda_lib):
     want = r(h + delta)
     mx, mean = ow.rel_err(y, want)
     print("stack vs restatement", dtype, m, mx, mean)
-    bars = (3e-2, 2e-3) if dtype == torch.float16 else (1.5e-1, 1e-2)
+    # The error is measured relative to max(|want|, 1e-2 max|want|).  Every hand-over rounds to the dtype, so one
+    # element that lands on the other side of a rounding boundary differs by one unit in the last place: 2^-11 of
+    # its own size in fp16, 2^-8 in bf16, i.e. up to 2^-8 / 1e-2 = 0.39 in this measure for a bf16 element of the
+    # largest size.  The maximum bar allows exactly that single flip; the mean bar is what holds the kernels.
+    bars = (3e-2, 2e-3) if dtype == torch.float16 else (0.4, 1e-2)
     assert mx <= bars[0] and mean <= bars[1], (mx, mean)
     assert stack.cache.seq_len(0) == stack.cache.seq_len(1) == ctx + 1
