@@ -274,9 +274,15 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
   constexpr int VROW = kBlk * BITS / 8;          // bytes of a channel's value codes in a 128-token block
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
-  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const size_t bh = (size_t)b * p.H + h;
-  const bool is_res = (split >= p.n_csplit);
+  // Launch order = block index: the long compressed splits of every (batch, head) come first, the short residual
+  // splits last, where they fill the gaps of the final wave instead of delaying a compressed split by a wave.
+  const int n_rsplit = p.n_split - p.n_csplit;
+  const int total_c = p.B * p.H * p.n_csplit;
+  const bool is_res = (int)blockIdx.x >= total_c;
+  const int pair_idx = is_res ? ((int)blockIdx.x - total_c) / n_rsplit : (int)blockIdx.x / p.n_csplit;
+  const int split = is_res ? p.n_csplit + ((int)blockIdx.x - total_c) % n_rsplit : (int)blockIdx.x % p.n_csplit;
+  const int b = pair_idx / p.H, h = pair_idx % p.H;
+  const size_t bh = (size_t)pair_idx;
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
   const uint32_t data_full = smem_u32(bars), data_empty = smem_u32(bars + 4);
@@ -809,7 +815,6 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
     // ================= residual window: dense fp16/bf16 tokens from the stage =================
     float* S = reinterpret_cast<float*>(Pring);                 // [8][s_stride] scores
     constexpr int s_stride = kResChunk + 4;
-    float* red = reinterpret_cast<float*>(Pring + 4096);        // [8][128] fp32
     for (int tile = warp; tile * 16 < valid; tile += kAttnWarps) {
       const int tA = min(tile * 16 + gid, valid - 1), tB = min(tile * 16 + gid + 8, valid - 1);
       float d0[4] = {0.f, 0.f, 0.f, 0.f};
@@ -840,8 +845,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
       for (int t = lane; t < valid; t += 32) m = fmaxf(m, srow[t]);
       m = warp_max(m);
       float l = 0.f;
-      for (int t = lane; t < valid; t += 32) {
-        const float e = __expf(srow[t] - m);
+      for (int t = lane; t < ((valid + 15) & ~15); t += 32) {   // the padding of the last 16-token step reads as zero
+        const float e = t < valid ? __expf(srow[t] - m) : 0.f;
         srow[t] = e;
         l += e;
       }
@@ -852,27 +857,39 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
       }
     }
     named_sync(1, kComputeThreads);
-    // P.V on the CUDA cores: thread = (channel, token half); 8 heads per thread
+    // P.V on the tensor cores: O^T[channel][head] = V^T[channel][token] . P[token][head], a warp per 16 channels.
+    // The transposing matrix load turns the staged rows (token-major) into the row operand; the probabilities go
+    // in as value + rounding residual in the window's own 16-bit type.
     {
-      const int c = threadIdx.x & 127, half = threadIdx.x >> 7;
-      const int t_mid = (valid + 1) >> 1;
-      const int tb = half ? t_mid : 0, te = half ? valid : t_mid;
-      float acc[kHeads];
-#pragma unroll
-      for (int hh = 0; hh < kHeads; ++hh) acc[hh] = 0.f;
-      for (int t = tb; t < te; ++t) {
-        const float vv = to_float<T>(*reinterpret_cast<const T*>(rv_s + t * kResPitch + c * 2));
-#pragma unroll
-        for (int hh = 0; hh < kHeads; ++hh) acc[hh] = fmaf(S[hh * s_stride + t], vv, acc[hh]);
+      const int c0 = warp * 16;
+      float dh[4] = {0.f, 0.f, 0.f, 0.f}, dl[4] = {0.f, 0.f, 0.f, 0.f};
+      const int ksteps = (valid + 15) >> 4;
+      for (int ks = 0; ks < ksteps; ++ks) {
+        // lane -> row of matrix (lane >> 3): tokens 0-7 | 0-7 | 8-15 | 8-15 of the step, channels 0-7 | 8-15 | 0-7 | 8-15;
+        // rows past the window repeat its last token (their probabilities are zero)
+        const int trow = min(ks * 16 + (lane >> 4) * 8 + (lane & 7), valid - 1);
+        const uint32_t addr = smem_u32(rv_s + trow * kResPitch + (c0 + ((lane >> 3) & 1) * 8) * 2);
+        uint32_t a0, a1, a2, a3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(addr));
+        const float* sp = S + gid * s_stride + ks * 16 + 2 * tig;
+        const float2 p0 = *reinterpret_cast<const float2*>(sp), p1 = *reinterpret_cast<const float2*>(sp + 8);
+        T hi[4] = {from_float<T>(p0.x), from_float<T>(p0.y), from_float<T>(p1.x), from_float<T>(p1.y)};
+        T lo[4] = {from_float<T>(p0.x - to_float<T>(hi[0])), from_float<T>(p0.y - to_float<T>(hi[1])),
+                   from_float<T>(p1.x - to_float<T>(hi[2])), from_float<T>(p1.y - to_float<T>(hi[3]))};
+        const uint32_t* hb = reinterpret_cast<const uint32_t*>(hi);
+        const uint32_t* lb = reinterpret_cast<const uint32_t*>(lo);
+        mma16816<T>(dh, a0, a1, a2, a3, hb[0], hb[1]);
+        mma16816<T>(dl, a0, a1, a2, a3, lb[0], lb[1]);
       }
-      if (half) {
+      float* po = p.part_o + (bh * p.n_split + split) * (size_t)(kHeads * kD);
 #pragma unroll
-        for (int hh = 0; hh < kHeads; ++hh) red[hh * kD + c] = acc[hh];
-      }
-      named_sync(1, kComputeThreads);
-      if (!half) {
-        float* po = p.part_o + (bh * p.n_split + split) * (size_t)(kHeads * kD);
-        for (int hh = 0; hh < p.rep; ++hh) __stcg(po + hh * kD + c, acc[hh] + red[hh * kD + c]);
+      for (int e = 0; e < 2; ++e) {
+        const int hh = 2 * tig + e;
+        if (hh < p.rep) {
+          __stcg(po + hh * kD + c0 + gid, dh[e] + dl[e]);
+          __stcg(po + hh * kD + c0 + gid + 8, dh[2 + e] + dl[2 + e]);
+        }
       }
     }
   }
@@ -1033,7 +1050,7 @@ AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group, int bits
     if (nb_even != nb) continue;                        // the same split count with fewer blocks per split comes later
     const double c_ctas = pairs * cs, r_ctas = pairs * a.n_rsplit;
     const bool light = c_ctas + r_ctas <= 0.6 * (double)slots;
-    const double t_blk = light ? 2.0 : 3.1, t_fix = light ? 3.0 : 4.5, t_res = light ? 3.0 : 4.0;
+    const double t_blk = light ? 2.0 : 3.1, t_fix = light ? 3.0 : 4.5, t_res = light ? 2.5 : 3.5;
     const double t_cta = t_fix + ((nb + 1) / 2) * t_blk;
     const double waves = (double)((long long)((c_ctas + slots - 1) / slots));
     double span = waves * t_cta;
@@ -1153,7 +1170,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
   auto launch = [&](auto kern) -> int {
     if (!ensure_smem_attr(reinterpret_cast<const void*>(kern), (int)kAttnSmemBudget)) return PARE_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.n_split, H, B);
+    cfg.gridDim = dim3((unsigned)(p.n_split * H * B), 1, 1);
     cfg.blockDim = dim3(kAttnThreads, 1, 1);
     cfg.dynamicSmemBytes = plan.smem;
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
