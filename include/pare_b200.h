@@ -75,6 +75,17 @@ const char* pare_status_string(int status);
  */
 size_t pare_w4a16_workspace_bytes(int M, int N, int K, int group_size);
 
+/* Status word of a workspace.  Every wait inside the kernels (on a bulk copy, on another warp, on the CTAs of a
+ * split) is bounded; one that runs out stores PARE_ERR_TIMEOUT in the workspace's status word, the kernel finishes
+ * with whatever it has, and the call's result is then undefined.  pare_workspace_status synchronises `stream`,
+ * returns the word (PARE_OK or PARE_ERR_TIMEOUT) and clears it; the word is sticky until read.  The same word
+ * serves every entry point that takes this workspace (linear layers and decode attention).
+ * pare_selftest_bounded_wait launches one thread that waits, through the kernels' own wait routine, at most
+ * `polls` (<= 4096) polls on a shared-memory barrier that nothing arrives at, so the time-out path and this
+ * accessor can be checked without a stuck kernel. */
+int pare_workspace_status(void* workspace, void* stream);
+int pare_selftest_bounded_wait(void* workspace, unsigned int polls, void* stream);
+
 int pare_w4a16_forward(const void* x, int x_dtype, int64_t ldx,
                        const uint8_t* packed,
                        const float* scale, const float* zero, const void* meta_h2,
@@ -247,6 +258,8 @@ int pare_silu_mul(const void* gate_up, void* out, void* prepared_out, int rows, 
  *   - All calls on a device share the one array: calls that may overlap on the GPU (different
  *     streams) race; order them on one stream. */
 size_t pare_w4a16_static_scratch_bytes(void);
+/* status word of the array (see pare_workspace_status): synchronises `stream`, returns and clears it */
+int pare_w4a16_static_status(void* stream);
 
 int pare_w4a16_forward_static(const void* x, int x_dtype, int64_t ldx,
                               const uint8_t* packed,

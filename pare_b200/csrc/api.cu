@@ -28,6 +28,29 @@ int gemm_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
                  int K, int G, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 }  // namespace pare
 
+namespace pare {
+namespace {
+// A wait that nothing ends: one thread waits on a shared-memory barrier nobody arrives at, through the same bounded
+// wait the kernels use, with a caller-chosen (small) limit.  It returns after `limit` polls with the time-out recorded.
+__global__ void bounded_wait_selftest_kernel(int* status, uint32_t limit) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    gemv::mbar_init(gemv::smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    gemv::mbar_wait_limit(gemv::smem_u32(&bar), 0, status, limit);
+  }
+}
+
+int read_and_clear_status(int* word, cudaStream_t s) {
+  int v = 0;
+  if (cudaMemcpyAsync(&v, word, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return PARE_ERR_CUDA;
+  if (cudaMemsetAsync(word, 0, sizeof(int), s) != cudaSuccess) return PARE_ERR_CUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return PARE_ERR_CUDA;
+  return v;
+}
+}  // namespace
+}  // namespace pare
+
 extern "C" {
 
 int pare_version(void) { return 100; }
@@ -219,5 +242,20 @@ int pare_w4a16_forward_produced_allreduce(int producer, const void* a, const voi
   return pare::gemv_forward(nullptr, x_dtype, K, packed, scale, zero, meta_h2, nullptr, nullptr, bias, y, ldy, M, N, K,
                             group_size, workspace, workspace_bytes, s, prepared, nullptr, &pc);
 }
+
+int pare_workspace_status(void* workspace, void* stream) {
+  PARE_REQUIRE(workspace, PARE_ERR_WORKSPACE);
+  return pare::read_and_clear_status(reinterpret_cast<int*>(workspace) + pare::gemv::kStatusIndex,
+                                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+int pare_selftest_bounded_wait(void* workspace, unsigned int polls, void* stream) {
+  PARE_REQUIRE(workspace, PARE_ERR_WORKSPACE);
+  PARE_REQUIRE(polls > 0 && polls <= 4096, PARE_ERR_SHAPE);   // a short wait by construction
+  pare::bounded_wait_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<int*>(workspace) + pare::gemv::kStatusIndex, polls);
+  return cudaGetLastError() == cudaSuccess ? PARE_OK : PARE_ERR_CUDA;
+}
+
 
 }  // extern "C"

@@ -74,13 +74,16 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: returns false (and records the failure) instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+// Bounded wait: returns false (and records the failure in the status word) instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, int* status, uint32_t limit) {
 #pragma unroll 1
-  for (uint32_t i = 0; i < kSpinLimit; ++i)
+  for (uint32_t i = 0; i < limit; ++i)
     if (mbar_test(bar, parity)) return true;
   if (status) atomicExch(status, PARE_ERR_TIMEOUT);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status) {
+  return mbar_wait_limit(bar, parity, status, kSpinLimit);
 }
 // contiguous global -> shared copy of `bytes` (multiple of 16, both addresses 16-byte aligned)
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {

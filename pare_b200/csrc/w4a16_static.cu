@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "gemv_common.cuh"
 #include "peer.cuh"
 
 namespace pare {
@@ -32,7 +33,7 @@ int gemv_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
 namespace {
 
 constexpr size_t kStaticScratchBytes = 16u << 20;   // 16 MiB per GPU that loads the library, held until exit
-constexpr size_t kZeroedPrefixBytes = 16384 * sizeof(int);  // the arrival counters of the split-K reduction
+constexpr size_t kZeroedPrefixBytes = pare::gemv::kStatusIndex * sizeof(int);  // the arrival counters of the split-K reduction (the status word after them is kept)
 
 // Device storage.  In host code this name is only a handle for the runtime, never an address a
 // kernel could use: the device address is looked up once per device with cudaGetSymbolAddress.
@@ -79,6 +80,13 @@ int pare_w4a16_forward_static(const void* x, int x_dtype, int64_t ldx, const uin
   if (cudaMemsetAsync(scratch, 0, kZeroedPrefixBytes, s) != cudaSuccess) return PARE_ERR_CUDA;
   return pare::gemv_forward(x, x_dtype, ldx, packed, scale, zero, meta_h2, col_perm, input_scale, bias, y, ldy, M, N, K,
                             group_size, scratch, kStaticScratchBytes, s, nullptr, nullptr);
+}
+
+int pare_w4a16_static_status(void* stream) {
+  void* scratch = nullptr;
+  const int rc = static_scratch(&scratch);
+  if (rc != PARE_OK) return rc;
+  return pare_workspace_status(scratch, stream);
 }
 
 }  // extern "C"

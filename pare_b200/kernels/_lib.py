@@ -63,6 +63,9 @@ SIGNATURES: dict[str, tuple] = {
     "pare_w4a16_forward_produced_allreduce": (_i, [_i, _vp, _vp, _vp, _vp, _i64, C.c_float, _i,
                                                    _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                                    _i, _i, _i, _i, _vp, _sz, _i, _i, C.POINTER(C.c_void_p), _sz, _vp]),
+    "pare_workspace_status": (_i, [_vp, _vp]),
+    "pare_selftest_bounded_wait": (_i, [_vp, C.c_uint, _vp]),
+    "pare_w4a16_static_status": (_i, [_vp]),
     "pare_w4a16_static_scratch_bytes": (_sz, []),
     "pare_w4a16_forward_static": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                        _i, _i, _i, _i, _vp]),
@@ -122,6 +125,17 @@ def current_stream(device: torch.device) -> int:
 
 # One zero-initialised workspace per device and stream; the kernels leave it zero-consistent.
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def workspace_status(device: torch.device) -> int:
+    """Status word of the current stream's workspace on ``device``: 0, or the time-out code if a bounded wait inside a
+    kernel gave up since the last read.  Synchronises the stream and clears the word; 0 if no workspace exists yet."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None:
+        return 0
+    return lib().pare_workspace_status(buf.data_ptr(), current_stream(device))
 
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
