@@ -6,51 +6,45 @@
 // materialises K or V.  Dequantization is folded into the operands that are small:
 //     S[h][t] = sum_c (q[h][c] * ks[g][c]) * code_k[t][c]  +  sum_c q[h][c] * kz[g][c]
 //     O[h][c] = sum_t (p[h][t] * vs[t]) * code_v[t][c]     +  sum_t p[h][t] * vz[t]
-// so the codes go to the warp-level MMA unit as integer-valued fp16 (OR-ed into the mantissa of
-// 1024.0, see common.cuh) and the per-channel / per-token scales multiply the query row (once per
-// token group) and the probabilities instead of every cache element.  The up to 8 query heads that
-// share a KV head sit in the 8 MMA columns, so the cache is read once for all of them.
+// so the codes go to the warp-level MMA unit as exact small integers and the per-channel / per-token scales
+// multiply the query row (once per token group) and the probabilities instead of every cache element.  The up
+// to 8 query heads that share a KV head sit in the 8 MMA columns, so the cache is read once for all of them.
 //
-// Grid: (splits, kv heads, batch).  A split is either a run of up to `nb` blocks of 128 compressed
+// Grid: one CTA per split, compressed splits of all (batch, KV head) pairs first, then the residual splits (they
+// are short and fill the gaps of the last wave).  A split is either a run of up to `nb` blocks of 128 compressed
 // tokens or up to 64 tokens of the full-precision residual window.
 //
 // A compressed split is a software pipeline over its blocks, with no CTA-wide barrier inside:
-//   * a ring of stages is kept full by one lane of the last value warp: the six pieces of a block (key
-//     codes, key scales, key zeros, value codes, value scales, value zeros) are contiguous in the cache
-//     layout and arrive by six bulk async copies on one mbarrier; a slot is refilled as soon as all eight
-//     warps have released it.  The compressed cache is immutable during a decode step, so the first
-//     copies start before griddepcontrol.wait and overlap the kernel that produces q.
-//   * four score warps, one per 32 tokens of the block: scaled-query operand for the token group
-//     (registers), scores by MMA, block maximum (one named barrier among the four warps), running
-//     maximum / sum, and the probabilities times the value scale written to a two-stage shared
-//     buffer in the operand order of the next MMA (online softmax: the rescale factor of the block
-//     goes with it);
-//   * four value warps, 32 channels each: O = O * alpha + codes_v^T . P per block, accumulators in
-//     registers for the whole split.
-// Codes enter the MMA as exact small integers (the mantissa offset is removed per element: attention outputs
-// and logits are small differences of large sums, so an offset left in the accumulator costs the digits
-// that matter); value codes are centred (c - 8) so that the products are half as large.
-// Partial (max, sum, O) of a split go to a workspace; the CTA that arrives last at the per-(batch,
-// head) counter merges them in split order and resets the counter.
+//   * a ring of stages: the six pieces of a block (key codes, key scales, key zeros, value codes, value scales,
+//     value zeros) are contiguous in the cache layout and arrive by six bulk async copies on one mbarrier.  The
+//     compressed cache is immutable during a decode step, so the first copies start before griddepcontrol.wait
+//     and overlap the kernel that produces q.
+//   * two teams of four warps; team t takes blocks t, t + 2, ...  Inside a team every warp does both halves of
+//     the work on the team's block: scaled-query operand of its token group, scores of its 32 tokens by MMA,
+//     block maximum (named barrier of the team), online-softmax rescale, probabilities times the value scale
+//     into the team's operand buffer (second named barrier), then O = O * alpha + codes_v^T . P for its 32
+//     channels.  The teams never wait for each other, so one team's barrier or dependency stalls are the other
+//     one's issue slots.  One lane of the team refills the slot once its four warps have released it.
+//   * the two teams' (max, sum, O) are combined in shared memory into the split's partial.
+// Key codes enter the MMA as fp16 subnormals (a mask per pair, no offset to remove; the query is pre-multiplied
+// by the position factor); value codes as exact centred integers (c - 8 or c - 2), see below why.
+// Partial (max, sum, O) of a split go to a workspace; the CTA that arrives last at the per-(batch, head)
+// counter (one release/acquire atomic) merges them in split order and resets the counter.
 //
-// The residual window, q and the newest token are read after the dependency wait.  The newest token
-// can be handed in separately (new_k / new_v, e.g. straight out of the q|k|v projection): the CTA
-// that owns the last window position attends to it and stores it into the window.  The merged
-// output can also be written as prepared activations of the next W4A16 linear (operand order +
-// per-step sums, see prep.cuh): head h is exactly one 128-column step.
+// The residual window, q and the newest token are read after the dependency wait: the window rows by plain
+// 16-byte loads of all threads, scores and P.V by MMA (transposing matrix loads for V).  The newest token can be
+// handed in separately (new_k / new_v, e.g. straight out of the q|k|v projection): the CTA that owns the last
+// window position attends to it and stores it into the window.  The merged output can also be written as
+// prepared activations of the next W4A16 linear (operand order + per-step sums, see prep.cuh): head h is exactly
+// one 128-column step.
 //
 // Every mbarrier wait is bounded: on expiry the thread records PARE_ERR_TIMEOUT in the workspace
 // status word and never waits again; the CTA still reaches every named barrier and returns.
 
-#include <cstdlib>
 #include <type_traits>
 
 #include "gemv_common.cuh"
 #include "prep.cuh"
-
-#ifndef PARE_ATTN_MODE
-#define PARE_ATTN_MODE 3   // bit 0: two-term scaled query, bit 1: two-term probabilities (see the kernel template)
-#endif
 
 namespace pare {
 namespace {
@@ -1063,12 +1057,6 @@ AttnPlan make_attn_plan(int B, int H, int n_comp, int n_res, int group, int bits
       best = nb;
     }
   }
-#ifdef PARE_EXPERIMENT
-  if (const char* env = getenv("PARE_ATTN_NB")) {
-    const int v = atoi(env);
-    if (v >= nb_min) best = v;
-  }
-#endif
   a.nb = best;
   a.n_csplit = nblk ? (nblk + a.nb - 1) / a.nb : 0;
   a.n_split = a.n_csplit + a.n_rsplit;
@@ -1181,7 +1169,7 @@ int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t 
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess ? PARE_OK : PARE_ERR_CUDA;
   };
-  constexpr int kMode = PARE_ATTN_MODE;
+  constexpr int kMode = 3;   // two-term scaled query and two-term probabilities: what the parity bars need
   if (vg == 1) {
     if (bits == 4) return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 4, 1, kMode>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 4, 1, kMode>);
     return dtype == PARE_F16 ? launch(kivi_decode_attn_kernel<__half, 2, 1, kMode>) : launch(kivi_decode_attn_kernel<__nv_bfloat16, 2, 1, kMode>);

@@ -87,3 +87,39 @@ def test_value_channel_groups_restatement():
             assert np.array_equal(a, b)
         rec = ok.dequantize_values(q, s, z)
         assert np.abs(rec - v).max() <= np.abs(ok.dequantize_values(*whole) - v).max() + 1e-6
+
+
+def test_timed_cpu_path_agrees_with_the_pinned_oracle():
+    """``oracle/cpu_path.py`` (the torch op sequence the benchmark TIMES on the host) computes what the pinned numpy
+    oracle computes: the linear within fp32 summation order (1e-5 relative), the cache bit for bit over a sequence of
+    updates that crosses the residual boundary several times (codes are integers, the reconstruction is one fused
+    multiply-add per element in both), attention within 1e-4."""
+    import torch
+
+    from oracle import cpu_path
+
+    rng = np.random.default_rng(3)
+    n, k, g = 96, 256, 128
+    packed = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    scale = (0.01 + rng.random((n, k // g, 1))).astype(np.float32)
+    zero = rng.integers(0, 16, size=(n, k // g, 1)).astype(np.float32)
+    x = rng.standard_normal((5, k)).astype(np.float32)
+    want = w4a16.linear(x, packed, scale[..., 0], zero[..., 0])
+    got = cpu_path.linear_forward(torch.from_numpy(x), torch.from_numpy(packed), torch.from_numpy(scale), torch.from_numpy(zero)).numpy()
+    mx, _ = w4a16.rel_err(got, want)
+    assert mx <= 1e-5, mx
+
+    ref, tim = kivi.Cache(4, 32, 128), cpu_path.TorchCache(4, 32, 128)
+    for t in (100, 60, 1, 1, 97, 1):
+        kk = rng.standard_normal((2, 2, t, 128)).astype(np.float32)
+        vv = rng.standard_normal((2, 2, t, 128)).astype(np.float32)
+        rk, rv = ref.update(kk, vv)
+        tk, tv = tim.update(torch.from_numpy(kk), torch.from_numpy(vv))
+        assert tk.shape == rk.shape and tv.shape == rv.shape
+        np.testing.assert_allclose(tk.numpy(), rk, rtol=0, atol=1e-6)   # same codes; q * scale + zero within an ulp
+        np.testing.assert_allclose(tv.numpy(), rv, rtol=0, atol=1e-6)
+    q = rng.standard_normal((2, 4, 1, 128)).astype(np.float32)
+    a_ref = kivi.decode_attention(q, rk, rv)
+    a_tim = cpu_path.attention(torch.from_numpy(q), tk, tv).numpy()
+    mx, _ = w4a16.rel_err(a_tim, a_ref)
+    assert mx <= 1e-4, mx   # fp32 softmax and sums in another order (measured 3e-5)
