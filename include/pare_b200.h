@@ -62,7 +62,11 @@ const char* pare_status_string(int status);
  *                (columns sorted by GPTQ act-order group; NULL = identity)
  *   input_scale  optional [K] float32: x[:, k] is divided by input_scale[k]
  *                (AWQ per-input-channel scale applied at run time; NULL = none);
- *                indexed by the ORIGINAL column, before col_perm
+ *                indexed by the ORIGINAL column, before col_perm.  The division is done
+ *                in fp32 and every kernel rounds the quotient to x_dtype before the
+ *                product (what a caller gets who divides the activations himself).  The
+ *                reference folds these scales into the weights offline
+ *                (pare/schemes/awq.py:388-424) and has no run-time counterpart
  *   bias         optional [N] x_dtype
  *   y            [M, ldy]  x_dtype
  *   workspace    pare_w4a16_workspace_bytes() bytes, zero-filled ONCE by the caller
@@ -201,8 +205,19 @@ int pare_kivi_dequant(const uint8_t* k_codes, const float* k_scale, const float*
  *   out           may be NULL when prepared_out is given
  *   prepared_out  NULL, or a pare_w4a16_prepared_bytes(B, Hq*D) buffer that receives the result as
  *                 prepared activations of the next W4A16 linear (B <= 16)
- * D == 128, bits == 4 or 2.  workspace: pare_kivi_attn_workspace_bytes(), zero-filled once
- * (same contract as the W4A16 workspace; one buffer may serve both). */
+ * D == 128, bits == 4 or 2, group in {16, 32, 64, 128}, n_res <= 512, B * H < 16383.
+ * Context length: the compressed tokens are cut into at most 250 splits per (batch, KV head), each
+ * a run of blocks of 128 tokens; a split takes as many blocks as that bound needs, so n_comp is
+ * limited only by `cap` and the workspace (beyond 64 blocks per split the planner merely stops
+ * balancing waves).
+ * Number range: BF16 keys and values of the residual window go to the tensor cores in their own
+ * type; the probabilities are split into value + rounding residual in the window's type.  The
+ * compressed path multiplies q by the key scale in fp32 and rounds the product (and the
+ * probabilities times the value scale) to fp16 pairs, so |q * k_scale| and p * v_scale must stay
+ * below 65504: value ranges (max - min per token) below 15 * 65504 (4-bit) -- any activations a
+ * 16-bit model produces.
+ * workspace: pare_kivi_attn_workspace_bytes(), zero-filled once (same contract and status word as
+ * the W4A16 workspace; one buffer may serve both). */
 size_t pare_kivi_attn_workspace_bytes(int B, int H, int n_comp, int n_res);
 
 int pare_kivi_decode_attn(const void* q, int dtype, int64_t q_stride_b, int64_t q_stride_h,

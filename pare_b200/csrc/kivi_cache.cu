@@ -44,6 +44,20 @@ __device__ __forceinline__ uint8_t affine_code(float x, float lo, float scale, f
   return (uint8_t)rintf(q);
 }
 
+// The same code without a division per element.  The quotient is approximated by a product with the correctly
+// rounded reciprocal (error below 2 units in the last place of a number below 16, i.e. < 4e-6) and rounded to the
+// nearest integer by adding 1.5 * 2^23 (round-to-nearest-even, like rintf; the integer then sits in the low mantissa
+// bits).  Only an approximation within 1e-4 of a rounding boundary could round differently from the exact quotient:
+// those elements (about one in ten thousand) take the division.  x >= lo by construction, so only the upper clamp is
+// needed.  Bit-identical to affine_code.
+__device__ __forceinline__ uint32_t affine_code_fast(float x, float lo, float inv, const float* scale_ptr, float qmax) {
+  const float q = fminf(__fmul_rn(__fsub_rn(x, lo), inv), qmax);
+  const float r = __fadd_rn(q, 12582912.f);
+  const float frac = __fsub_rn(__fsub_rn(r, 12582912.f), q);
+  if (fabsf(frac) > 0.4999f) return affine_code(x, lo, *scale_ptr, qmax);
+  return __float_as_uint(r) & 0xffu;
+}
+
 // One CTA per (token group, head, batch); blockDim.x == D.
 template <typename T>
 __global__ void kivi_append_kernel(const void* k_src, const void* v_src, int64_t sb, int64_t sh, int64_t st, int t0,
@@ -146,8 +160,10 @@ __global__ void __launch_bounds__(128) kivi_append128_kernel(const void* k_src, 
   T* vt = kt + G * D;                                       // [G][D]
   float* ks_s = reinterpret_cast<float*>(vt + G * D);       // [D] scale, channel order
   float* kl_s = ks_s + D;                                   // [D] group minimum
-  float* vs_s = kl_s + D;                                   // [G][VG]
+  float* ki_s = kl_s + D;                                   // [D] 1 / scale
+  float* vs_s = ki_s + D;                                   // [G][VG]
   float* vl_s = vs_s + G * VG;                              // [G][VG]
+  float* vi_s = vl_s + G * VG;                              // [G][VG] 1 / scale
   const int g = blockIdx.x, h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const float qmax = (float)((1 << BITS) - 1);
   const int tok0 = t0 + g * G;
@@ -175,6 +191,7 @@ __global__ void __launch_bounds__(128) kivi_append128_kernel(const void* k_src, 
     c.k_zero[mi] = lo;
     ks_s[d] = scale;
     kl_s[d] = lo;
+    ki_s[d] = __frcp_rn(scale);
   }
   // ---- values: per token over each group of D / VG channels (a warp per token, a lane per four channels) ----
   for (int t = warp; t < G; t += 4) {
@@ -189,8 +206,10 @@ __global__ void __launch_bounds__(128) kivi_append128_kernel(const void* k_src, 
       hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
     }
     if ((lane & (kLanes - 1)) == 0) {
-      vs_s[t * VG + lane / kLanes] = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), qmax), 1e-8f);
+      const float scale = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), qmax), 1e-8f);
+      vs_s[t * VG + lane / kLanes] = scale;
       vl_s[t * VG + lane / kLanes] = lo;
+      vi_s[t * VG + lane / kLanes] = __frcp_rn(scale);
     }
   }
   __syncthreads();
@@ -210,9 +229,13 @@ __global__ void __launch_bounds__(128) kivi_append128_kernel(const void* k_src, 
       for (int j = 0; j < CPI; j += 8) {
         const uint4 raw = *reinterpret_cast<const uint4*>(kt + t * D + c0 + j);
         const T* e = reinterpret_cast<const T*>(&raw);
+        const float4 l0 = *reinterpret_cast<const float4*>(kl_s + c0 + j), l1 = *reinterpret_cast<const float4*>(kl_s + c0 + j + 4);
+        const float4 i0 = *reinterpret_cast<const float4*>(ki_s + c0 + j), i1 = *reinterpret_cast<const float4*>(ki_s + c0 + j + 4);
+        const float lo8[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+        const float in8[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t code = affine_code(to_float<T>(e[k]), kl_s[c0 + j + k], ks_s[c0 + j + k], qmax);
+          const uint32_t code = affine_code_fast(to_float<T>(e[k]), lo8[k], in8[k], ks_s + c0 + j + k, qmax);
           w[((j + k) * BITS) >> 5] |= code << (((j + k) * BITS) & 31);
         }
       }
@@ -232,7 +255,7 @@ __global__ void __launch_bounds__(128) kivi_append128_kernel(const void* k_src, 
 #pragma unroll
         for (int k = 0; k < TPW; ++k) {
           const int t = (w0 + wi) * TPW + k;
-          w[wi] |= (uint32_t)affine_code(to_float<T>(vt[t * D + d]), vl_s[t * VG + gi], vs_s[t * VG + gi], qmax) << (k * BITS);
+          w[wi] |= affine_code_fast(to_float<T>(vt[t * D + d]), vl_s[t * VG + gi], vi_s[t * VG + gi], vs_s + t * VG + gi, qmax) << (k * BITS);
         }
       if (nw == 4) *reinterpret_cast<uint4*>(row + w0 * 4) = make_uint4(w[0], w[1], w[2], w[3]);
       else if (nw == 2) *reinterpret_cast<uint2*>(row + w0 * 4) = make_uint2(w[0], w[1]);
@@ -390,7 +413,7 @@ int pare_kivi_append(const void* k_src, const void* v_src, int src_dtype, int64_
   if (D == 128 && (bits == 2 || bits == 4) && (vg == 1 || vg == 4) && group <= 64 && (src_dtype == PARE_F16 || src_dtype == PARE_BF16) &&
       pare::aligned16(k_src) && pare::aligned16(v_src) && stride_b % 8 == 0 && stride_h % 8 == 0 && stride_t % 8 == 0 &&
       pare::aligned16(k_codes) && pare::aligned16(v_codes)) {
-    const size_t smem = (size_t)2 * group * 128 * 2 + 2 * 128 * sizeof(float) + 2 * (size_t)group * vg * sizeof(float);
+    const size_t smem = (size_t)2 * group * 128 * 2 + 3 * 128 * sizeof(float) + 3 * (size_t)group * vg * sizeof(float);
 #define PARE_AP(T)                                                                                                                   \
   do {                                                                                                                               \
     if (bits == 4 && vg == 1) pare::kivi_append128_kernel<T, 4, 1><<<grid, 128, smem, s>>>(k_src, v_src, stride_b, stride_h, stride_t, t0, c); \

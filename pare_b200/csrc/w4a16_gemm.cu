@@ -51,7 +51,8 @@ struct GemmParams {
   void* y;
   int64_t ldy;
   int M, N, K, ngroups, group_size;
-  int mt;               // activation rows per tile (UMMA N): 32, 64 or 128
+  int mt;               // activation rows per tile (UMMA N): 32, 64, 128 or 256
+  int raw_stages;       // depth of the packed-code ring (4; 2 when the 256-row activation tiles take the shared memory)
   int kblocks_per_split;
   int splits;
   float* partial;       // [splits][M][N]
@@ -221,10 +222,13 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
                                                                  const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // an activation block is mt rows x 128 bytes: 16 KB up to 128 rows, 32 KB at 256
+  const uint32_t b_blk = p.mt > 128 ? 32768u : 16384u, b_stage = 2 * b_blk;
+  const int rstages = p.raw_stages;
   unsigned char* a_ring = smem;                                   // kStages x 2 blocks x 16 KB
-  unsigned char* b_ring = a_ring + kStages * kStageBytes;         // kStages x 2 blocks x 16 KB (mt <= 128 rows x 128 B)
-  unsigned char* raw = b_ring + kStages * kStageBytes;            // kRawStages x 16 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + kRawStages * kRawBytes);
+  unsigned char* b_ring = a_ring + kStages * kStageBytes;         // kStages x 2 blocks x b_blk
+  unsigned char* raw = b_ring + kStages * b_stage;                // rstages x 16 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + rstages * kRawBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
   const uint32_t raw_full = s_u32(bars), raw_empty = s_u32(bars + 4), a_full = s_u32(bars + 8), b_full = s_u32(bars + 12),
                  ab_empty = s_u32(bars + 16), acc_full = s_u32(bars + 20);
@@ -271,8 +275,8 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
     // of the MMA.  A raw stage is one tensor-map copy of 128 rows x 128 bytes.
     if (lane == 1) {
       for (int rs = 0; rs < nkb / kRawKb; ++rs) {
-        const int slot = rs % kRawStages;
-        bar_wait(raw_empty + slot * 8, ((rs / kRawStages) & 1) ^ 1, status, dead);
+        const int slot = rs % rstages;
+        bar_wait(raw_empty + slot * 8, ((rs / rstages) & 1) ^ 1, status, dead);
         bar_expect(raw_full + slot * 8, kRawBytes);
         const int xb = (kb0 + rs * kRawKb) * (kBlockK / 2);   // byte column of the stage
         tma_tile(s_u32(raw) + slot * kRawBytes, &tm_w, xb, row0, raw_full + slot * 8);
@@ -282,8 +286,8 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
         const int s = kd % kStages;
         bar_wait(ab_empty + s * 8, ((kd / kStages) & 1) ^ 1, status, dead);
         bar_expect(a_full + s * 8, 2 * p.mt * 128);
-        tma_tile(s_u32(b_ring) + s * kStageBytes, &tm_x, (kb0 + 2 * kd) * kBlockK, m0, a_full + s * 8);
-        tma_tile(s_u32(b_ring) + s * kStageBytes + 16384, &tm_x, (kb0 + 2 * kd + 1) * kBlockK, m0, a_full + s * 8);
+        tma_tile(s_u32(b_ring) + s * b_stage, &tm_x, (kb0 + 2 * kd) * kBlockK, m0, a_full + s * 8);
+        tma_tile(s_u32(b_ring) + s * b_stage + b_blk, &tm_x, (kb0 + 2 * kd + 1) * kBlockK, m0, a_full + s * 8);
       }
     }
     __syncwarp();
@@ -301,12 +305,13 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
         const uint32_t par = (kd / kStages) & 1;
         bar_wait(a_full + s * 8, par, status, dead);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t a_desc = a_desc0 + (uint64_t)(s * (kStageBytes >> 4)), b_desc = b_desc0 + (uint64_t)(s * (kStageBytes >> 4));
+        const uint64_t a_desc = a_desc0 + (uint64_t)(s * (kStageBytes >> 4)), b_desc = b_desc0 + (uint64_t)(s * (b_stage >> 4));
         umma_f16(tmem_acc, a_desc, b_desc, idesc, kd != 0);
 #pragma unroll
-        for (int j = 1; j < 2 * (kBlockK / 16); ++j) {   // the second block's tiles start 16 KB after the first's
-          const uint64_t o = (uint64_t)((j >> 2) * (16384 >> 4) + (j & 3) * 2);
-          umma_f16(tmem_acc, a_desc + o, b_desc + o, idesc, 1u);
+        for (int j = 1; j < 2 * (kBlockK / 16); ++j) {   // the second block's tiles start one block after the first's
+          const uint64_t oa = (uint64_t)((j >> 2) * (16384 >> 4) + (j & 3) * 2);
+          const uint64_t ob = (uint64_t)((j >> 2) * (b_blk >> 4) + (j & 3) * 2);
+          umma_f16(tmem_acc, a_desc + oa, b_desc + ob, idesc, 1u);
         }
         umma_commit(ab_empty + s * 8);  // frees the operand stage when these MMAs have read it
       }
@@ -335,7 +340,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
     };
     load_meta(0, sc_n, zc_n);
     for (int kb = grp; kb < nkb; kb += 2) {
-      const int rsi = kb / kRawKb, slot = rsi % kRawStages;
+      const int rsi = kb / kRawKb, slot = rsi % rstages;
       if ((kb & (kRawKb - 1)) == grp) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -343,7 +348,7 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
           zc[i] = zc_n[i];
         }
         if (kb - grp + kRawKb < nkb) load_meta(kb - grp + kRawKb, sc_n, zc_n);
-        bar_wait(raw_full + slot * 8, (rsi / kRawStages) & 1, status, dead);
+        bar_wait(raw_full + slot * 8, (rsi / rstages) & 1, status, dead);
       }
       const int kd = kb >> 1, s = kd % kStages;   // this group writes block grp of stage kd
       bar_wait(ab_empty + s * 8, ((kd / kStages) & 1) ^ 1, status, dead);
@@ -447,12 +452,59 @@ __global__ void __launch_bounds__(kGemmThreads) w4a16_gemm_kernel(const __grid_c
   const int tile_rows = min(kRows, p.N - row0), tile_m = min(p.mt, p.M - m0);
   T* yg = reinterpret_cast<T*>(p.y);
   const T* bias = reinterpret_cast<const T*>(p.bias);
-  for (int idx = threadIdx.x; idx < tile_rows * tile_m; idx += kGemmThreads) {
-    const int mi = idx / tile_rows, n = row0 + (idx - mi * tile_rows), m = m0 + mi;
-    float v = 0.f;
-    for (int s = 0; s < p.splits; ++s) v += __ldcg(p.partial + ((size_t)s * p.M + m) * p.N + n);
-    if (bias) v += to_float<T>(bias[n]);
-    yg[(size_t)m * p.ldy + n] = from_float<T>(v);
+  const bool vec = tile_rows == kRows && (p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 7u) == 0 && (p.ldy & 3) == 0;
+  if (vec) {
+    // Four outputs per 16-byte load, four such pieces per thread and up to four splits requested before anything is
+    // added: the loop is a chain of L2 round trips, so what counts is how many loads each trip carries.  Every
+    // output is still the sum of its partials in split order.
+    constexpr int kU = 4, kS = 4, kQ = kRows / 4;
+    const int total = tile_m * kQ;
+    for (int base = threadIdx.x; base < total; base += kGemmThreads * kU) {
+      float4 acc[kU];
+      const float* src[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int idx = min(base + u * kGemmThreads, total - 1);
+        acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        src[u] = p.partial + (size_t)(m0 + idx / kQ) * p.N + row0 + (idx % kQ) * 4;
+      }
+      for (int s0 = 0; s0 < p.splits; s0 += kS) {
+        float4 t[kS][kU];
+#pragma unroll
+        for (int si = 0; si < kS; ++si)
+#pragma unroll
+          for (int u = 0; u < kU; ++u)
+            t[si][u] = s0 + si < p.splits ? __ldcg(reinterpret_cast<const float4*>(src[u] + (size_t)(s0 + si) * p.M * p.N))
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int si = 0; si < kS; ++si)
+#pragma unroll
+          for (int u = 0; u < kU; ++u) {
+            acc[u].x += t[si][u].x; acc[u].y += t[si][u].y; acc[u].z += t[si][u].z; acc[u].w += t[si][u].w;
+          }
+      }
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int idx = base + u * kGemmThreads;
+        if (idx < total) {
+          const int m = m0 + idx / kQ, n = row0 + (idx % kQ) * 4;
+          float4 v = acc[u];
+          if (bias) {
+            v.x += to_float<T>(bias[n]); v.y += to_float<T>(bias[n + 1]); v.z += to_float<T>(bias[n + 2]); v.w += to_float<T>(bias[n + 3]);
+          }
+          T o[4] = {from_float<T>(v.x), from_float<T>(v.y), from_float<T>(v.z), from_float<T>(v.w)};
+          *reinterpret_cast<uint2*>(yg + (size_t)m * p.ldy + n) = *reinterpret_cast<const uint2*>(o);
+        }
+      }
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < tile_rows * tile_m; idx += kGemmThreads) {
+      const int mi = idx / tile_rows, n = row0 + (idx - mi * tile_rows), m = m0 + mi;
+      float v = 0.f;
+      for (int s = 0; s < p.splits; ++s) v += __ldcg(p.partial + ((size_t)s * p.M + m) * p.N + n);
+      if (bias) v += to_float<T>(bias[n]);
+      yg[(size_t)m * p.ldy + n] = from_float<T>(v);
+    }
   }
   if (threadIdx.x == 0) p.counters[tile_id] = 0;
 }
@@ -476,30 +528,37 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-constexpr size_t kGemmSmem = 1024 + 2 * kStages * kStageBytes + kRawStages * kRawBytes + 25 * 8 + 64;
+// alignment slack + dequantized-weight ring + activation ring + packed-code ring + barriers and the TMEM slot
+constexpr size_t gemm_smem_bytes(int mt, int raw_stages) {
+  return 1024 + (size_t)kStages * kStageBytes + (size_t)kStages * 2 * (mt > 128 ? 32768 : 16384) + (size_t)raw_stages * kRawBytes + 25 * 8 + 64;
+}
+constexpr size_t kGemmSmemMax = gemm_smem_bytes(256, 2);   // 224 KB of rings: the 256-row tile leaves room for two packed stages
+static_assert(kGemmSmemMax >= gemm_smem_bytes(128, kRawStages) && kGemmSmemMax <= 227 * 1024, "shared memory plan");
 
 struct GemmPlan {
   int mt, mtiles, mpad, splits, kblocks_per_split;
 };
 
-GemmPlan gemm_plan(int M, int N, int K) {
+// K splits by a cost model in microseconds: whole waves of one CTA per SM, each CTA a fixed part (launch, first
+// loads, epilogue: ~10) plus a time per 64-column block that grows mildly with the activation tile, plus the
+// cross-CTA sum when K is split.  What it avoids is a second, nearly empty wave: 48 row tiles take 3 splits (144
+// CTAs), not 4 (192).
+GemmPlan gemm_plan_for(int mt, int M, int N, int K, double* cost_out) {
   GemmPlan g{};
-  g.mt = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+  g.mt = mt;
   g.mtiles = (M + g.mt - 1) / g.mt;
   g.mpad = g.mtiles * g.mt;
   const int row_tiles = (N + kRows - 1) / kRows;
   const int raw_stages = K / kRawK;
-  // K splits by a cost model in microseconds: whole waves of one CTA per SM, each CTA a fixed part (launch, first
-  // loads, epilogue: ~10) plus ~0.35 per 64-column block, plus the cross-CTA sum when K is split (~2).  What it
-  // avoids is a second, nearly empty wave: 48 row tiles take 3 splits (144 CTAs), not 4 (192).
   const int tiles = row_tiles * g.mtiles;
   const int sms = sm_count();
+  const double per_block = mt > 128 ? 0.40 : 0.35;
   int best_per = raw_stages;
   double best_cost = 1e30;
   for (int s = 1; s <= 16 && s <= raw_stages; ++s) {
     const int per = (raw_stages + s - 1) / s, s_eff = (raw_stages + per - 1) / per;
     const int waves = (tiles * s_eff + sms - 1) / sms;
-    const double cost = waves * (10.0 + per * kRawKb * 0.35) + (s_eff > 1 ? 2.0 : 0.0);
+    const double cost = waves * (10.0 + per * kRawKb * per_block) + (s_eff > 1 ? 3.0 + 0.25 * s_eff : 0.0);
     if (cost < best_cost - 1e-9) {
       best_cost = cost;
       best_per = per;
@@ -507,7 +566,19 @@ GemmPlan gemm_plan(int M, int N, int K) {
   }
   g.splits = (raw_stages + best_per - 1) / best_per;
   g.kblocks_per_split = best_per * kRawKb;
+  *cost_out = best_cost;
   return g;
+}
+
+// Above 128 rows a CTA may take 256 activation rows (UMMA N = 256, 256 TMEM columns): a weight stage is then
+// dequantized once per 256 rows, and dequantization, not the tensor pipe, is what bounds this kernel.  Layers with few
+// row tiles can be better off with twice the CTAs of 128 rows; the cost model decides.
+GemmPlan gemm_plan(int M, int N, int K) {
+  double c = 0.0;
+  if (M <= 128) return gemm_plan_for(M <= 32 ? 32 : (M <= 64 ? 64 : 128), M, N, K, &c);
+  double c128 = 0.0, c256 = 0.0;
+  const GemmPlan g128 = gemm_plan_for(128, M, N, K, &c128), g256 = gemm_plan_for(256, M, N, K, &c256);
+  return c256 <= c128 ? g256 : g128;
 }
 
 }  // namespace
@@ -584,6 +655,7 @@ int gemm_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   p.ngroups = K / G;
   p.group_size = G;
   p.mt = g.mt;
+  p.raw_stages = g.mt > 128 ? 2 : kRawStages;
   p.kblocks_per_split = g.kblocks_per_split;
   p.splits = g.splits;
   p.counters = reinterpret_cast<int*>(ws);
@@ -591,9 +663,8 @@ int gemm_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
 
   const dim3 grid(row_tiles, g.splits, g.mtiles);
   auto launch = [&](auto kern) -> int {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem) != cudaSuccess)
-      return PARE_ERR_CUDA;
-    kern<<<grid, kGemmThreads, kGemmSmem, stream>>>(tm, tw, p);
+    if (!ensure_smem_attr(reinterpret_cast<const void*>(kern), (int)kGemmSmemMax)) return PARE_ERR_CUDA;
+    kern<<<grid, kGemmThreads, gemm_smem_bytes(p.mt, p.raw_stages), stream>>>(tm, tw, p);
     return launch_status();
   };
   return x_dtype == PARE_F16 ? launch(w4a16_gemm_kernel<__half>) : launch(w4a16_gemm_kernel<__nv_bfloat16>);

@@ -79,14 +79,14 @@ __global__ void __launch_bounds__(128) w4a16_prep_kernel(const GemvParams p) {
       for (int i = 0; i < 8; ++i) v[i] = to_float<T>(e[i]);
       if (p.input_scale) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = __fdiv_rn(v[i], __ldg(p.input_scale + k + i));
+        for (int i = 0; i < 8; ++i) v[i] = to_float<T>(from_float<T>(__fdiv_rn(v[i], __ldg(p.input_scale + k + i))));   // quotient rounded to the activation type, in every kernel
       }
     } else {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int src = p.col_perm ? __ldg(p.col_perm + k + i) : k + i;
         v[i] = to_float<T>(xg[(size_t)m * p.ldx + src]);
-        if (p.input_scale) v[i] = __fdiv_rn(v[i], __ldg(p.input_scale + src));
+        if (p.input_scale) v[i] = to_float<T>(from_float<T>(__fdiv_rn(v[i], __ldg(p.input_scale + src))));
       }
     }
   }

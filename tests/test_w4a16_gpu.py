@@ -268,7 +268,7 @@ def _check_tensor_core(y, ql, x, dtype, **kw):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("m", [17, 32, 64, 100, 128, 200, 256])
+@pytest.mark.parametrize("m", [17, 32, 64, 100, 128, 129, 200, 256, 300, 520])
 @pytest.mark.parametrize("shape", [(512, 1024), (1000, 512), (4096, 4096)])
 def test_tensor_core_path_matches_oracle(shape, m, dtype, cuda_lib):
     n, k = shape
