@@ -70,6 +70,7 @@ def parse_args():
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="for profiler captures: GPU work only")
     ap.add_argument("--table-batches", default="1,4,16", help="activation rows of the per-layer table")
     ap.add_argument("--skip-70b", action="store_true", help="leave out the 70B-shaped stack")
+    ap.add_argument("--attn-filter", default="", help="run only the attention cells whose name contains this text (profiler captures)")
     ap.add_argument("--only", default="", help="comma list of tables to run (layers,act_order,attention,kivi_cache,prefill,70b)")
     return ap.parse_args()
 
@@ -469,7 +470,7 @@ def prompt_table(args, dtype, device, lengths=(512, 2048)) -> dict:
     return table
 
 
-def attention_table(dtype, device, peak: float, cases) -> dict:
+def attention_table(dtype, device, peak: float, cases, name_filter: str = "") -> dict:
     """Fused KIVI decode attention alone (D = 128, g32, residual window 128): one CUDA graph over ``layers`` distinct
     caches (at least 0.5 GB together, so nothing is served from L2), us per call and fraction of the HBM peak by the
     bytes the call must read (168 B per compressed token and KV head at 4 bits, 104 B at 2 bits, 512 B per window
@@ -481,6 +482,9 @@ def attention_table(dtype, device, peak: float, cases) -> dict:
     for case in cases:
         batch, ctx, hq, hkv, bits = case[:5]
         v_group = case[5] if len(case) > 5 else None
+        key = f"b{batch}_ctx{ctx}_{hq}q{hkv}kv_{bits}bit" + (f"_vg{v_group}" if v_group else "")
+        if name_filter and name_filter not in key:
+            continue
         per_token = (168 if bits == 4 else 104) + (24 if v_group else 0)
         layer_bytes = batch * hkv * ctx * per_token
         layers = max(2, min(192, -(-(512 << 20) // layer_bytes)))
@@ -508,7 +512,6 @@ def attention_table(dtype, device, peak: float, cases) -> dict:
         us = time_graph(run, reps=10 if layer_bytes > (64 << 20) else 20) / layers * 1e6
         st = cache._stores[0]
         nbytes = batch * hkv * (st.n_comp * per_token + (st.r_len + 1) * 512) + batch * hq * 128 * 4
-        key = f"b{batch}_ctx{ctx}_{hq}q{hkv}kv_{bits}bit" + (f"_vg{v_group}" if v_group else "")
         table[key] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peak, 4),
                       "bytes": nbytes, "caches": layers}
         del cache
@@ -718,7 +721,7 @@ def run_ours(args) -> None:
     torch.cuda.empty_cache()
     if world == 1:
         line["act_order"] = act_order_table(peak, tf_peak, f"cuda:{local}") if want("act_order") else {}
-        line["attention"] = attention_table(dtype, torch.device(f"cuda:{local}"), peak, attention_cases()) if want("attention") else {}
+        line["attention"] = attention_table(dtype, torch.device(f"cuda:{local}"), peak, attention_cases(), args.attn_filter) if want("attention") else {}
         line["kivi_cache"] = kivi_cache_table(dtype, torch.device(f"cuda:{local}"), peak) if want("kivi_cache") else {}
         line["prefill_attention"] = prefill_attention_table(dtype, torch.device(f"cuda:{local}")) if want("prefill") else {}
         line["prompt"] = prompt_table(args, dtype, torch.device(f"cuda:{local}")) if want("prefill") else {}

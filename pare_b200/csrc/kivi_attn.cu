@@ -171,6 +171,9 @@ __device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpr
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void sts_h(uint32_t addr, __half v) {
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(*reinterpret_cast<const unsigned short*>(&v)) : "memory");
+}
 __device__ __forceinline__ void named_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -433,7 +436,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
     unsigned char* pst = Pring + team * p_stage_bytes(VG);   // the team's probability buffer
     float* gm = gmax_s + team * (4 * kHeads);
     // where this lane's four (tile, row half) tokens go in a probability row, per head of its pair
-    int poff[2][2][2];
+    uint32_t paddr[2][2][2];   // shared-memory addresses
 #pragma unroll
     for (int tile = 0; tile < 2; ++tile)
 #pragma unroll
@@ -441,7 +444,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int tl = 32 * tw + 16 * tile + gid + 8 * hf, head = 2 * tig + e;
-          poff[tile][hf][e] = head * kPHead + p_offset<BITS>(tl, head);
+          paddr[tile][hf][e] = smem_u32(pst) + head * kPHead + p_offset<BITS>(tl, head);
         }
     const int pg = VG == 1 ? 0 : tw;   // value part: channels [32 tw, 32 tw + 32) = one value group
     const int pchunk = ((tig ^ (gid >> 1)) & 3) * 16;
@@ -629,7 +632,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
         for (int g = 0; g < VG; ++g) z_run[g][e] *= alpha[e];
       }
       // ---------------- probabilities times the value scale into the team's operand buffer ----------------
-      {
+      // (FULL: all 128 tokens of the block exist, which is every block but the last one of a context: no predicates)
+      auto write_probs = [&](auto full_tag) {
+        constexpr bool FULL = decltype(full_tag)::value;
         const float* vs = reinterpret_cast<const float*>(st + off_vs);
         const float* vz = reinterpret_cast<const float*>(st + off_vz);
 #pragma unroll
@@ -637,7 +642,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
             const int tl = 32 * tw + 16 * tile + gid + 8 * hf;
-            const bool live = tl < bvalid;
+            const bool live = FULL || tl < bvalid;
             float pe[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
@@ -653,13 +658,15 @@ __global__ void __launch_bounds__(kAttnThreads, 2) kivi_decode_attn_kernel(const
                 const float pv = pe[e] * sc;
                 z_run[g][e] = fmaf(pe[e], zc, z_run[g][e]);
                 const __half hv = __float2half_rn(pv);
-                unsigned char* dst = pst + g * (2 * kHeads * kPHead) + poff[tile][hf][e];
-                *reinterpret_cast<__half*>(dst) = hv;
-                if constexpr (P2) *reinterpret_cast<__half*>(dst + kHeads * kPHead) = __float2half_rn(pv - __half2float(hv));
+                const uint32_t dst = paddr[tile][hf][e] + g * (2 * kHeads * kPHead);
+                sts_h(dst, hv);
+                if constexpr (P2) sts_h(dst + kHeads * kPHead, __float2half_rn(pv - __half2float(hv)));
               }
             }
           }
-      }
+      };
+      if (bvalid == kBlk) write_probs(std::true_type{});
+      else write_probs(std::false_type{});
       named_sync(team_bar, 128);   // the block's probabilities are complete
       // ---------------- O = O * alpha + codes_v^T . P for this warp's 32 channels ----------------
       {

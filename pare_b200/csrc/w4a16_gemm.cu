@@ -541,8 +541,8 @@ struct GemmPlan {
 
 // K splits by a cost model in microseconds: whole waves of one CTA per SM, each CTA a fixed part (launch, first
 // loads, epilogue: ~10) plus a time per 64-column block that grows mildly with the activation tile, plus the
-// cross-CTA sum when K is split.  What it avoids is a second, nearly empty wave: 48 row tiles take 3 splits (144
-// CTAs), not 4 (192).
+// cross-CTA sum when K is split (it grows with the rows: splitting pays below about a hundred rows only).  It also
+// avoids a second, nearly empty wave.
 GemmPlan gemm_plan_for(int mt, int M, int N, int K, double* cost_out) {
   GemmPlan g{};
   g.mt = mt;
@@ -558,7 +558,9 @@ GemmPlan gemm_plan_for(int mt, int M, int N, int K, double* cost_out) {
   for (int s = 1; s <= 16 && s <= raw_stages; ++s) {
     const int per = (raw_stages + s - 1) / s, s_eff = (raw_stages + per - 1) / per;
     const int waves = (tiles * s_eff + sms - 1) / sms;
-    const double cost = waves * (10.0 + per * kRawKb * per_block) + (s_eff > 1 ? 3.0 + 0.25 * s_eff : 0.0);
+    // a split costs its fp32 partials written and read again by the one CTA per tile that adds them: measured at
+    // about 1 us per MB of partials (qkv 6144 x 4096, 256 rows: 43 us unsplit, 54 / 55 us in 2 / 3 splits)
+    const double cost = waves * (10.0 + per * kRawKb * per_block) + (s_eff > 1 ? 3.0 + (double)s_eff * M * N * 8e-6 : 0.0);
     if (cost < best_cost - 1e-9) {
       best_cost = cost;
       best_per = per;
