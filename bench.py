@@ -53,7 +53,7 @@ FALLBACK_HBM_GBS = 6650.0
 LAUNCHES_PER_BLOCK = 5
 # dram__bytes_read + dram__bytes_write of one gate|up GEMV launch (28672 x 4096, M = 1): a stored figure from an ncu
 # capture of that launch, not measured by this script (the JSON line says so in roofline.traffic_source)
-GATE_UP_DRAM_TRAFFIC = 66_100_000 + 540_000
+GATE_UP_DRAM_TRAFFIC = 66_143_000 + 577_000   # read + write, mean of two captured launches
 
 
 def parse_args():
