@@ -121,10 +121,9 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// ---- activations for the tensor-core path: inside every 8-column chunk the columns are stored in
-// the order 0,4,1,5,2,6,3,7 — the order in which one 32-bit word of codes unpacks into pairs — so the
-// dequantizing threads never have to re-pair registers.  (The contraction does not care about the
-// order of K as long as both operands agree.)  Applies the act-order gather and the input scale. ----
+// ---- activations for the tensor-core path when they need work: the act-order gather and / or the run-time input
+// scale, into a dense [M][K] copy in column order.  Plain layers skip this launch: the activation tiles are then
+// fetched by TMA straight from the caller's tensor. ----
 template <typename T>
 __global__ void w4a16_gemm_prep_kernel(const T* x, int64_t ldx, const int32_t* col_perm, const float* input_scale, T* xq,
                                        int M, int K) {
@@ -134,8 +133,7 @@ __global__ void w4a16_gemm_prep_kernel(const T* x, int64_t ldx, const int32_t* c
   const int src = col_perm ? col_perm[k] : k;
   float v = to_float<T>(x[(int64_t)m * ldx + src]);
   if (input_scale) v = __fdiv_rn(v, input_scale[src]);
-  const int pos = k & 7, slot = ((pos & 3) << 1) | (pos >> 2);
-  xq[(int64_t)m * K + (k & ~7) + slot] = from_float<T>(v);
+  xq[(int64_t)m * K + k] = from_float<T>(v);
 }
 
 template <typename T>
@@ -161,24 +159,24 @@ struct Pair<__nv_bfloat16> {
 };
 
 // Packed fp32 pairs (two independent IEEE operations per instruction).
-__device__ __forceinline__ void fma_pair(float& a, float& b, float m, float c) {   // (a, b) = (a, b) * m + c
+__device__ __forceinline__ void fma_pair2(float& a, float& b, float m, float c0, float c1) {   // (a, b) = (a, b) * m + (c0, c1)
   asm("{\n\t.reg .b64 x, y, z;\n\t"
       "mov.b64 x, {%0, %1};\n\t"
       "mov.b64 y, {%2, %2};\n\t"
-      "mov.b64 z, {%3, %3};\n\t"
+      "mov.b64 z, {%3, %4};\n\t"
       "fma.rn.f32x2 x, x, y, z;\n\t"
       "mov.b64 {%0, %1}, x;\n\t}"
       : "+f"(a), "+f"(b)
-      : "f"(m), "f"(c));
+      : "f"(m), "f"(c0), "f"(c1));
 }
-__device__ __forceinline__ void mul_pair(float& a, float& b, float m) {   // (a, b) = (a, b) * m
+__device__ __forceinline__ void mul_pair2(float& a, float& b, float m0, float m1) {   // (a, b) = (a, b) * (m0, m1)
   asm("{\n\t.reg .b64 x, y;\n\t"
       "mov.b64 x, {%0, %1};\n\t"
-      "mov.b64 y, {%2, %2};\n\t"
+      "mov.b64 y, {%2, %3};\n\t"
       "mul.rn.f32x2 x, x, y;\n\t"
       "mov.b64 {%0, %1}, x;\n\t}"
       : "+f"(a), "+f"(b)
-      : "f"(m));
+      : "f"(m0), "f"(m1));
 }
 
 // Per (weight row, group) constants of the dequantization below.
@@ -194,25 +192,30 @@ struct DqConst {
   }
 };
 
-// One 32-bit word of codes -> 8 dequantized 16-bit values (slot order 0,4,1,5,2,6,3,7) as one 16-byte chunk, each
-// EXACTLY dtype(fp32((q - zero) * scale)): the weight the reference's eager path feeds its GEMM
+// One 32-bit word of codes -> 8 dequantized 16-bit values in COLUMN ORDER as one 16-byte chunk, each EXACTLY
+// dtype(fp32((q - zero) * scale)): the weight the reference's eager path feeds its GEMM
 // (pare/layers/linear.py:112-118, 129: fp32 subtract, fp32 multiply, cast).  A code nibble left in place at bits
-// 4k .. 4k+3 and read as a float's bit pattern is the subnormal q * 2^(4k - 149); one fused multiply-add by 2^127 with
-// -zero * 2^(4k - 22) gives (q - zero) * 2^(4k - 22) with the single rounding of the reference's fp32 subtraction
-// (powers of two do not change a rounding; no rounding at all for the integer zero-points of the reference's
-// quantizers), one multiply by scale * 2^(22 - 4k) its fp32 product, one conversion per pair the cast.
+// 4k .. 4k+3 (k = 0..3; the upper four codes after one shift by 16) and read as a float's bit pattern is the subnormal
+// q * 2^(4k - 149); one fused multiply-add by 2^127 with -zero * 2^(4k - 22) gives (q - zero) * 2^(4k - 22) with the
+// single rounding of the reference's fp32 subtraction (powers of two do not change a rounding; no rounding at all for
+// the integer zero-points of the reference's quantizers), one multiply by scale * 2^(22 - 4k) its fp32 product, one
+// conversion per pair the cast.  The two lanes of a packed instruction are neighbouring columns (positions k, k + 1),
+// each with its own constants, so the operand tile is in the activations' own column order and the activations need
+// no re-ordering pass.
 template <typename T>
 __device__ __forceinline__ uint4 dequant_word(uint32_t w, const DqConst& c) {
   const uint32_t t = w >> 16;
   constexpr float kTwo127 = 1.7014118346046923e38f;
   uint32_t o[4];
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    float a = __uint_as_float(w & (0xFu << (4 * k)));   // code k
-    float b = __uint_as_float(t & (0xFu << (4 * k)));   // code k + 4
-    fma_pair(a, b, kTwo127, c.zc[k]);
-    mul_pair(a, b, c.sc[k]);
-    o[k] = Pair<T>::pack(a, b);
+  for (int j = 0; j < 4; ++j) {   // columns 2j, 2j + 1
+    const uint32_t src = j < 2 ? w : t;
+    const int k = (2 * j) & 3;
+    float a = __uint_as_float(src & (0xFu << (4 * k)));
+    float b = __uint_as_float(src & (0xFu << (4 * k + 4)));
+    fma_pair2(a, b, kTwo127, c.zc[k], c.zc[k + 1]);
+    mul_pair2(a, b, c.sc[k], c.sc[k + 1]);
+    o[j] = Pair<T>::pack(a, b);
   }
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
@@ -609,8 +612,10 @@ int gemm_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   void* xq = ws + kCounterBytes;
 
-  // 1) activations: slot order inside every 8-column chunk, gather, input scale
-  {
+  // 1) activations: gathered / scaled into the workspace if the layer asks for that (or the caller's rows cannot be
+  //    described by a tensor map: 16-byte aligned base and row pitch), otherwise used where they are
+  const bool direct = col_perm == nullptr && input_scale == nullptr && aligned16(x) && (ldx % 8) == 0;
+  if (!direct) {
     const int64_t total = (int64_t)M * K;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (x_dtype == PARE_F16)
@@ -621,15 +626,17 @@ int gemm_forward(const void* x, int x_dtype, int64_t ldx, const uint8_t* packed,
     if (cudaGetLastError() != cudaSuccess) return PARE_ERR_CUDA;
   }
 
-  // 2) tensor map over the prepared activations [mpad][K], box 64 columns x mt rows, 128B swizzle
+  // 2) tensor map over the activations [M][K] (rows of the last tile beyond M read as zeros), box 64 columns x mt
+  //    rows, 128B swizzle
   EncodeTiledFn enc = encode_fn();
   PARE_REQUIRE(enc != nullptr, PARE_ERR_CUDA);
   CUtensorMap tm;
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)g.mpad};
-  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)(direct ? ldx : K) * 2};
   const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)g.mt};
   const cuuint32_t estr[2] = {1, 1};
-  PARE_REQUIRE(enc(&tm, x_dtype == PARE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xq, dims,
+  PARE_REQUIRE(enc(&tm, x_dtype == PARE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                   direct ? const_cast<void*>(x) : xq, dims,
                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
                PARE_ERR_CUDA);

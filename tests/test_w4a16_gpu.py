@@ -284,6 +284,25 @@ def test_tensor_core_path_matches_oracle(shape, m, dtype, cuda_lib):
     assert torch.equal(y, y2)
 
 
+@pytest.mark.parametrize("pitch_pad,offset", [(8, 0), (3, 0), (8, 1)])
+def test_tensor_core_path_reads_activations_in_place(pitch_pad, offset, cuda_lib):
+    """Above 16 rows the activation tiles are fetched straight from the caller's tensor when its rows are 16-byte
+    aligned (dense, or a view whose row pitch is a multiple of 8 elements), and through a gathered copy otherwise (a
+    pitch of K + 3, or a view that starts 2 bytes off the alignment): the same bits as for the dense tensor."""
+    n, k, m = 1024, 1024, 200
+    ql = make_ql(n, k, seed=5).cuda()
+    sc, ze = ql.scale.squeeze(-1).contiguous(), ql.zero.squeeze(-1).contiguous()
+    torch.manual_seed(9)
+    dense = torch.randn(m, k, device="cuda", dtype=torch.float16)
+    want = w4a16_forward(dense, ql.packed_weight, sc, ze, 128)
+    _check_tensor_core(want, ql, dense, torch.float16)
+    wide = torch.zeros(m, k + pitch_pad, device="cuda", dtype=torch.float16)
+    view = wide[:, offset:offset + k]
+    view.copy_(dense)
+    assert view.stride(0) == k + pitch_pad and not view.is_contiguous()
+    assert torch.equal(w4a16_forward(view, ql.packed_weight, sc, ze, 128), want)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_tensor_core_operand_is_the_reference_cast_bit_for_bit(dtype, cuda_lib):
     """One-hot activation rows pick single weights out of the tensor-core path: every output is one operand value,
