@@ -258,6 +258,14 @@ int pare_rmsnorm_residual(const void* x, const void* delta, const void* weight, 
 int pare_silu_mul(const void* gate_up, void* out, void* prepared_out, int rows, int n, int64_t ld, int dtype,
                   void* stream);
 
+/* Rotary embedding of a prompt's q or k (model code in front of the cache, like the `rope` argument of
+ * pare_kivi_decode_attn for one token): out [B][H][T][D] dense = x [B][H][T][D] (element strides stride_b/h/t,
+ * channels contiguous) rotated with rows [T][D] floats, cos[0..D/2) then sin[0..D/2) per token, pairs (i, i + D/2):
+ * x'[i] = x[i] cos[i] - x[i+D/2] sin[i], x'[i+D/2] = x[i+D/2] cos[i] + x[i] sin[i]; fp32 products and sum, each
+ * rounded, then rounded to the dtype (F16 / BF16).  No counterpart in the reference, whose callers rotate. */
+int pare_rope(const void* x, int64_t stride_b, int64_t stride_h, int64_t stride_t, void* out, const float* rows,
+              int B, int H, int T, int D, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------
  * W4A16 decode linear without any caller-provided workspace.  No counterpart in the reference;
  * it exists for callers that cannot allocate device memory (code running inside another

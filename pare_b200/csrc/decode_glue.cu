@@ -170,6 +170,29 @@ int silu_launch(const void* gate_up, void* out, void* prepared, int rows, int n,
                     n, ld, vec_ok);
 }
 
+// Rotary embedding of x [B][H][T][D] (element strides sb / sh / st, channels contiguous) into a dense out [B][H][T][D]:
+// pairs (i, i + D/2), rows [T][D] = cos[0..D/2) | sin[0..D/2) per token.  Products and sum in fp32, each rounded
+// separately (no fused multiply-add), then rounded to T: the arithmetic of the decode-attention kernel's rope8 and of
+// an fp32 restatement.  One thread per pair of channels.
+template <typename T>
+__global__ void rope_kernel(const T* x, int64_t sb, int64_t sh, int64_t st, T* out, const float* rows, int B, int H, int Tn, int D) {
+  const int half = D >> 1;
+  const int64_t total = (int64_t)B * H * Tn * half;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % half);
+    const int64_t row = idx / half;                 // (b * H + h) * Tn + t
+    const int t = (int)(row % Tn);
+    const int64_t bh = row / Tn;
+    const int h = (int)(bh % H), b = (int)(bh / H);
+    const T* src = x + (int64_t)b * sb + (int64_t)h * sh + (int64_t)t * st;
+    const float a = to_float<T>(src[i]), bb = to_float<T>(src[i + half]);
+    const float co = rows[(int64_t)t * D + i], si = rows[(int64_t)t * D + half + i];
+    T* dst = out + row * D;
+    dst[i] = from_float<T>(__fsub_rn(__fmul_rn(a, co), __fmul_rn(bb, si)));
+    dst[i + half] = from_float<T>(__fadd_rn(__fmul_rn(bb, co), __fmul_rn(a, si)));
+  }
+}
+
 }  // namespace
 }  // namespace pare
 
@@ -201,6 +224,24 @@ int pare_silu_mul(const void* gate_up, void* out, void* prepared_out, int rows, 
   if (dtype == PARE_F16) return pare::silu_launch<__half>(gate_up, out, prepared_out, rows, n, ld, s);
   if (dtype == PARE_BF16) return pare::silu_launch<__nv_bfloat16>(gate_up, out, prepared_out, rows, n, ld, s);
   return PARE_ERR_DTYPE;
+}
+
+// out [B][H][T][D] (dense) = rotary embedding of x [B][H][T][D] (element strides given, channels contiguous) with one
+// row of D floats (cos | sin) per token: the step a model takes between its q|k|v projection and the prompt's
+// attention (the reference's callers hand update() keys that are already rotated).
+int pare_rope(const void* x, int64_t stride_b, int64_t stride_h, int64_t stride_t, void* out, const float* rows, int B, int H,
+              int T, int D, int dtype, void* stream) {
+  PARE_REQUIRE(x && out && rows && B > 0 && H > 0 && T > 0 && D > 0 && (D % 2) == 0, PARE_ERR_SHAPE);
+  const int64_t total = (int64_t)B * H * T * (D / 2);
+  const unsigned blocks = (unsigned)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == PARE_F16)
+    pare::rope_kernel<__half><<<blocks, 256, 0, s>>>((const __half*)x, stride_b, stride_h, stride_t, (__half*)out, rows, B, H, T, D);
+  else if (dtype == PARE_BF16)
+    pare::rope_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)x, stride_b, stride_h, stride_t, (__nv_bfloat16*)out, rows, B, H, T, D);
+  else
+    return PARE_ERR_DTYPE;
+  return pare::launch_status();
 }
 
 }  // extern "C"

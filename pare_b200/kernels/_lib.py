@@ -52,6 +52,7 @@ SIGNATURES: dict[str, tuple] = {
                                _i, _i, _i, _i, _i, _i, C.c_float, _i, _vp]),
     "pare_rmsnorm_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, C.c_float, _i, _vp]),
     "pare_silu_mul": (_i, [_vp, _vp, _vp, _i, _i, _i64, _i, _vp]),
+    "pare_rope": (_i, [_vp, _i64, _i64, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "pare_peer_buffer_create": (_i, [_sz, C.POINTER(C.c_void_p), C.c_char_p]),
     "pare_peer_buffer_open": (_i, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "pare_peer_buffer_close": (_i, [_vp]),

@@ -61,6 +61,13 @@ def apply_rope(x: Tensor, rows: Tensor) -> Tensor:
     """Rotary embedding of ``x [..., T, D]`` with ``rows [T, D]`` (or ``[D]``) of a :func:`rope_table`: pairs
     ``(i, i + D/2)``, products and sum in float32, each rounded separately, result rounded to ``x.dtype`` -- what the
     attention kernel does to ``q`` and the newest key."""
+    if (x.is_cuda and x.dim() == 4 and x.dtype in (torch.float16, torch.bfloat16) and x.stride(3) == 1 and rows.dim() == 2
+            and rows.shape[0] == x.shape[2] and rows.dtype == torch.float32 and rows.is_contiguous() and rows.device == x.device):
+        out = torch.empty(x.shape, device=x.device, dtype=x.dtype)     # one pass instead of a dozen element-wise launches
+        B, H, T, D = x.shape
+        _lib.check(_lib.lib().pare_rope(x.data_ptr(), x.stride(0), x.stride(1), x.stride(2), out.data_ptr(), rows.data_ptr(),
+                                        B, H, T, D, _lib.dtype_code(x.dtype), _lib.current_stream(x.device)), "pare_rope")
+        return out
     half = x.shape[-1] // 2
     cos, sin = rows[..., :half].float(), rows[..., half:].float()
     a, b = x[..., :half].float(), x[..., half:].float()
@@ -85,7 +92,9 @@ def prefill_attention(q: Tensor, k: Tensor, v: Tensor, scale: float | None = Non
     q, k, v = usable(q), usable(k), usable(v)
     B, Hq, Tq, D = q.shape
     H, Tk = k.shape[1], k.shape[2]
-    out = torch.empty(B, Hq, Tq, D, device=q.device, dtype=q.dtype)
+    # token-major storage [B, Tq, Hq, D] behind the [B, Hq, Tq, D] result: the o projection that follows reads the
+    # heads of a token side by side, so its ``transpose(1, 2).reshape(B * Tq, Hq * D)`` is a view, not a copy
+    out = torch.empty(B, Tq, Hq, D, device=q.device, dtype=q.dtype).transpose(1, 2)
     status = _lib.lib().pare_prefill_attn(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _lib.dtype_code(q.dtype),
         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2),

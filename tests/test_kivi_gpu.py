@@ -487,3 +487,28 @@ def test_cache_prefill_then_decode(cuda_lib):
     out2 = a.prefill(0, q2, k2, v2)
     _bars_prefill(out2.float().cpu().numpy(), ref2, torch.float16)
     assert a.seq_len(0) == b.seq_len(0) == T + 1 + 64
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_rope_kernel_bit_exact_on_strided_views(dtype, cuda_lib):
+    """The prompt's rotary embedding in one launch (``apply_rope`` on 4-D CUDA tensors): on the q / k views of a fused
+    q|k|v projection output (token-major rows, heads interleaved) it equals the fp32 restatement rounded to the dtype,
+    bit for bit, and the element-wise torch formula it replaces."""
+    from pare_b200.kv_cache import apply_rope, rope_table
+    B, T, hq, hkv = 2, 70, 6, 2
+    torch.manual_seed(4)
+    qkv = torch.randn(B, T, (hq + 2 * hkv) * D, device="cuda").to(dtype)
+    q = qkv[..., : hq * D].unflatten(2, (hq, D)).transpose(1, 2)
+    k = qkv[..., hq * D:(hq + hkv) * D].unflatten(2, (hkv, D)).transpose(1, 2)
+    table = rope_table(T + 5, D, 500000.0, device="cuda")
+    rows = ok.rope_rows(np.arange(T + 5), D, 500000.0)
+    for x in (q, k):
+        assert not x.is_contiguous()
+        got = apply_rope(x, table[3:3 + T])
+        assert got.shape == x.shape and got.dtype == dtype and got.is_contiguous()
+        want = torch.from_numpy(ok.apply_rope(x.float().cpu().numpy(), rows[3:3 + T])).to(dtype)
+        assert torch.equal(got.cpu(), want)
+        half = D // 2
+        cos, sin = table[3:3 + T, :half], table[3:3 + T, half:]
+        a, b = x[..., :half].float(), x[..., half:].float()
+        assert torch.equal(got, torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1).to(dtype))
