@@ -44,71 +44,18 @@ __device__ __forceinline__ uint8_t affine_code(float x, float lo, float scale, f
   return (uint8_t)rintf(q);
 }
 
-template <typename T>
-struct Packed2;
-template <>
-struct Packed2<__half> { using type = __half2; };
-template <>
-struct Packed2<__nv_bfloat16> { using type = __nv_bfloat162; };
-
-// two independent fp32 operations per instruction
-__device__ __forceinline__ float2 mul2f(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t.reg .b64 x, y;\n\tmov.b64 x, {%2, %3};\n\tmov.b64 y, {%4, %5};\n\tmul.rn.f32x2 x, x, y;\n\tmov.b64 {%0, %1}, x;\n\t}"
-      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-__device__ __forceinline__ float2 fma2f(float2 a, float2 b, float2 c) {
-  float2 d;
-  asm("{\n\t.reg .b64 x, y, z;\n\tmov.b64 x, {%2, %3};\n\tmov.b64 y, {%4, %5};\n\tmov.b64 z, {%6, %7};\n\tfma.rn.f32x2 x, x, y, z;\n\tmov.b64 {%0, %1}, x;\n\t}"
-      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-  return d;
-}
-
-// Eight codes at once, code k at bit k * BITS of the result, each bit-identical to affine_code, without a division
-// per element.  The quotient is approximated by a product with the correctly rounded reciprocal (error below 2 units
-// in the last place of a number below 16, i.e. < 4e-6) and rounded to the nearest integer by adding 1.5 * 2^23
-// (round-to-nearest-even, like rintf; subtracting the constant again leaves the integer as a float).  Only an
-// approximation within 1e-4 of a rounding boundary could round differently from the exact quotient: if any of the
-// eight is that close (about one call in a thousand), all eight take the division.  x >= lo and (hi - lo) / scale <=
-// qmax up to rounding, so the clamp only matters on that exact path.  The arithmetic runs on packed fp32 pairs (a
-// difference is a fused multiply-add by -1, which rounds like the subtraction); the integers are packed by exact fp32
-// sums of code * 2^(k BITS) (below 2^24 for four 4-bit or eight 2-bit codes), one conversion per 16 bits of codes.
-// scale: pointer to the first element's scale, stride between the elements' scales.
-template <int BITS>
-__device__ __forceinline__ uint32_t affine_codes8(const float (&x)[8], const float (&lo)[8], const float (&inv)[8],
-                                                  const float* scale, int scale_stride, float qmax) {
-  constexpr float kMagic = 12582912.f;
-  const float2 magic = make_float2(kMagic, kMagic), one = make_float2(1.f, 1.f), neg = make_float2(-1.f, -1.f);
-  float cf[8];
-  float worst = 0.f;
-#pragma unroll
-  for (int k = 0; k < 8; k += 2) {
-    const float2 d = fma2f(make_float2(lo[k], lo[k + 1]), neg, make_float2(x[k], x[k + 1]));   // x - lo
-    const float2 q = mul2f(d, make_float2(inv[k], inv[k + 1]));
-    const float2 r = fma2f(q, one, magic);                                                      // q + magic
-    const float2 c = fma2f(magic, neg, r);                                                      // r - magic: the integer
-    const float2 f = fma2f(q, neg, c);                                                          // c - q
-    worst = fmaxf(worst, fmaxf(fabsf(f.x), fabsf(f.y)));
-    cf[k] = c.x;
-    cf[k + 1] = c.y;
-  }
-  if (worst > 0.4999f || !(worst == worst)) {   // near a boundary (or not a number): the exact path for all eight
-    uint32_t w = 0u;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) w |= (uint32_t)affine_code(x[k], lo[k], scale[k * scale_stride], qmax) << (k * BITS);
-    return w;
-  }
-  if constexpr (BITS == 4) {
-    const float a = fmaf(cf[3], 4096.f, fmaf(cf[2], 256.f, fmaf(cf[1], 16.f, cf[0])));
-    const float b = fmaf(cf[7], 4096.f, fmaf(cf[6], 256.f, fmaf(cf[5], 16.f, cf[4])));
-    return (uint32_t)a | ((uint32_t)b << 16);
-  } else {
-    float a = cf[0];
-#pragma unroll
-    for (int k = 1; k < 8; ++k) a = fmaf(cf[k], (float)(1 << (2 * k)), a);
-    return (uint32_t)a;
-  }
+// The same code without a division per element.  The quotient is approximated by a product with the correctly
+// rounded reciprocal (error below 2 units in the last place of a number below 16, i.e. < 4e-6) and rounded to the
+// nearest integer by adding 1.5 * 2^23 (round-to-nearest-even, like rintf; the integer then sits in the low mantissa
+// bits).  Only an approximation within 1e-4 of a rounding boundary could round differently from the exact quotient:
+// those elements (about one in ten thousand) take the division.  x >= lo by construction, so only the upper clamp is
+// needed.  Bit-identical to affine_code.
+__device__ __forceinline__ uint32_t affine_code_fast(float x, float lo, float inv, const float* scale_ptr, float qmax) {
+  const float q = fminf(__fmul_rn(__fsub_rn(x, lo), inv), qmax);
+  const float r = __fadd_rn(q, 12582912.f);
+  const float frac = __fsub_rn(__fsub_rn(r, 12582912.f), q);
+  if (fabsf(frac) > 0.4999f) return affine_code(x, lo, *scale_ptr, qmax);
+  return __float_as_uint(r) & 0xffu;
 }
 
 // One CTA per (token group, head, batch); blockDim.x == D.
@@ -217,7 +164,6 @@ __global__ void __launch_bounds__(128) kivi_append128_kernel(const void* k_src, 
   float* vs_s = ki_s + D;                                   // [G][VG]
   float* vl_s = vs_s + G * VG;                              // [G][VG]
   float* vi_s = vl_s + G * VG;                              // [G][VG] 1 / scale
-  float* kp_s = vi_s + G * VG;                              // [2 token halves][min | max][D] partial key statistics
   const int g = blockIdx.x, h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const float qmax = (float)((1 << BITS) - 1);
   const int tok0 = t0 + g * G;
@@ -230,27 +176,15 @@ __global__ void __launch_bounds__(128) kivi_append128_kernel(const void* k_src, 
     reinterpret_cast<uint4*>(vt)[i] = __ldg(reinterpret_cast<const uint4*>(vg_ + (int64_t)t * st) + part);
   }
   __syncthreads();
-  // ---- keys: per channel over the G tokens of the group.  Minimum and maximum of 16-bit numbers are exact in
-  // 16 bits: a thread takes two channels (one 32-bit word per token, packed min / max) over half of the tokens ----
-  {
-    using T2 = typename Packed2<T>::type;
-    const int cp = tid & 63, th = tid >> 6;
-    const int tb = th * (G / 2);
-    T2 mn = *reinterpret_cast<const T2*>(kt + tb * D + 2 * cp), mx = mn;
-    for (int t = tb + 1; t < tb + G / 2; ++t) {
-      const T2 v = *reinterpret_cast<const T2*>(kt + t * D + 2 * cp);
-      mn = __hmin2(mn, v);
-      mx = __hmax2(mx, v);
-    }
-    kp_s[(th * 2 + 0) * D + 2 * cp] = to_float<T>(mn.x);
-    kp_s[(th * 2 + 0) * D + 2 * cp + 1] = to_float<T>(mn.y);
-    kp_s[(th * 2 + 1) * D + 2 * cp] = to_float<T>(mx.x);
-    kp_s[(th * 2 + 1) * D + 2 * cp + 1] = to_float<T>(mx.y);
-  }
-  __syncthreads();
+  // ---- keys: per channel over the G tokens of the group ----
   {
     const int d = tid;
-    const float lo = fminf(kp_s[d], kp_s[2 * D + d]), hi = fmaxf(kp_s[D + d], kp_s[3 * D + d]);
+    float lo = INFINITY, hi = -INFINITY;
+    for (int t = 0; t < G; ++t) {
+      const float x = to_float<T>(kt[t * D + d]);
+      lo = fminf(lo, x);
+      hi = fmaxf(hi, x);
+    }
     const float scale = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), qmax), 1e-8f);
     const size_t mi = (bh * (c.cap / G) + tok0 / G) * D + kmeta_pos(d, D);
     c.k_scale[mi] = scale;
@@ -299,10 +233,11 @@ __global__ void __launch_bounds__(128) kivi_append128_kernel(const void* k_src, 
         const float4 i0 = *reinterpret_cast<const float4*>(ki_s + c0 + j), i1 = *reinterpret_cast<const float4*>(ki_s + c0 + j + 4);
         const float lo8[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
         const float in8[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
-        float x8[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) x8[k] = to_float<T>(e[k]);
-        w[(j * BITS) >> 5] |= affine_codes8<BITS>(x8, lo8, in8, ks_s + c0 + j, 1, qmax) << ((j * BITS) & 31);
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t code = affine_code_fast(to_float<T>(e[k]), lo8[k], in8[k], ks_s + c0 + j + k, qmax);
+          w[((j + k) * BITS) >> 5] |= code << (((j + k) * BITS) & 31);
+        }
       }
       *reinterpret_cast<uint4*>(dst + (size_t)i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -318,16 +253,9 @@ __global__ void __launch_bounds__(128) kivi_append128_kernel(const void* k_src, 
       const int nw = min(4, words - w0);
       for (int wi = 0; wi < nw; ++wi)
 #pragma unroll
-        for (int k0 = 0; k0 < TPW; k0 += 8) {
-          const int tb = (w0 + wi) * TPW + k0;
-          float x8[8], lo8[8], in8[8];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            x8[k] = to_float<T>(vt[(tb + k) * D + d]);
-            lo8[k] = vl_s[(tb + k) * VG + gi];
-            in8[k] = vi_s[(tb + k) * VG + gi];
-          }
-          w[wi] |= affine_codes8<BITS>(x8, lo8, in8, vs_s + tb * VG + gi, VG, qmax) << (k0 * BITS);
+        for (int k = 0; k < TPW; ++k) {
+          const int t = (w0 + wi) * TPW + k;
+          w[wi] |= affine_code_fast(to_float<T>(vt[t * D + d]), vl_s[t * VG + gi], vi_s[t * VG + gi], vs_s + t * VG + gi, qmax) << (k * BITS);
         }
       if (nw == 4) *reinterpret_cast<uint4*>(row + w0 * 4) = make_uint4(w[0], w[1], w[2], w[3]);
       else if (nw == 2) *reinterpret_cast<uint2*>(row + w0 * 4) = make_uint2(w[0], w[1]);
@@ -485,7 +413,7 @@ int pare_kivi_append(const void* k_src, const void* v_src, int src_dtype, int64_
   if (D == 128 && (bits == 2 || bits == 4) && (vg == 1 || vg == 4) && group <= 64 && (src_dtype == PARE_F16 || src_dtype == PARE_BF16) &&
       pare::aligned16(k_src) && pare::aligned16(v_src) && stride_b % 8 == 0 && stride_h % 8 == 0 && stride_t % 8 == 0 &&
       pare::aligned16(k_codes) && pare::aligned16(v_codes)) {
-    const size_t smem = (size_t)2 * group * 128 * 2 + 7 * 128 * sizeof(float) + 3 * (size_t)group * vg * sizeof(float);
+    const size_t smem = (size_t)2 * group * 128 * 2 + 3 * 128 * sizeof(float) + 3 * (size_t)group * vg * sizeof(float);
 #define PARE_AP(T)                                                                                                                   \
   do {                                                                                                                               \
     if (bits == 4 && vg == 1) pare::kivi_append128_kernel<T, 4, 1><<<grid, 128, smem, s>>>(k_src, v_src, stride_b, stride_h, stride_t, t0, c); \
