@@ -291,3 +291,26 @@ def test_rope_helpers_agree_with_the_oracle():
     n0 = x.numpy()[..., :64] ** 2 + x.numpy()[..., 64:] ** 2
     n1 = y[..., :64] ** 2 + y[..., 64:] ** 2
     assert np.allclose(n0, n1, rtol=1e-5, atol=1e-6)
+
+
+def test_reference_arm_prints_the_contract_line():
+    """``bench.py --impl reference`` (the CPU op sequence of the reference, timed on the host) prints one JSON line with
+    the keys the harness reads; under a multi-rank launch only rank 0 prints."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    cmd = [sys.executable, str(root / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0", "--layers", "1",
+           "--context", "256"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=root)
+    assert out.returncode == 0, out.stderr[-500:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["higher_is_better"] is True and line["value"] > 0
+    assert line["unit"] == "tok/s" and line["metric"].startswith("decode_tok_s")
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"] == {"value": line["value"], "unit": line["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    other = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=root, env=dict(os.environ, RANK="1", WORLD_SIZE="2"))
+    assert other.returncode == 0 and other.stdout.strip() == ""
