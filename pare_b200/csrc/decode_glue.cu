@@ -193,6 +193,41 @@ __global__ void rope_kernel(const T* x, int64_t sb, int64_t sh, int64_t st, T* o
   }
 }
 
+// The same, eight channel pairs per thread with 16-byte accesses (rows 16-byte aligned, D a multiple of 16).
+template <typename T>
+__global__ void rope_vec_kernel(const T* x, int64_t sb, int64_t sh, int64_t st, T* out, const float* rows, int B, int H, int Tn, int D) {
+  const int half = D >> 1, per_row = half >> 3;
+  const int64_t total = (int64_t)B * H * Tn * per_row;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % per_row) * 8;
+    const int64_t row = idx / per_row;              // (b * H + h) * Tn + t
+    const int t = (int)(row % Tn);
+    const int64_t bh = row / Tn;
+    const int h = (int)(bh % H), b = (int)(bh / H);
+    const T* src = x + (int64_t)b * sb + (int64_t)h * sh + (int64_t)t * st;
+    const uint4 ra = *reinterpret_cast<const uint4*>(src + i), rb = *reinterpret_cast<const uint4*>(src + half + i);
+    const T* a = reinterpret_cast<const T*>(&ra);
+    const T* bb = reinterpret_cast<const T*>(&rb);
+    const float* cs = rows + (int64_t)t * D;
+    const float4 c0 = *reinterpret_cast<const float4*>(cs + i), c1 = *reinterpret_cast<const float4*>(cs + i + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(cs + half + i), s1 = *reinterpret_cast<const float4*>(cs + half + i + 4);
+    const float co[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float si[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    uint4 oa, ob;
+    T* pa = reinterpret_cast<T*>(&oa);
+    T* pb = reinterpret_cast<T*>(&ob);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float av = to_float<T>(a[j]), bv = to_float<T>(bb[j]);
+      pa[j] = from_float<T>(__fsub_rn(__fmul_rn(av, co[j]), __fmul_rn(bv, si[j])));
+      pb[j] = from_float<T>(__fadd_rn(__fmul_rn(bv, co[j]), __fmul_rn(av, si[j])));
+    }
+    T* dst = out + row * D;
+    *reinterpret_cast<uint4*>(dst + i) = oa;
+    *reinterpret_cast<uint4*>(dst + half + i) = ob;
+  }
+}
+
 }  // namespace
 }  // namespace pare
 
@@ -232,9 +267,20 @@ int pare_silu_mul(const void* gate_up, void* out, void* prepared_out, int rows, 
 int pare_rope(const void* x, int64_t stride_b, int64_t stride_h, int64_t stride_t, void* out, const float* rows, int B, int H,
               int T, int D, int dtype, void* stream) {
   PARE_REQUIRE(x && out && rows && B > 0 && H > 0 && T > 0 && D > 0 && (D % 2) == 0, PARE_ERR_SHAPE);
-  const int64_t total = (int64_t)B * H * T * (D / 2);
-  const unsigned blocks = (unsigned)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const bool vec = (D % 16) == 0 && pare::aligned16(x) && pare::aligned16(out) && pare::aligned16(rows) && stride_b % 8 == 0 &&
+                   stride_h % 8 == 0 && stride_t % 8 == 0;
+  const int64_t total = (int64_t)B * H * T * (vec ? D / 16 : D / 2);
+  const unsigned blocks = (unsigned)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
+  if (vec) {
+    if (dtype == PARE_F16)
+      pare::rope_vec_kernel<__half><<<blocks, 256, 0, s>>>((const __half*)x, stride_b, stride_h, stride_t, (__half*)out, rows, B, H, T, D);
+    else if (dtype == PARE_BF16)
+      pare::rope_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)x, stride_b, stride_h, stride_t, (__nv_bfloat16*)out, rows, B, H, T, D);
+    else
+      return PARE_ERR_DTYPE;
+    return pare::launch_status();
+  }
   if (dtype == PARE_F16)
     pare::rope_kernel<__half><<<blocks, 256, 0, s>>>((const __half*)x, stride_b, stride_h, stride_t, (__half*)out, rows, B, H, T, D);
   else if (dtype == PARE_BF16)

@@ -502,8 +502,10 @@ def test_rope_kernel_bit_exact_on_strided_views(dtype, cuda_lib):
     k = qkv[..., hq * D:(hq + hkv) * D].unflatten(2, (hkv, D)).transpose(1, 2)
     table = rope_table(T + 5, D, 500000.0, device="cuda")
     rows = ok.rope_rows(np.arange(T + 5), D, 500000.0)
-    for x in (q, k):
-        assert not x.is_contiguous()
+    off = torch.randn(B * hkv * T * D + 1, device="cuda").to(dtype)[1:].view(B, hkv, T, D)   # 2 bytes off: the scalar kernel
+    assert off.data_ptr() % 16 != 0
+    for x in (q, k, off):
+        assert x is off or not x.is_contiguous()
         got = apply_rope(x, table[3:3 + T])
         assert got.shape == x.shape and got.dtype == dtype and got.is_contiguous()
         want = torch.from_numpy(ok.apply_rope(x.float().cpu().numpy(), rows[3:3 + T])).to(dtype)
